@@ -1,0 +1,169 @@
+"""ctypes binding of ``libbastile_b200.so`` (declarations: ``include/bastile_b200.h``).
+
+The library is the only implementation of the ops: when it cannot be loaded the
+ops raise, they never fall back to torch or the CPU.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_void_p, POINTER
+from pathlib import Path
+
+import torch
+
+BT_BF16, BT_FP16, BT_FP32 = 0, 1, 2
+
+_DTYPES = {torch.bfloat16: BT_BF16, torch.float16: BT_FP16, torch.float32: BT_FP32}
+
+_lock = threading.Lock()
+_lib = None
+
+I64x3 = c_int64 * 3
+I64x2 = c_int64 * 2
+
+# name -> (restype, argtypes); mirrors include/bastile_b200.h one to one.
+SIGNATURES = {
+    "bt_version": (c_int, []),
+    "bt_last_error": (c_char_p, []),
+    "bt_sm_count": (c_int, []),
+    "bt_rmsnorm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                               c_float, c_int, c_void_p]),
+    "bt_rmsnorm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                               c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "bt_rmsnorm_bwd_ws_bytes": (c_int64, [c_int64]),
+    "bt_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                        c_int64, c_int64, POINTER(c_int64), POINTER(c_int64), POINTER(c_int64),
+                        POINTER(c_int64), POINTER(c_int64), c_int64, c_int, c_int, c_void_p]),
+    "bt_swiglu_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int,
+                              c_void_p]),
+    "bt_swiglu_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                              c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "bt_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                        c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "bt_mlp_fwd": (c_int, [c_void_p] * 8 + [c_int64] * 4 + [c_int, c_void_p, c_void_p]),
+    "bt_mlp_bwd": (c_int, [c_void_p] * 14 + [c_int64] * 5 + [c_int, c_void_p, c_void_p]),
+    "bt_lce_logits_stats": (c_int, [c_void_p] * 6 + [c_int64] * 7 + [c_int, c_void_p, c_void_p]),
+    "bt_lce_num_vtiles": (c_int64, [c_int64]),
+    "bt_lce_row_stats": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "bt_lce_dlogits": (c_int, [c_void_p] * 5 + [c_int64] * 5 + [c_int, c_int, c_void_p]),
+    "bt_lce_count_valid": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
+    "bt_lce_reduce_loss": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "bt_scale_cast": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]),
+}
+
+
+def lib_path() -> Path:
+    env = os.environ.get("BASTILE_B200_LIB")
+    return Path(env) if env else Path(__file__).resolve().parent / "libbastile_b200.so"
+
+
+def get_lib() -> ctypes.CDLL:
+    """Load (once) and return the shared library; raises if it is not built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            path = lib_path()
+            if not path.exists():
+                raise RuntimeError(
+                    f"{path} is missing: build it with `python -m bastile_b200.build` "
+                    "(bastile_b200 has no fallback implementation)"
+                )
+            lib = ctypes.CDLL(str(path))
+            for name, (res, args) in SIGNATURES.items():
+                fn = getattr(lib, name)  # AttributeError here = library older than the header
+                fn.restype = res
+                fn.argtypes = args
+            _lib = lib
+    return _lib
+
+
+class BastileB200Error(RuntimeError):
+    pass
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = get_lib().bt_last_error().decode(errors="replace")
+        raise BastileB200Error(f"{what} failed (code {rc}): {msg}")
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise TypeError(f"bastile_b200: unsupported dtype {dtype}") from None
+
+
+def require_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = tensors[0].device
+    for t in tensors:
+        if t.device.type != "cuda":
+            raise RuntimeError(
+                "bastile_b200 ops run on CUDA (sm_100a) tensors only; got a tensor on "
+                f"'{t.device}'. There is no CPU implementation."
+            )
+        if t.device != dev:
+            raise RuntimeError(f"bastile_b200: tensors on different devices ({dev} vs {t.device})")
+    return dev
+
+
+def stream_ptr(dev: torch.device) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+class device_of:
+    """Make ``dev`` the current CUDA device for the duration of a launch."""
+
+    def __init__(self, dev: torch.device):
+        self.idx = dev.index if dev.index is not None else torch.cuda.current_device()
+        self.prev = -1
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
+# Per (device, stream) scratch that must start zeroed and that kernels leave zeroed.
+_zero_ws: dict[tuple[int, int], torch.Tensor] = {}
+# Per (device, stream) int32 status word for the bounded waits of the GEMM kernels.
+_status: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def zero_workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
+    key = (dev.index or 0, stream_ptr(dev))
+    buf = _zero_ws.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(nbytes, 1 << 16), dtype=torch.uint8, device=dev)
+        _zero_ws[key] = buf
+    return buf
+
+
+def status_word(dev: torch.device) -> torch.Tensor:
+    key = (dev.index or 0, stream_ptr(dev))
+    buf = _status.get(key)
+    if buf is None:
+        buf = torch.zeros(1, dtype=torch.int32, device=dev)
+        _status[key] = buf
+    return buf
+
+
+def check_status(dev: torch.device, what: str) -> None:
+    """Synchronising read of the device status word (tests / debugging only)."""
+    st = status_word(dev)
+    v = int(st.item())
+    if v != 0:
+        st.zero_()
+        raise BastileB200Error(f"{what}: a bounded device-side wait ran out (status {v:#x})")

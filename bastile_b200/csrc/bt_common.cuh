@@ -1,0 +1,144 @@
+// Shared host/device helpers of the bastile_b200 kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/bastile_b200.h"
+
+namespace bt {
+
+// ---------------------------------------------------------------- errors
+void set_error(const char* fmt, ...);  // defined in c_api.cu (thread-local text)
+
+#define BT_CHECK_ARG(cond, ...)      \
+  do {                               \
+    if (!(cond)) {                   \
+      ::bt::set_error(__VA_ARGS__);  \
+      return BT_ERR_ARG;             \
+    }                                \
+  } while (0)
+
+#define BT_CHECK_LAUNCH(what)                                                \
+  do {                                                                       \
+    cudaError_t e__ = cudaGetLastError();                                    \
+    if (e__ != cudaSuccess) {                                                \
+      ::bt::set_error("%s: %s", (what), cudaGetErrorString(e__));            \
+      return BT_ERR_LAUNCH;                                                  \
+    }                                                                        \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int sm_count();  // cached per device (c_api.cu)
+
+// ---------------------------------------------------------------- 16-byte vectors
+template <typename T>
+struct Vec16 {
+  static constexpr int kElems = 16 / sizeof(T);
+  uint4 raw;
+};
+
+__device__ __forceinline__ uint4 ld_global_v4(const void* p) {
+  return *reinterpret_cast<const uint4*>(p);
+}
+// Streaming variants: data that is touched exactly once should not displace the
+// weights / cos / sin rows that every CTA re-reads.
+__device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_global_v4(void* p, uint4 v) {
+  *reinterpret_cast<uint4*>(p) = v;
+}
+
+// unpack / pack one 16-byte vector to fp32 lanes
+template <typename T>
+struct Cvt;
+
+template <>
+struct Cvt<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ __forceinline__ static void unpack(uint4 v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  __device__ __forceinline__ static uint4 pack(const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  __device__ __forceinline__ static float to_f(__nv_bfloat16 x) { return __bfloat162float(x); }
+  __device__ __forceinline__ static __nv_bfloat16 from_f(float x) { return __float2bfloat16_rn(x); }
+};
+
+template <>
+struct Cvt<__half> {
+  static constexpr int N = 8;
+  __device__ __forceinline__ static void unpack(uint4 v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+      float2 t = __half22float2(h);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+  __device__ __forceinline__ static uint4 pack(const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  __device__ __forceinline__ static float to_f(__half x) { return __half2float(x); }
+  __device__ __forceinline__ static __half from_f(float x) { return __float2half_rn(x); }
+};
+
+template <>
+struct Cvt<float> {
+  static constexpr int N = 4;
+  __device__ __forceinline__ static void unpack(uint4 v, float (&f)[4]) {
+    f[0] = __uint_as_float(v.x);
+    f[1] = __uint_as_float(v.y);
+    f[2] = __uint_as_float(v.z);
+    f[3] = __uint_as_float(v.w);
+  }
+  __device__ __forceinline__ static uint4 pack(const float (&f)[4]) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]),
+                      __float_as_uint(f[3]));
+  }
+  __device__ __forceinline__ static float to_f(float x) { return x; }
+  __device__ __forceinline__ static float from_f(float x) { return x; }
+};
+
+// Sum over the G consecutive lanes (G a power of two <= 32) that hold one row.
+template <int G>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = G / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+}  // namespace bt

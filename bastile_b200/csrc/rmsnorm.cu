@@ -1,0 +1,593 @@
+// RMSNorm forward / backward for sm_100a: bandwidth-bound, every row is read
+// from HBM exactly once and kept in registers between the reduction and the
+// scaled write-back.
+//
+// Layouts
+//   rows kernel : a group of LPR lanes (8..32) owns one row, VPT 16-byte vectors
+//                 per lane; a 256-thread CTA works on 256/LPR rows x RPI at a
+//                 time and strides over the matrix persistently.  Row sums are
+//                 warp shuffles only - no shared memory, no __syncthreads.
+//   block kernel: (backward, wide rows) all 256 threads share one row so that a
+//                 thread owns a fixed set of columns and can keep its slice of
+//                 dw in registers across the rows it visits.
+//   generic     : any N / alignment, scalar accesses; correctness net only.
+//
+// dw is accumulated as fp32 partial sums: registers -> shared -> one global
+// atomic per column per CTA into a zeroed scratch row; the last CTA to finish
+// converts the row to the weight dtype and zeroes the scratch again.
+#include "bt_common.cuh"
+
+namespace bt {
+namespace {
+
+constexpr int kThreads = 256;
+
+// ------------------------------------------------------------------ forward
+template <typename T, int VPT, int LPR, int RPI>
+__global__ void __launch_bounds__(kThreads)
+rms_fwd_rows(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+             float* __restrict__ rstd, int64_t M, int N, int64_t ld_x, int64_t ld_y, float eps) {
+  constexpr int E = Cvt<T>::N;
+  constexpr int kGroups = kThreads / LPR;
+  const int lane = threadIdx.x % LPR;
+  const int group = threadIdx.x / LPR;
+  const int nv = N / E;
+  const float inv_n = 1.0f / static_cast<float>(N);
+  const int64_t rows_per_iter = static_cast<int64_t>(kGroups) * RPI;
+
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * rows_per_iter; base < M;
+       base += static_cast<int64_t>(gridDim.x) * rows_per_iter) {
+    uint4 xv[RPI][VPT];
+#pragma unroll
+    for (int r = 0; r < RPI; ++r) {
+      const int64_t row = base + r * kGroups + group;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = lane + i * LPR;
+        xv[r][i] = (row < M && v < nv) ? ld_stream_v4(x + row * ld_x + static_cast<int64_t>(v) * E)
+                                       : make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < RPI; ++r) {
+      const int64_t row = base + r * kGroups + group;
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        float f[E];
+        Cvt<T>::unpack(xv[r][i], f);
+#pragma unroll
+        for (int e = 0; e < E; ++e) ss = fmaf(f[e], f[e], ss);
+      }
+      ss = group_sum<LPR>(ss);
+      const float rs = rsqrtf(ss * inv_n + eps);
+      if (row < M) {
+        if (lane == 0) rstd[row] = rs;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+          const int v = lane + i * LPR;
+          if (v < nv) {
+            float f[E], wf[E];
+            Cvt<T>::unpack(xv[r][i], f);
+            Cvt<T>::unpack(ld_global_v4(w + static_cast<int64_t>(v) * E), wf);
+#pragma unroll
+            for (int e = 0; e < E; ++e) f[e] = f[e] * rs * wf[e];
+            st_global_v4(y + row * ld_y + static_cast<int64_t>(v) * E, Cvt<T>::pack(f));
+          }
+        }
+      }
+    }
+  }
+}
+
+// One CTA per row, scalar accesses, two passes (second one from cache).
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+rms_fwd_generic(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                float* __restrict__ rstd, int64_t M, int64_t N, int64_t ld_x, int64_t ld_y,
+                float eps) {
+  __shared__ float red[kThreads / 32];
+  __shared__ float s_rs;
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    const T* xr = x + row * ld_x;
+    float ss = 0.f;
+    for (int64_t c = threadIdx.x; c < N; c += kThreads) {
+      const float f = Cvt<T>::to_f(xr[c]);
+      ss = fmaf(f, f, ss);
+    }
+    ss = group_sum<32>(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int i = 0; i < kThreads / 32; ++i) t += red[i];
+      s_rs = rsqrtf(t / static_cast<float>(N) + eps);
+      rstd[row] = s_rs;
+    }
+    __syncthreads();
+    const float rs = s_rs;
+    for (int64_t c = threadIdx.x; c < N; c += kThreads)
+      y[row * ld_y + c] = Cvt<T>::from_f(Cvt<T>::to_f(xr[c]) * rs * Cvt<T>::to_f(w[c]));
+    __syncthreads();
+  }
+}
+
+// ----------------------------------------------------------------- backward
+// Scratch layout: float acc[N] followed by one uint32 arrival counter.
+template <typename T>
+__device__ __forceinline__ void dw_finalize(float* __restrict__ ws, T* __restrict__ dw, int N) {
+  __shared__ bool s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned int* counter = reinterpret_cast<unsigned int*>(ws + N);
+    const unsigned int ticket = atomicAdd(counter, 1u);
+    s_last = (ticket == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (s_last) {
+    __threadfence();
+    for (int c = threadIdx.x; c < N; c += blockDim.x) {
+      const float v = __ldcg(ws + c);
+      dw[c] = Cvt<T>::from_f(v);
+      ws[c] = 0.f;
+    }
+    if (threadIdx.x == 0) *reinterpret_cast<unsigned int*>(ws + N) = 0u;
+  }
+}
+
+template <typename T, int VPT, int LPR, int RPI>
+__global__ void __launch_bounds__(kThreads)
+rms_bwd_rows(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+             const float* __restrict__ rstd, T* __restrict__ dx, T* __restrict__ dw,
+             float* __restrict__ ws, int64_t M, int N, int64_t ld_dy, int64_t ld_x,
+             int64_t ld_dx) {
+  constexpr int E = Cvt<T>::N;
+  constexpr int kGroups = kThreads / LPR;
+  extern __shared__ float s_dw[];  // N floats
+  const int lane = threadIdx.x % LPR;
+  const int group = threadIdx.x / LPR;
+  const int nv = N / E;
+  const float inv_n = 1.0f / static_cast<float>(N);
+  const int64_t rows_per_iter = static_cast<int64_t>(kGroups) * RPI;
+
+  for (int c = threadIdx.x; c < N; c += kThreads) s_dw[c] = 0.f;
+
+  float wf[VPT][E];
+  float acc[VPT][E];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = lane + i * LPR;
+    uint4 wv = (v < nv) ? ld_global_v4(w + static_cast<int64_t>(v) * E) : make_uint4(0, 0, 0, 0);
+    Cvt<T>::unpack(wv, wf[i]);
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[i][e] = 0.f;
+  }
+
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * rows_per_iter; base < M;
+       base += static_cast<int64_t>(gridDim.x) * rows_per_iter) {
+    uint4 xv[RPI][VPT], gv[RPI][VPT];
+    float rs[RPI];
+#pragma unroll
+    for (int r = 0; r < RPI; ++r) {
+      const int64_t row = base + r * kGroups + group;
+      rs[r] = (row < M) ? rstd[row] : 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = lane + i * LPR;
+        const bool ok = (row < M && v < nv);
+        xv[r][i] = ok ? ld_stream_v4(x + row * ld_x + static_cast<int64_t>(v) * E)
+                      : make_uint4(0, 0, 0, 0);
+        gv[r][i] = ok ? ld_stream_v4(dy + row * ld_dy + static_cast<int64_t>(v) * E)
+                      : make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < RPI; ++r) {
+      const int64_t row = base + r * kGroups + group;
+      float xh[VPT][E], wdy[VPT][E];
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        float xf[E], gf[E];
+        Cvt<T>::unpack(xv[r][i], xf);
+        Cvt<T>::unpack(gv[r][i], gf);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          xh[i][e] = xf[e] * rs[r];
+          wdy[i][e] = gf[e] * wf[i][e];
+          dot = fmaf(xh[i][e], wdy[i][e], dot);
+          acc[i][e] = fmaf(gf[e], xh[i][e], acc[i][e]);
+        }
+      }
+      dot = group_sum<LPR>(dot) * inv_n;
+      if (row < M) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+          const int v = lane + i * LPR;
+          if (v < nv) {
+            float o[E];
+#pragma unroll
+            for (int e = 0; e < E; ++e) o[e] = (wdy[i][e] - xh[i][e] * dot) * rs[r];
+            st_global_v4(dx + row * ld_dx + static_cast<int64_t>(v) * E, Cvt<T>::pack(o));
+          }
+        }
+      }
+    }
+  }
+
+  __syncthreads();  // s_dw zeroed
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = lane + i * LPR;
+    if (v < nv) {
+#pragma unroll
+      for (int e = 0; e < E; ++e) atomicAdd(&s_dw[v * E + e], acc[i][e]);
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < N; c += kThreads) atomicAdd(ws + c, s_dw[c]);
+  dw_finalize<T>(ws, dw, N);
+}
+
+// Wide rows: one row is spread over the whole CTA, R rows per iteration.
+template <typename T, int VPT, int R>
+__global__ void __launch_bounds__(kThreads)
+rms_bwd_block(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+              const float* __restrict__ rstd, T* __restrict__ dx, T* __restrict__ dw,
+              float* __restrict__ ws, int64_t M, int N, int64_t ld_dy, int64_t ld_x,
+              int64_t ld_dx) {
+  constexpr int E = Cvt<T>::N;
+  constexpr int kWarps = kThreads / 32;
+  __shared__ float s_red[2][kWarps][R];
+  const int nv = N / E;
+  const float inv_n = 1.0f / static_cast<float>(N);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  float wf[VPT][E];
+  float acc[VPT][E];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * kThreads;
+    uint4 wv = (v < nv) ? ld_global_v4(w + static_cast<int64_t>(v) * E) : make_uint4(0, 0, 0, 0);
+    Cvt<T>::unpack(wv, wf[i]);
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[i][e] = 0.f;
+  }
+
+  int buf = 0;
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * R; base < M;
+       base += static_cast<int64_t>(gridDim.x) * R, buf ^= 1) {
+    uint4 xv[R][VPT], gv[R][VPT];
+    float rs[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int64_t row = base + r;
+      rs[r] = (row < M) ? rstd[row] : 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = threadIdx.x + i * kThreads;
+        const bool ok = (row < M && v < nv);
+        xv[r][i] = ok ? ld_stream_v4(x + row * ld_x + static_cast<int64_t>(v) * E)
+                      : make_uint4(0, 0, 0, 0);
+        gv[r][i] = ok ? ld_stream_v4(dy + row * ld_dy + static_cast<int64_t>(v) * E)
+                      : make_uint4(0, 0, 0, 0);
+      }
+    }
+    float dot[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float d = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        float xf[E], gf[E];
+        Cvt<T>::unpack(xv[r][i], xf);
+        Cvt<T>::unpack(gv[r][i], gf);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const float xh = xf[e] * rs[r];
+          d = fmaf(xh, gf[e] * wf[i][e], d);
+          acc[i][e] = fmaf(gf[e], xh, acc[i][e]);
+        }
+      }
+      d = group_sum<32>(d);
+      if (lane == 0) s_red[buf][warp][r] = d;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float d = 0.f;
+#pragma unroll
+      for (int k = 0; k < kWarps; ++k) d += s_red[buf][k][r];
+      dot[r] = d * inv_n;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int64_t row = base + r;
+      if (row < M) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+          const int v = threadIdx.x + i * kThreads;
+          if (v < nv) {
+            float xf[E], gf[E], o[E];
+            Cvt<T>::unpack(xv[r][i], xf);
+            Cvt<T>::unpack(gv[r][i], gf);
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+              const float xh = xf[e] * rs[r];
+              o[e] = (gf[e] * wf[i][e] - xh * dot[r]) * rs[r];
+            }
+            st_global_v4(dx + row * ld_dx + static_cast<int64_t>(v) * E, Cvt<T>::pack(o));
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * kThreads;
+    if (v < nv) {
+#pragma unroll
+      for (int e = 0; e < E; ++e) atomicAdd(ws + v * E + e, acc[i][e]);
+    }
+  }
+  dw_finalize<T>(ws, dw, N);
+}
+
+// Generic backward, part 1: dx, one CTA per row (scalar).
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+rms_bwd_dx_generic(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+                   const float* __restrict__ rstd, T* __restrict__ dx, int64_t M, int64_t N,
+                   int64_t ld_dy, int64_t ld_x, int64_t ld_dx) {
+  __shared__ float red[kThreads / 32];
+  __shared__ float s_dot;
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    const float rs = rstd[row];
+    float d = 0.f;
+    for (int64_t c = threadIdx.x; c < N; c += kThreads)
+      d = fmaf(Cvt<T>::to_f(x[row * ld_x + c]) * rs,
+               Cvt<T>::to_f(dy[row * ld_dy + c]) * Cvt<T>::to_f(w[c]), d);
+    d = group_sum<32>(d);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = d;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int i = 0; i < kThreads / 32; ++i) t += red[i];
+      s_dot = t / static_cast<float>(N);
+    }
+    __syncthreads();
+    const float dot = s_dot;
+    for (int64_t c = threadIdx.x; c < N; c += kThreads) {
+      const float xh = Cvt<T>::to_f(x[row * ld_x + c]) * rs;
+      const float wdy = Cvt<T>::to_f(dy[row * ld_dy + c]) * Cvt<T>::to_f(w[c]);
+      dx[row * ld_dx + c] = Cvt<T>::from_f((wdy - xh * dot) * rs);
+    }
+    __syncthreads();
+  }
+}
+
+// Generic backward, part 2: dw.  blockDim = (32 columns, 8 row lanes).
+template <typename T>
+__global__ void rms_bwd_dw_generic(const T* __restrict__ dy, const T* __restrict__ x,
+                                   const float* __restrict__ rstd, T* __restrict__ dw,
+                                   float* __restrict__ ws, int64_t M, int N, int64_t ld_dy,
+                                   int64_t ld_x) {
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  float a = 0.f;
+  if (c < N) {
+    for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < M;
+         row += static_cast<int64_t>(gridDim.y) * blockDim.y)
+      a = fmaf(Cvt<T>::to_f(dy[row * ld_dy + c]), Cvt<T>::to_f(x[row * ld_x + c]) * rstd[row], a);
+    atomicAdd(ws + c, a);
+  }
+  // dw_finalize counts CTAs through gridDim.x only: fold the 2-D grid into it.
+  __shared__ bool s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0 && threadIdx.y == 0) {
+    unsigned int* counter = reinterpret_cast<unsigned int*>(ws + N);
+    const unsigned int ticket = atomicAdd(counter, 1u);
+    s_last = (ticket == gridDim.x * gridDim.y - 1);
+  }
+  __syncthreads();
+  if (s_last) {
+    __threadfence();
+    for (int i = threadIdx.y * 32 + threadIdx.x; i < N; i += 32 * blockDim.y) {
+      dw[i] = Cvt<T>::from_f(__ldcg(ws + i));
+      ws[i] = 0.f;
+    }
+    if (threadIdx.x == 0 && threadIdx.y == 0) *reinterpret_cast<unsigned int*>(ws + N) = 0u;
+  }
+}
+
+// ------------------------------------------------------------ host dispatch
+struct RowCfg {
+  int lpr, vpt, rpi;
+};
+
+// nv = 16-byte vectors per row.  Returns false when the rows layout does not apply.
+bool pick_rows(int64_t nv, int max_vpt, RowCfg* c) {
+  if (nv <= 0) return false;
+  int lpr = 8;
+  while (lpr < 32 && lpr < nv) lpr *= 2;
+  int vpt = 1;
+  while (static_cast<int64_t>(vpt) * lpr < nv) vpt *= 2;
+  if (vpt > max_vpt) return false;
+  c->lpr = lpr;
+  c->vpt = vpt;
+  c->rpi = (vpt == 1) ? 4 : (vpt == 2 ? 2 : 1);
+  return true;
+}
+
+int grid_for(int64_t work_items, int ctas_per_sm) {
+  const int64_t cap = static_cast<int64_t>(sm_count()) * ctas_per_sm;
+  return static_cast<int>(work_items < cap ? (work_items < 1 ? 1 : work_items) : cap);
+}
+
+template <typename T>
+int fwd_t(const void* x, const void* w, void* y, float* rstd, int64_t M, int64_t N, int64_t ld_x,
+          int64_t ld_y, float eps, cudaStream_t s) {
+  constexpr int E = Cvt<T>::N;
+  const T* xp = static_cast<const T*>(x);
+  const T* wp = static_cast<const T*>(w);
+  T* yp = static_cast<T*>(y);
+  RowCfg c{};
+  const bool vec_ok = (N % E == 0) && (ld_x % E == 0) && (ld_y % E == 0) && aligned16(x) &&
+                      aligned16(w) && aligned16(y) && pick_rows(N / E, 16, &c);
+  if (!vec_ok) {
+    rms_fwd_generic<T><<<grid_for(M, 8), kThreads, 0, s>>>(xp, wp, yp, rstd, M, N, ld_x, ld_y, eps);
+    BT_CHECK_LAUNCH("rms_fwd_generic");
+    return BT_OK;
+  }
+  const int64_t rows_per_iter = static_cast<int64_t>(kThreads / c.lpr) * c.rpi;
+  const int grid = grid_for(ceil_div(M, rows_per_iter), c.vpt >= 16 ? 2 : 4);
+#define BT_FWD(L, V, R)                                                                         \
+  if (c.lpr == L && c.vpt == V) {                                                               \
+    rms_fwd_rows<T, V, L, R><<<grid, kThreads, 0, s>>>(xp, wp, yp, rstd, M, static_cast<int>(N), \
+                                                       ld_x, ld_y, eps);                        \
+    BT_CHECK_LAUNCH("rms_fwd_rows");                                                            \
+    return BT_OK;                                                                               \
+  }
+  BT_FWD(8, 1, 4)
+  BT_FWD(16, 1, 4)
+  BT_FWD(32, 1, 4)
+  BT_FWD(32, 2, 2)
+  BT_FWD(32, 4, 1)
+  BT_FWD(32, 8, 1)
+  BT_FWD(32, 16, 1)
+#undef BT_FWD
+  set_error("rmsnorm_fwd: no kernel for lpr=%d vpt=%d", c.lpr, c.vpt);
+  return BT_ERR_ARG;
+}
+
+template <typename T>
+int bwd_t(const void* dy, const void* x, const void* w, const float* rstd, void* dx, void* dw,
+          void* ws, int64_t M, int64_t N, int64_t ld_dy, int64_t ld_x, int64_t ld_dx,
+          cudaStream_t s) {
+  constexpr int E = Cvt<T>::N;
+  const T* gp = static_cast<const T*>(dy);
+  const T* xp = static_cast<const T*>(x);
+  const T* wp = static_cast<const T*>(w);
+  T* dxp = static_cast<T*>(dx);
+  T* dwp = static_cast<T*>(dw);
+  float* wsp = static_cast<float*>(ws);
+  const bool vec_ok = (N % E == 0) && (ld_x % E == 0) && (ld_dy % E == 0) && (ld_dx % E == 0) &&
+                      aligned16(x) && aligned16(w) && aligned16(dy) && aligned16(dx);
+  const int64_t nv = vec_ok ? N / E : 0;
+  RowCfg c{};
+  if (vec_ok && pick_rows(nv, 4, &c)) {
+    const int64_t rows_per_iter = static_cast<int64_t>(kThreads / c.lpr) * c.rpi;
+    const int grid = grid_for(ceil_div(M, rows_per_iter), 4);
+    const size_t smem = static_cast<size_t>(N) * sizeof(float);
+#define BT_BWD(L, V, R)                                                                        \
+  if (c.lpr == L && c.vpt == V) {                                                              \
+    rms_bwd_rows<T, V, L, R><<<grid, kThreads, smem, s>>>(gp, xp, wp, rstd, dxp, dwp, wsp, M,  \
+                                                          static_cast<int>(N), ld_dy, ld_x,    \
+                                                          ld_dx);                              \
+    BT_CHECK_LAUNCH("rms_bwd_rows");                                                           \
+    return BT_OK;                                                                              \
+  }
+    BT_BWD(8, 1, 4)
+    BT_BWD(16, 1, 4)
+    BT_BWD(32, 1, 4)
+    BT_BWD(32, 2, 2)
+    BT_BWD(32, 4, 1)
+#undef BT_BWD
+  }
+  if (vec_ok && nv <= static_cast<int64_t>(kThreads) * 4) {
+    const int vpt = nv <= kThreads ? 1 : (nv <= 2 * kThreads ? 2 : 4);
+#define BT_BWDB(V, R)                                                                          \
+  if (vpt == V) {                                                                              \
+    const int grid = grid_for(ceil_div(M, R), 2);                                              \
+    rms_bwd_block<T, V, R><<<grid, kThreads, 0, s>>>(gp, xp, wp, rstd, dxp, dwp, wsp, M,       \
+                                                     static_cast<int>(N), ld_dy, ld_x, ld_dx); \
+    BT_CHECK_LAUNCH("rms_bwd_block");                                                          \
+    return BT_OK;                                                                              \
+  }
+    BT_BWDB(1, 4)
+    BT_BWDB(2, 4)
+    BT_BWDB(4, 2)
+#undef BT_BWDB
+  }
+  rms_bwd_dx_generic<T><<<grid_for(M, 8), kThreads, 0, s>>>(gp, xp, wp, rstd, dxp, M, N, ld_dy,
+                                                            ld_x, ld_dx);
+  BT_CHECK_LAUNCH("rms_bwd_dx_generic");
+  dim3 g(static_cast<unsigned>(ceil_div(N, 32)),
+         static_cast<unsigned>(M < 8 * 64 ? 1 : (M / 8 < 64 ? M / 8 : 64)));
+  rms_bwd_dw_generic<T><<<g, dim3(32, 8), 0, s>>>(gp, xp, rstd, dwp, wsp, M, static_cast<int>(N),
+                                                  ld_dy, ld_x);
+  BT_CHECK_LAUNCH("rms_bwd_dw_generic");
+  return BT_OK;
+}
+
+}  // namespace
+}  // namespace bt
+
+extern "C" int bt_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int64_t M,
+                              int64_t N, int64_t ld_x, int64_t ld_y, float eps, int dtype,
+                              void* stream) {
+  using namespace bt;
+  BT_CHECK_ARG(M >= 0 && N > 0 && N < (1ll << 31), "rmsnorm_fwd: bad shape M=%lld N=%lld",
+               (long long)M, (long long)N);
+  BT_CHECK_ARG(ld_x >= N && ld_y >= N, "rmsnorm_fwd: row stride smaller than N");
+  if (M == 0) return BT_OK;
+  BT_CHECK_ARG(x && w && y && rstd, "rmsnorm_fwd: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case BT_BF16: return fwd_t<__nv_bfloat16>(x, w, y, rstd, M, N, ld_x, ld_y, eps, s);
+    case BT_FP16: return fwd_t<__half>(x, w, y, rstd, M, N, ld_x, ld_y, eps, s);
+    case BT_FP32: return fwd_t<float>(x, w, y, rstd, M, N, ld_x, ld_y, eps, s);
+  }
+  set_error("rmsnorm_fwd: unknown dtype %d", dtype);
+  return BT_ERR_ARG;
+}
+
+extern "C" int64_t bt_rmsnorm_bwd_ws_bytes(int64_t N) { return (N + 1) * 4; }
+
+extern "C" int bt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
+                              void* dx, void* dw, void* ws, int64_t M, int64_t N, int64_t ld_dy,
+                              int64_t ld_x, int64_t ld_dx, int dtype, void* stream) {
+  using namespace bt;
+  BT_CHECK_ARG(M >= 0 && N > 0 && N < (1ll << 31), "rmsnorm_bwd: bad shape M=%lld N=%lld",
+               (long long)M, (long long)N);
+  BT_CHECK_ARG(ld_x >= N && ld_dy >= N && ld_dx >= N, "rmsnorm_bwd: row stride smaller than N");
+  BT_CHECK_ARG(dw && ws, "rmsnorm_bwd: null dw / ws");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (M == 0) {
+    // No rows: dw = 0.  The scratch row is all zeros by contract, so reuse the
+    // finalize path of the generic dw kernel with an empty row range.
+    dim3 g(static_cast<unsigned>(ceil_div(N, 32)), 1);
+    switch (dtype) {
+      case BT_BF16:
+        rms_bwd_dw_generic<__nv_bfloat16><<<g, dim3(32, 8), 0, s>>>(
+            nullptr, nullptr, nullptr, static_cast<__nv_bfloat16*>(dw), static_cast<float*>(ws), 0,
+            static_cast<int>(N), 0, 0);
+        break;
+      case BT_FP16:
+        rms_bwd_dw_generic<__half><<<g, dim3(32, 8), 0, s>>>(nullptr, nullptr, nullptr,
+                                                            static_cast<__half*>(dw),
+                                                            static_cast<float*>(ws), 0,
+                                                            static_cast<int>(N), 0, 0);
+        break;
+      case BT_FP32:
+        rms_bwd_dw_generic<float><<<g, dim3(32, 8), 0, s>>>(nullptr, nullptr, nullptr,
+                                                           static_cast<float*>(dw),
+                                                           static_cast<float*>(ws), 0,
+                                                           static_cast<int>(N), 0, 0);
+        break;
+      default: set_error("rmsnorm_bwd: unknown dtype %d", dtype); return BT_ERR_ARG;
+    }
+    BT_CHECK_LAUNCH("rms_bwd_dw_generic(empty)");
+    return BT_OK;
+  }
+  BT_CHECK_ARG(dy && x && w && rstd && dx, "rmsnorm_bwd: null pointer");
+  switch (dtype) {
+    case BT_BF16:
+      return bwd_t<__nv_bfloat16>(dy, x, w, rstd, dx, dw, ws, M, N, ld_dy, ld_x, ld_dx, s);
+    case BT_FP16: return bwd_t<__half>(dy, x, w, rstd, dx, dw, ws, M, N, ld_dy, ld_x, ld_dx, s);
+    case BT_FP32: return bwd_t<float>(dy, x, w, rstd, dx, dw, ws, M, N, ld_dy, ld_x, ld_dx, s);
+  }
+  set_error("rmsnorm_bwd: unknown dtype %d", dtype);
+  return BT_ERR_ARG;
+}

@@ -1,0 +1,269 @@
+"""Fused lm_head + cross-entropy on sm_100a
+(replaces src/bastile/ops/fused_linear_cross_entropy.py).
+
+Per chunk of ``chunk_size`` rows the work is the reference's (``_chunked_fwd``,
+:136-187): logits GEMM, softmax statistics, ``dlogits``, the ``dx`` GEMM and the
+``dW`` GEMM, with the gradients produced during the forward and only scaled by
+the incoming ``dloss`` in the backward (:371-399).  What changes is where the
+arithmetic runs:
+
+* the logits GEMM is a tcgen05 kernel whose epilogue produces the per-row
+  (max, sum-exp) of each 256-column tile and picks up the target logit while the
+  accumulator is still in tensor memory, and writes the chunk of logits once;
+* one streaming pass turns that chunk into scaled ``dlogits`` in place (loss,
+  ``-1`` at the label, zeroed ignored rows, ``1/n_valid``) - the reference needs
+  two reads and a write plus torch indexing kernels with host syncs (:103-130);
+* ``n_valid`` is counted on the device, so nothing in the forward or backward
+  waits for the host (the reference calls ``.item()`` at :338 and :394);
+* the ``dW`` accumulation across chunks happens in the fp32 epilogue of the
+  GEMM, and the last chunk's GEMM in the backward applies ``dloss`` and writes
+  the weight dtype directly.
+
+With ``vocab_parallel_group`` every rank holds a slice ``[vocab_start,
+vocab_start + V_local)`` of the lm_head rows and sees all rows of ``hidden``;
+the only exchanges are one all-gather of the packed per-row statistics per
+chunk and one all-reduce of ``d hidden``; ``dW`` stays local.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+
+from .. import _lib
+
+_GEMM_DTYPES = (torch.bfloat16, torch.float16)
+
+
+def merge_shard_stats(gathered: Tensor) -> Tensor:
+    """[n_shards, rows, 3] (max, sum-exp, target logit) -> [rows, 3] for the full vocabulary."""
+    mx = gathered[..., 0]
+    gmax = mx.max(dim=0).values
+    gsum = (gathered[..., 1] * torch.exp(mx - gmax)).sum(dim=0)
+    tgt = gathered[..., 2].sum(dim=0)
+    return torch.stack((gmax, gsum, tgt), dim=-1).contiguous()
+
+
+class LinearCrossEntropyFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, target, ignore_index, reduction, chunk_size, v_chunk_size,
+                group=None, vocab_start=0):
+        dev = _lib.require_cuda(x, weight, target)
+        lib = _lib.get_lib()
+        if x.dtype not in _GEMM_DTYPES:
+            raise TypeError(
+                f"bastile_b200 fused_linear_cross_entropy: tensor-core kernels take bf16/fp16 hidden states, got {x.dtype}"
+            )
+        if reduction not in ("mean", "sum"):
+            raise ValueError(f"reduction must be 'mean' or 'sum', got {reduction!r}")
+        code = _lib.dtype_code(x.dtype)
+        batch_shape = x.shape[:-1]
+        hdim = x.shape[-1]
+        xf = x.reshape(-1, hdim)
+        if xf.stride(-1) != 1 or (xf.shape[0] > 1 and xf.stride(0) % 8 != 0):
+            xf = xf.contiguous()
+        bt = xf.shape[0]
+        w = weight.detach()
+        if w.dtype != x.dtype:
+            w = w.to(x.dtype)
+        w = w.contiguous()
+        vloc = w.shape[0]
+        if w.shape[1] != hdim:
+            raise ValueError("fused_linear_cross_entropy: weight must be [vocab, hidden]")
+        labels = target.reshape(-1)
+        if labels.dtype != torch.int64:
+            labels = labels.to(torch.int64)
+        labels = labels.contiguous()
+        if labels.numel() != bt:
+            raise ValueError("fused_linear_cross_entropy: target does not match hidden_states")
+
+        chunk = max(1, min(int(chunk_size), bt)) if bt > 0 else 1
+        n_chunks = (bt + chunk - 1) // chunk if bt > 0 else 0
+        ld_logits = (vloc + 7) // 8 * 8
+        n_vt = int(lib.bt_lce_num_vtiles(vloc))
+        stream = _lib.stream_ptr(dev)
+        st = _lib.status_word(dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+
+        scal = torch.empty(3, **f32)  # n_valid, grad_scale, loss
+        loss_row = torch.empty(max(bt, 1), **f32)
+        logits_buf = torch.empty((chunk, ld_logits), dtype=x.dtype, device=dev)
+        tile_stats = torch.empty((chunk, n_vt, 2), **f32)
+        tgt_logit = torch.empty(chunk, **f32)
+        row_stats = torch.empty((chunk, 3), **f32)
+        dx_dtype = torch.float32 if group is not None else x.dtype
+        dx = torch.empty((bt, hdim), dtype=dx_dtype, device=dev)
+        dw_acc = torch.empty((vloc, hdim), **f32) if n_chunks > 1 else None
+        world = 1
+        if group is not None:
+            import torch.distributed as dist
+
+            world = dist.get_world_size(group)
+            gathered = torch.empty((world, chunk, 3), **f32)
+
+        with _lib.device_of(dev):
+            _lib.check(lib.bt_lce_count_valid(labels.data_ptr(), bt, ignore_index, 1 if reduction == "mean" else 0,
+                                              scal[0:].data_ptr(), scal[1:].data_ptr(), stream), "bt_lce_count_valid")
+            last_rows = 0
+            x_last = None
+            for i in range(n_chunks):
+                s = i * chunk
+                rows = min(chunk, bt - s)
+                xc = xf[s:s + rows]
+                lc = labels[s:s + rows]
+                _lib.check(lib.bt_lce_logits_stats(xc.data_ptr(), w.data_ptr(), lc.data_ptr(), logits_buf.data_ptr(),
+                                                   tile_stats.data_ptr(), tgt_logit.data_ptr(), rows, hdim, vloc,
+                                                   xf.stride(0) if bt > 1 else hdim, ld_logits, int(vocab_start),
+                                                   ignore_index, code, st.data_ptr(), stream),
+                           "bt_lce_logits_stats")
+                _lib.check(lib.bt_lce_row_stats(tile_stats.data_ptr(), tgt_logit.data_ptr(), row_stats.data_ptr(),
+                                                rows, n_vt, stream), "bt_lce_row_stats")
+                stats = row_stats
+                if group is not None:
+                    import torch.distributed as dist
+
+                    dist.all_gather_into_tensor(gathered.view(-1), row_stats.view(-1), group=group)
+                    stats = merge_shard_stats(gathered[:, :rows])
+                _lib.check(lib.bt_lce_dlogits(logits_buf.data_ptr(), stats.data_ptr(), lc.data_ptr(),
+                                              loss_row[s:].data_ptr(), scal[1:].data_ptr(), rows, vloc, ld_logits,
+                                              int(vocab_start), ignore_index, 1, code, stream), "bt_lce_dlogits")
+                # dx_chunk = dlogits[rows, V] @ W[V, H]
+                _lib.check(lib.bt_gemm(logits_buf.data_ptr(), w.data_ptr(), dx[s:].data_ptr(), rows, hdim, vloc,
+                                       ld_logits, hdim, hdim, 1, 0, code, _lib.dtype_code(dx_dtype), None, 0, None,
+                                       st.data_ptr(), stream), "bt_gemm(dx)")
+                if i < n_chunks - 1:
+                    # dW += dlogits^T[V, rows] @ x_chunk[rows, H], fp32 accumulation across chunks
+                    _lib.check(lib.bt_gemm(logits_buf.data_ptr(), xc.data_ptr(), dw_acc.data_ptr(), vloc, hdim, rows,
+                                           ld_logits, xf.stride(0) if bt > 1 else hdim, hdim, 0, 0, code,
+                                           _lib.BT_FP32, dw_acc.data_ptr() if i > 0 else None, hdim, None,
+                                           st.data_ptr(), stream), "bt_gemm(dW)")
+                else:
+                    last_rows, x_last = rows, xc
+            _lib.check(lib.bt_lce_reduce_loss(loss_row.data_ptr(), bt, scal[1:].data_ptr() if reduction == "mean"
+                                              else None, scal[2:].data_ptr(), stream), "bt_lce_reduce_loss")
+        if group is not None and bt > 0:
+            import torch.distributed as dist
+
+            dist.all_reduce(dx, group=group)
+
+        ctx.save_for_backward(dx, w, logits_buf, x_last if x_last is not None else xf[:0],
+                              dw_acc if dw_acc is not None else scal[:0])
+        ctx.meta = (batch_shape, hdim, vloc, last_rows, ld_logits, x.dtype, weight.dtype, n_chunks,
+                    xf.stride(0) if bt > 1 else hdim)
+        return scal[2].clone()
+
+    @staticmethod
+    def backward(ctx, dloss):
+        dx, w, dlogits_last, x_last, dw_acc = ctx.saved_tensors
+        batch_shape, hdim, vloc, last_rows, ld_logits, x_dtype, w_dtype, n_chunks, ld_x = ctx.meta
+        dev = dx.device
+        lib = _lib.get_lib()
+        stream = _lib.stream_ptr(dev)
+        st = _lib.status_word(dev)
+        code = _lib.dtype_code(x_dtype)
+        scale = dloss.detach().to(torch.float32).reshape(1).contiguous()
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        dx_out = dw_out = None
+        with _lib.device_of(dev):
+            if need_x:
+                dx_out = torch.empty(dx.shape, dtype=x_dtype, device=dev)
+                _lib.check(lib.bt_scale_cast(dx.data_ptr(), dx_out.data_ptr(), dx.numel(), scale.data_ptr(),
+                                             _lib.dtype_code(dx.dtype), code, stream), "bt_scale_cast(dx)")
+                dx_out = dx_out.view(*batch_shape, hdim)
+            if need_w:
+                out_dtype = w_dtype if w_dtype in _lib._DTYPES else x_dtype
+                dw_out = torch.empty((vloc, hdim), dtype=out_dtype, device=dev)
+                if n_chunks == 0:
+                    dw_out.zero_()
+                else:
+                    _lib.check(lib.bt_gemm(dlogits_last.data_ptr(), x_last.data_ptr(), dw_out.data_ptr(), vloc, hdim,
+                                           last_rows, ld_logits, ld_x, hdim, 0, 0, code, _lib.dtype_code(out_dtype),
+                                           dw_acc.data_ptr() if n_chunks > 1 else None, hdim, scale.data_ptr(),
+                                           st.data_ptr(), stream), "bt_gemm(dW last)")
+                if dw_out.dtype != w_dtype:
+                    dw_out = dw_out.to(w_dtype)
+        return dx_out, dw_out, None, None, None, None, None, None, None
+
+
+ChunkedLinearCrossEntropyFunction = LinearCrossEntropyFunction
+
+
+def fused_linear_cross_entropy(hidden_states: Tensor, weight: Tensor, target: Tensor, bias=None,
+                               ignore_index: int = -100, chunk_size: int = 4096, reduction: str = "mean",
+                               v_chunk_size: int | None = None, vocab_parallel_group=None,
+                               vocab_start: int = 0) -> Tensor:
+    """Loss of ``cross_entropy(hidden_states @ weight.T, target)`` without ever holding
+    ``[tokens, vocab]`` logits; same arguments as the reference (:405-438).
+
+    ``v_chunk_size`` is accepted for compatibility: the kernels already tile the
+    vocabulary, so it selects nothing.  ``vocab_parallel_group`` / ``vocab_start``
+    are additions for the vocabulary-sharded form (``weight`` is then the local
+    slice of rows starting at ``vocab_start``; ``target`` holds global ids).
+    """
+    if hidden_states.ndim == 3:
+        hidden_states = hidden_states.reshape(-1, hidden_states.shape[-1])
+        target = target.reshape(-1)
+    if bias is not None:
+        if vocab_parallel_group is not None:
+            raise ValueError("fused_linear_cross_entropy: bias is not supported with a vocabulary-parallel group")
+        logits = F.linear(hidden_states, weight, bias)
+        return F.cross_entropy(logits, target, ignore_index=ignore_index, reduction=reduction)
+    return LinearCrossEntropyFunction.apply(hidden_states, weight, target, ignore_index, reduction, chunk_size,
+                                            v_chunk_size, vocab_parallel_group, vocab_start)
+
+
+def bastile_lce_forward(self, input_ids=None, attention_mask=None, position_ids=None, past_key_values=None,
+                        inputs_embeds=None, labels=None, use_cache=None, output_attentions=None,
+                        output_hidden_states=None, cache_position=None, logits_to_keep=0, return_dict=None,
+                        **kwargs):
+    """Replacement for ``Qwen3ForCausalLM.forward`` (:444-511): in training with labels the
+    shifted hidden states go straight into the fused loss and ``logits`` is ``None``;
+    otherwise the stock ``lm_head`` + ``loss_function`` path runs."""
+    from transformers.modeling_outputs import CausalLMOutputWithPast
+
+    cfg = self.config
+    if output_attentions is None:
+        output_attentions = cfg.output_attentions
+    if output_hidden_states is None:
+        output_hidden_states = cfg.output_hidden_states
+    if return_dict is None:
+        return_dict = getattr(cfg, "return_dict", True)
+
+    outputs = self.model(
+        input_ids=input_ids, attention_mask=attention_mask, position_ids=position_ids,
+        past_key_values=past_key_values, inputs_embeds=inputs_embeds, use_cache=use_cache,
+        output_attentions=output_attentions, output_hidden_states=output_hidden_states,
+        cache_position=cache_position, **kwargs,
+    )
+    hidden_states = outputs[0]
+    logits = loss = None
+    if self.training and labels is not None:
+        # Drop the last position / first label; the fused loss takes row strides,
+        # so the shifted hidden states are only copied when batch > 1 makes the
+        # flattened view non-uniform.
+        shift_hidden = hidden_states[..., :-1, :]
+        shift_labels = labels[..., 1:]
+        loss = fused_linear_cross_entropy(shift_hidden, self.lm_head.weight, shift_labels,
+                                          bias=getattr(self.lm_head, "bias", None), ignore_index=-100)
+    else:
+        keep = slice(-logits_to_keep, None) if isinstance(logits_to_keep, int) else logits_to_keep
+        logits = self.lm_head(hidden_states[:, keep, :])
+        if labels is not None:
+            loss = self.loss_function(logits=logits, labels=labels, vocab_size=cfg.vocab_size, **kwargs)
+
+    if not return_dict:
+        out = (logits,) + tuple(outputs[1:])
+        return ((loss,) + out) if loss is not None else out
+    return CausalLMOutputWithPast(loss=loss, logits=logits, past_key_values=outputs.past_key_values,
+                                  hidden_states=outputs.hidden_states, attentions=outputs.attentions)
+
+
+def warmup_fused_lce(hidden_size: int = 4096, vocab_size: int = 151936, dtype: torch.dtype = torch.bfloat16,
+                     device: str = "cuda"):
+    """One tiny forward+backward at the model's (hidden, vocab) (:517-529)."""
+    x = torch.randn(8, hidden_size, dtype=dtype, device=device, requires_grad=True)
+    w = torch.randn(vocab_size, hidden_size, dtype=dtype, device=device, requires_grad=True)
+    t = torch.randint(0, vocab_size, (8,), device=device)
+    fused_linear_cross_entropy(x, w, t).backward()
+    torch.cuda.synchronize()

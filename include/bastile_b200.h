@@ -1,0 +1,205 @@
+/*
+ * bastile_b200 — C ABI of the sm_100a kernels behind the four Qwen3 training
+ * ops that aghilann/bastile patches into HuggingFace transformers.
+ *
+ * Conventions shared by every entry point
+ *   - plain device pointers, element counts and element strides; no torch types;
+ *   - `dtype`: BT_BF16 / BT_FP16 / BT_FP32 storage, all arithmetic in fp32;
+ *   - `stream`: a cudaStream_t passed as void* (NULL = legacy default stream);
+ *   - return value: 0 on success, a negative BT_ERR_* code otherwise; the text of
+ *     the last failure on the calling thread is available from bt_last_error();
+ *   - nothing here allocates or frees device memory, synchronises the device or
+ *     throws: the caller owns every buffer for the duration of the call only.
+ *   - there is no CPU implementation behind this interface.
+ *
+ * Each declaration cites the function of the reference (path within the
+ * aghilann/bastile source tree : lines) whose device work it replaces.
+ */
+#ifndef BASTILE_B200_H_
+#define BASTILE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BT_BF16 0
+#define BT_FP16 1
+#define BT_FP32 2
+
+#define BT_OK 0
+#define BT_ERR_ARG (-1)      /* bad shape, stride, alignment or dtype            */
+#define BT_ERR_LAUNCH (-2)   /* CUDA runtime error at launch (cudaGetLastError)  */
+#define BT_ERR_DEVICE (-3)   /* a bounded device-side wait ran out (status word) */
+#define BT_ERR_DRIVER (-4)   /* tensor-map encode / driver entry point failure   */
+#define BT_ERR_LIMIT (-5)    /* size beyond a stated maximum                     */
+
+/* Library version (major*10000 + minor*100 + patch). No reference counterpart
+ * (the reference is a JIT Python package: src/bastile/__init__.py:23). */
+int bt_version(void);
+
+/* Text of the last error raised on this thread ("" if none). */
+const char* bt_last_error(void);
+
+/* Number of SMs of the current device (src/bastile/ops/utils.py:8-13). */
+int bt_sm_count(void);
+
+/* ------------------------------------------------------------------ RMSNorm */
+
+/* y[m,:] = x[m,:] * rsqrt(mean(x[m,:]^2) + eps) * w, rounded once to `dtype`;
+ * rstd[m] (fp32) is saved for the backward.  x rows are ld_x elements apart,
+ * y rows ld_y.  Replaces _rms_fwd + CuTileRMSNormFunction.forward
+ * (src/bastile/ops/rms_norm.py:15-34, 105-126). */
+int bt_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd,
+                   int64_t M, int64_t N, int64_t ld_x, int64_t ld_y,
+                   float eps, int dtype, void* stream);
+
+/* dx = (dy*w - xhat*mean(xhat*dy*w)) * rstd, dw = sum_rows dy*xhat with
+ * xhat = x*rstd.  `ws` is caller-owned scratch of bt_rmsnorm_bwd_ws_bytes(N)
+ * bytes that must be ZERO on entry; the kernel leaves it zero again on exit, so
+ * one zero-initialised buffer can be reused by successive calls on one stream.
+ * Replaces _rms_bwd, the torch partial-sum reduction and the dtype cast
+ * (src/bastile/ops/rms_norm.py:37-68, 128-153). */
+int bt_rmsnorm_bwd(const void* dy, const void* x, const void* w,
+                   const float* rstd, void* dx, void* dw, void* ws,
+                   int64_t M, int64_t N, int64_t ld_dy, int64_t ld_x,
+                   int64_t ld_dx, int dtype, void* stream);
+int64_t bt_rmsnorm_bwd_ws_bytes(int64_t N);
+
+/* --------------------------------------------------------------------- RoPE */
+
+/* Rotate-half rotary embedding of q [B,Hq,T,D] and k [B,Hk,T,D]:
+ *   out1 = in1*cos - in2*sin ; out2 = in2*cos + in1*sin   (halves of D)
+ * using the FIRST D/2 columns of cos/sin rows [cos_bs in {1,B}, T, >=D/2].
+ * Strides are in elements; the last dimension must be contiguous.  q_out may
+ * equal q_in (in place, the forward) or be a separate buffer (the backward,
+ * called with negate_sin = 1 on the incoming gradients).  Replaces
+ * _rope_kernel / _reshape_and_launch / RoPEFunction
+ * (src/bastile/ops/rope.py:13-90, 93-122, 125-136). */
+int bt_rope(const void* q_in, const void* k_in, void* q_out, void* k_out,
+            const void* cos, const void* sin,
+            int64_t B, int64_t Hq, int64_t Hk, int64_t T, int64_t D,
+            const int64_t q_in_strides[3],  /* b, h, t */
+            const int64_t k_in_strides[3],
+            const int64_t q_out_strides[3],
+            const int64_t k_out_strides[3],
+            const int64_t cos_strides[2],   /* b, t (shared by cos and sin) */
+            int64_t cos_bs, int negate_sin, int dtype, void* stream);
+
+/* ------------------------------------------------------ SwiGLU (elementwise) */
+
+/* out = T(silu_fp32(gate)) * up, the product rounded to `dtype`
+ * (swiglu_forward_kernel, src/bastile/ops/swiglu.py:23-50, 93-117). */
+int bt_swiglu_fwd(const void* gate, const void* up, void* out,
+                  int64_t rows, int64_t cols, int64_t ld_gate, int64_t ld_up,
+                  int64_t ld_out, int dtype, void* stream);
+
+/* dgate = dy*up*sig(g)*(1+g*(1-sig(g))), dup = dy*g*sig(g), fp32 math
+ * (swiglu_backward_kernel, src/bastile/ops/swiglu.py:53-90, 120-146). */
+int bt_swiglu_bwd(const void* dy, const void* gate, const void* up,
+                  void* dgate, void* dup, int64_t rows, int64_t cols,
+                  int64_t ld_dy, int64_t ld_gate, int64_t ld_up,
+                  int64_t ld_dgate, int64_t ld_dup, int dtype, void* stream);
+
+/* ------------------------------------------------------- tcgen05 GEMM core  */
+
+/* D[M,N] = op(A) * op(B) with fp32 accumulation in tensor memory, 16-bit
+ * operands (BT_BF16 or BT_FP16) and a 16-bit or fp32 result.
+ *   a_kmajor = 1: A is stored [M,K] with K contiguous (row stride lda)
+ *   a_kmajor = 0: A is stored [K,M] with M contiguous (row stride lda)
+ *   b_kmajor = 1: B is stored [N,K] with K contiguous (row stride ldb)
+ *   b_kmajor = 0: B is stored [K,N] with N contiguous (row stride ldb)
+ * out_dtype selects the storage of D (row stride ldd); accumulate != 0 adds the
+ * product to the existing fp32 D (requires out_dtype = BT_FP32).
+ * `status` points at a caller-owned, zero-initialised int32 device word that a
+ * kernel sets non-zero if one of its bounded barrier waits runs out.
+ * This is the library GEMM that the reference takes from cuBLAS through
+ * torch.mm / nn.Linear (src/bastile/ops/swiglu.py:179-187,
+ * src/bastile/ops/fused_linear_cross_entropy.py:167-185, 385). */
+int bt_gemm(const void* A, const void* B, void* D,
+            int64_t M, int64_t N, int64_t K,
+            int64_t lda, int64_t ldb, int64_t ldd,
+            int a_kmajor, int b_kmajor, int in_dtype, int out_dtype,
+            int accumulate, int32_t* status, void* stream);
+
+/* ------------------------------------------------------ SwiGLU MLP (fused)  */
+
+/* Forward of CuTileSwiGLUMLP (src/bastile/ops/swiglu.py:170-187):
+ *   gate = x Wg^T, up = x Wu^T  (one tensor-core kernel, two accumulators),
+ *   h = T(silu(gate)) * up fused in that kernel's epilogue,  y = h Wd^T.
+ * x [T,H] (row stride ld_x), Wg/Wu [I,H], Wd [H,I] contiguous; gate, up, h
+ * [T,I] and y [T,H] contiguous outputs (gate/up/h are what the backward needs). */
+int bt_mlp_fwd(const void* x, const void* wg, const void* wu, const void* wd,
+               void* gate, void* up, void* h, void* y,
+               int64_t T, int64_t H, int64_t I, int64_t ld_x,
+               int dtype, int32_t* status, void* stream);
+
+/* Backward of the same block (autograd of src/bastile/ops/swiglu.py:186-187
+ * plus swiglu_backward_kernel :53-90):
+ *   dh = dy Wd (epilogue turns it into dgate, dup using saved gate/up),
+ *   dWd = dy^T h, dWg = dgate^T x, dWu = dup^T x, dx = dgate Wg + dup Wu.
+ * dgate/dup [T,I] are caller-owned scratch.  Any of dx, dwg, dwu, dwd may be
+ * NULL to skip that product. */
+int bt_mlp_bwd(const void* dy, const void* x, const void* wg, const void* wu,
+               const void* wd, const void* gate, const void* up, const void* h,
+               void* dgate, void* dup, void* dx, void* dwg, void* dwu, void* dwd,
+               int64_t T, int64_t H, int64_t I, int64_t ld_x, int64_t ld_dy,
+               int dtype, int32_t* status, void* stream);
+
+/* ------------------------------------------- fused lm_head + cross-entropy  */
+
+/* Step 1 of the fused loss for one chunk of rows and one vocabulary shard:
+ * logits = hidden W^T on the tensor cores; the epilogue keeps, per row and per
+ * 256-column tile, (max, sum exp(logit-max)) and the target's logit, and writes
+ * the logits once as 16-bit values into `logits` [rows, ld_logits] (the chunk
+ * buffer, never [tokens, V]).  `tile_stats` has rows * bt_lce_num_vtiles(V)
+ * float2 entries, `tgt_logit` one float per row (0 when the label is ignored or
+ * outside [v_offset, v_offset+V)).  Replaces GEMM1 + pass 1 of
+ * _ce_online_kernel + the target gather
+ * (src/bastile/ops/fused_linear_cross_entropy.py:167, 46-100, 108-114). */
+int bt_lce_logits_stats(const void* hidden, const void* W, const int64_t* labels,
+                        void* logits, float* tile_stats, float* tgt_logit,
+                        int64_t rows, int64_t H, int64_t V, int64_t ld_hidden,
+                        int64_t ld_logits, int64_t v_offset, int64_t ignore_index,
+                        int dtype, int32_t* status, void* stream);
+int64_t bt_lce_num_vtiles(int64_t V);
+
+/* Step 2: merge the per-tile statistics of each row into row_stats[rows,3] =
+ * (max, sum exp, target logit) for this vocabulary shard
+ * (the per-row reduction of _ce_online_kernel, :62-85). */
+int bt_lce_row_stats(const float* tile_stats, const float* tgt_logit,
+                     float* row_stats, int64_t rows, int64_t n_vtiles, void* stream);
+
+/* Step 3: given (possibly cross-shard merged) row statistics, write
+ * loss_row = max + log(sum) - target (0 for ignored rows) and turn the logits
+ * chunk in place into scaled gradients
+ *   dlogits = (exp(logit - max)/sum - [col == label]) * grad_scale[0]
+ * with ignored rows zeroed.  grad_scale is a DEVICE float (1/n_valid for mean,
+ * 1 for sum).  write_loss = 0 skips the loss write.  Replaces pass 2 of
+ * _ce_online_kernel and the torch fix-ups (:87-100, 126-130). */
+int bt_lce_dlogits(void* logits, const float* row_stats, const int64_t* labels,
+                   float* loss_row, const float* grad_scale,
+                   int64_t rows, int64_t V, int64_t ld_logits, int64_t v_offset,
+                   int64_t ignore_index, int write_loss, int dtype, void* stream);
+
+/* Counts labels != ignore_index into n_valid[0] (fp32) and writes
+ * grad_scale[0] = mean ? (n_valid > 0 ? 1/n_valid : 0) : 1 without a host
+ * round trip (replaces the .item() sync of
+ * src/bastile/ops/fused_linear_cross_entropy.py:334-343). */
+int bt_lce_count_valid(const int64_t* labels, int64_t n, int64_t ignore_index,
+                       int mean, float* n_valid, float* grad_scale, void* stream);
+
+/* loss[0] = sum(loss_row[0:n]) * (mean ? grad_scale[0] : 1)  (:333, 367). */
+int bt_lce_reduce_loss(const float* loss_row, int64_t n, const float* grad_scale,
+                       float* loss, void* stream);
+
+/* out[i] = T(scale[0] * (float)in[i]) for i < n, `scale` a DEVICE float: the
+ * dloss scaling of the saved gradients in the backward (:371-399). */
+int bt_scale_cast(const void* in, void* out, int64_t n, const float* scale,
+                  int in_dtype, int out_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BASTILE_B200_H_ */

@@ -1,0 +1,627 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a with pluggable epilogues.
+//
+//   CTA tile 128 x 256 x 64 (16-bit operands), one CTA per SM, 192 threads:
+//     warp 0      TMA producer   - one lane issues the tile loads of a 4-stage ring
+//     warp 1      MMA issuer     - owns the 512 TMEM columns, one lane issues tcgen05.mma
+//     warps 2..5  epilogue       - each owns one 32-lane quarter of TMEM
+//   The fp32 accumulator (128 lanes x 256 columns) is double-buffered in tensor
+//   memory, so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+//   Operands may be K-major (rows = M/N index, K contiguous) or MN-major (rows = K
+//   index, M/N contiguous); both land in shared memory as 128-byte rows with the
+//   128-byte TMA swizzle, which is what the UMMA shared-memory descriptors expect.
+//   Ragged M / N / K need no special casing in the main loop: TMA zero-fills reads
+//   outside the tensor, and the epilogues bound-check their global accesses.
+//
+//   Optional main-loop modes
+//     dual_b    : the B tile is 128 rows of B0 followed by 128 rows of B1 (same A),
+//                 i.e. accumulator columns [0,128) = A*B0^T, [128,256) = A*B1^T;
+//     two pairs : the K loop runs over (A0,B0) and then (A1,B1) into one accumulator.
+//
+//   Every mbarrier wait is bounded (sm100_ptx.cuh); a wait that runs out sets the
+//   caller's status word, makes all roles leave their loops, and the CTA still
+//   frees its tensor memory before exiting.
+#pragma once
+
+#include <mutex>
+
+#include "bt_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace bt {
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr int kABytes = BM * BK * 2;
+constexpr int kBBytes = BN * BK * 2;
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kTmemCols = 512;
+constexpr int kGroupM = 16;  // tile rasterisation: walk 16 row-tiles per column-tile
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kBoxBytesMN = BK * 128;  // one MN-major box: 64 K rows x 128 bytes
+
+enum : int { EPI_PLAIN = 0, EPI_SWIGLU_FWD = 1, EPI_SWIGLU_BWD = 2, EPI_LCE = 3 };
+
+// Status-word bits set when a bounded wait runs out.
+enum : int { ST_PRODUCER = 1, ST_MMA_ACC = 2, ST_MMA_FULL = 4, ST_EPILOGUE = 8 };
+
+struct Params {
+  int M, N;        // output extent; with dual_b, N is the width of ONE of the two outputs
+  int K0, K1;      // contraction lengths of pair 0 and pair 1 (K1 = 0: single pair)
+  int tiles_m, tiles_n, num_tiles;
+  int a_kmajor, b_kmajor, dual_b;
+  uint32_t idesc;
+  uint64_t a_desc_hi, b_desc_hi;
+  uint32_t a_kstep, b_kstep;  // descriptor address step per 16-element K slice, 16-byte units
+  int32_t* status;
+  // --- plain epilogue: out = T(alpha * (acc + addend))
+  void* out;
+  int64_t ldo;
+  int out_fp32;
+  int vec_ok;  // rows of every global tensor the epilogue touches are 16-byte aligned
+  const float* addend;
+  int64_t ld_add;
+  const float* alpha;
+  // --- SwiGLU epilogues (row stride ld_act)
+  void* gate;  // fwd: out, bwd: in
+  void* up;    // fwd: out, bwd: in
+  void* h;     // fwd: out (h), bwd: out (dup); bwd writes dgate to `out`
+  int64_t ld_act;
+  // --- fused cross-entropy epilogue
+  const int64_t* labels;
+  float* tile_stats;
+  float* tgt_logit;
+  int64_t v_offset, ignore_index;
+  int n_vtiles;
+};
+
+__device__ __forceinline__ void tile_coords(const Params& p, int tile, int* m_idx, int* n_idx) {
+  const int per_group = kGroupM * p.tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * kGroupM;
+  const int gs = min(p.tiles_m - first_m, kGroupM);
+  const int r = tile - g * per_group;
+  *m_idx = first_m + r % gs;
+  *n_idx = r / gs;
+}
+
+template <typename T>
+__device__ __forceinline__ float round_through(float x) {
+  return Cvt<T>::to_f(Cvt<T>::from_f(x));
+}
+
+// Store 32 consecutive values of one row (vector path when the span is whole and aligned).
+template <typename T>
+__device__ __forceinline__ void store_row32(T* dst, const float (&v)[32], int valid, bool vec) {
+  if (vec && valid >= 32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float f[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = v[i * 8 + e];
+      st_global_v4(dst + i * 8, Cvt<T>::pack(f));
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) dst[j] = Cvt<T>::from_f(v[j]);
+  }
+}
+__device__ __forceinline__ void store_row32_f32(float* dst, const float (&v)[32], int valid,
+                                                bool vec) {
+  if (vec && valid >= 32) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      *reinterpret_cast<float4*>(dst + i * 4) =
+          make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) dst[j] = v[j];
+  }
+}
+template <typename T>
+__device__ __forceinline__ void load_row32(const T* src, float (&v)[32], int valid, bool vec) {
+  if (vec && valid >= 32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float f[8];
+      Cvt<T>::unpack(ld_global_v4(src + i * 8), f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[i * 8 + e] = f[e];
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = (j < valid) ? Cvt<T>::to_f(src[j]) : 0.f;
+  }
+}
+
+// ------------------------------------------------------------------ epilogues
+template <typename T>
+__device__ __forceinline__ void epi_plain(const Params& p, uint32_t taddr, int64_t row, int n0) {
+  const float alpha = p.alpha != nullptr ? __ldg(p.alpha) : 1.0f;
+  const bool row_ok = row < p.M;
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    float v[32];
+    ptx::tmem_ld_32cols(taddr + c * 32, v);
+    const int col0 = n0 + c * 32;
+    const int valid = p.N - col0;
+    if (row_ok && valid > 0) {
+      if (p.addend != nullptr) {
+        const float* a = p.addend + row * p.ld_add + col0;
+        if (p.vec_ok && valid >= 32) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 t = *reinterpret_cast<const float4*>(a + i * 4);
+            v[i * 4] += t.x;
+            v[i * 4 + 1] += t.y;
+            v[i * 4 + 2] += t.z;
+            v[i * 4 + 3] += t.w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < valid) v[j] += a[j];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] *= alpha;
+      if (p.out_fp32)
+        store_row32_f32(static_cast<float*>(p.out) + row * p.ldo + col0, v, valid, p.vec_ok);
+      else
+        store_row32<T>(static_cast<T*>(p.out) + row * p.ldo + col0, v, valid, p.vec_ok);
+    }
+  }
+}
+
+// Accumulator columns [0,128) = gate, [128,256) = up for output columns n0 .. n0+127.
+template <typename T>
+__device__ __forceinline__ void epi_swiglu_fwd(const Params& p, uint32_t taddr, int64_t row,
+                                               int n0) {
+  const bool row_ok = row < p.M;
+#pragma unroll 1
+  for (int c = 0; c < (BN / 2) / 32; ++c) {
+    float g[32], u[32];
+    ptx::tmem_ld_32cols(taddr + c * 32, g);
+    ptx::tmem_ld_32cols(taddr + BN / 2 + c * 32, u);
+    const int col0 = n0 + c * 32;
+    const int valid = p.N - col0;
+    if (row_ok && valid > 0) {
+      float hh[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        g[j] = round_through<T>(g[j]);
+        u[j] = round_through<T>(u[j]);
+        const float silu = round_through<T>(g[j] * __fdividef(1.0f, 1.0f + __expf(-g[j])));
+        hh[j] = silu * u[j];
+      }
+      const int64_t off = row * p.ld_act + col0;
+      store_row32<T>(static_cast<T*>(p.gate) + off, g, valid, p.vec_ok);
+      store_row32<T>(static_cast<T*>(p.up) + off, u, valid, p.vec_ok);
+      store_row32<T>(static_cast<T*>(p.h) + off, hh, valid, p.vec_ok);
+    }
+  }
+}
+
+// Accumulator = dh tile; reads saved gate/up, writes dgate (p.out) and dup (p.h).
+template <typename T>
+__device__ __forceinline__ void epi_swiglu_bwd(const Params& p, uint32_t taddr, int64_t row,
+                                               int n0) {
+  const bool row_ok = row < p.M;
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    float d[32];
+    ptx::tmem_ld_32cols(taddr + c * 32, d);
+    const int col0 = n0 + c * 32;
+    const int valid = p.N - col0;
+    if (row_ok && valid > 0) {
+      const int64_t off = row * p.ld_act + col0;
+      float g[32], u[32];
+      load_row32<T>(static_cast<const T*>(p.gate) + off, g, valid, p.vec_ok);
+      load_row32<T>(static_cast<const T*>(p.up) + off, u, valid, p.vec_ok);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float dh = round_through<T>(d[j]);
+        const float sg = 1.0f / (1.0f + expf(-g[j]));
+        d[j] = dh * (sg * (1.0f + g[j] * (1.0f - sg))) * u[j];  // dgate
+        g[j] = dh * (g[j] * sg);                                 // dup
+      }
+      store_row32<T>(static_cast<T*>(p.out) + off, d, valid, p.vec_ok);
+      store_row32<T>(static_cast<T*>(p.h) + off, g, valid, p.vec_ok);
+    }
+  }
+}
+
+// Accumulator = logits tile: per-row (max, sum exp) of the tile, the target logit, and
+// the logits themselves rounded to T.
+template <typename T>
+__device__ __forceinline__ void epi_lce(const Params& p, uint32_t taddr, int64_t row, int n0,
+                                        int n_idx) {
+  const bool row_ok = row < p.M;
+  constexpr float kNegBig = -1e30f;
+  int tgt_col = -1;  // column of the label inside this tile, if it is here
+  bool owned = false;
+  if (row_ok) {
+    const int64_t label = p.labels[row];
+    const int64_t loc = label - p.v_offset;
+    owned = (label != p.ignore_index) && loc >= 0 && loc < p.N;
+    if (owned && loc >= n0 && loc < n0 + BN) tgt_col = static_cast<int>(loc - n0);
+  }
+  float mx = kNegBig, sum = 0.f, tgt = 0.f;
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    float v[32];
+    ptx::tmem_ld_32cols(taddr + c * 32, v);
+    const int col0 = n0 + c * 32;
+    const int valid = p.N - col0;
+    if (valid > 0) {
+      float cmax = kNegBig;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        v[j] = (j < valid) ? round_through<T>(v[j]) : kNegBig;
+        cmax = fmaxf(cmax, v[j]);
+      }
+      const float newm = fmaxf(mx, cmax);
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) s += __expf(v[j] - newm);
+      sum = sum * __expf(mx - newm) + s;
+      mx = newm;
+      if (tgt_col >= c * 32 && tgt_col < c * 32 + 32) {
+        const int jj = tgt_col - c * 32;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j == jj) tgt = v[j];
+      }
+      if (row_ok)
+        store_row32<T>(static_cast<T*>(p.out) + row * p.ldo + col0, v, valid, p.vec_ok);
+    }
+  }
+  if (row_ok) {
+    *reinterpret_cast<float2*>(p.tile_stats + (row * p.n_vtiles + n_idx) * 2) =
+        make_float2(mx, sum);
+    if (tgt_col >= 0)
+      p.tgt_logit[row] = tgt;
+    else if (n_idx == 0 && !owned)
+      p.tgt_logit[row] = 0.f;
+  }
+}
+
+// --------------------------------------------------------------------- kernel
+template <int EPI, typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
+            const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
+            const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* empty = full + kStages;
+  uint64_t* tfull = empty + kStages;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      ptx::mbar_init(&full[i], 1);
+      ptx::mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&tfull[i], 1);
+      ptx::mbar_init(&tempty[i], 128);
+    }
+    *cta_abort = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tmA0);
+    ptx::prefetch_tensormap(&tmB0);
+    if (p.K1 > 0 || p.dual_b) ptx::prefetch_tensormap(&tmB1);
+    if (p.K1 > 0) ptx::prefetch_tensormap(&tmA1);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish_alloc_permit();
+  }
+  ptx::tcgen05_fence_before_sync();
+  __syncthreads();
+  ptx::tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int nkb0 = (p.K0 + BK - 1) / BK;
+  const int nkb1 = (p.K1 + BK - 1) / BK;
+  const int nkb = nkb0 + nkb1;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        int m_idx, n_idx;
+        tile_coords(p, tile, &m_idx, &n_idx);
+        const int m0 = m_idx * BM;
+        const int n0 = n_idx * (p.dual_b ? BN / 2 : BN);
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!ptx::mbar_wait(&empty[stage], phase ^ 1u, cta_abort, p.status, ST_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          ptx::mbar_arrive_expect_tx(&full[stage], kStageBytes);
+          const bool second = kb >= nkb0;
+          const int k0 = (second ? kb - nkb0 : kb) * BK;
+          const CUtensorMap* ta = second ? &tmA1 : &tmA0;
+          const CUtensorMap* tb = second ? &tmB1 : &tmB0;
+          uint8_t* sa = smem + stage * kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          if (p.a_kmajor) {
+            ptx::tma_load_2d(sa, ta, k0, m0, &full[stage]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              ptx::tma_load_2d(sa + j * kBoxBytesMN, ta, m0 + j * 64, k0, &full[stage]);
+          }
+          if (p.dual_b) {
+            ptx::tma_load_2d(sb, &tmB0, k0, n0, &full[stage]);
+            ptx::tma_load_2d(sb + kBBytes / 2, &tmB1, k0, n0, &full[stage]);
+          } else if (p.b_kmajor) {
+            ptx::tma_load_2d(sb, tb, k0, n0, &full[stage]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              ptx::tma_load_2d(sb + j * kBoxBytesMN, tb, n0 + j * 64, k0, &full[stage]);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok || *cta_abort != 0) {
+        // Something gave up: give the copies that are still in flight time to land
+        // before this CTA's shared memory can be handed to another CTA.
+        const uint64_t t0 = ptx::globaltimer_ns();
+        while (ptx::globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        if (!ptx::mbar_wait(&tempty[acc], acc_phase ^ 1u, cta_abort, p.status, ST_MMA_ACC)) break;
+        ptx::tcgen05_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!ptx::mbar_wait(&full[stage], phase, cta_abort, p.status, ST_MMA_FULL)) {
+            ok = false;
+            break;
+          }
+          ptx::tcgen05_fence_after_sync();
+          const uint32_t a_addr = ptx::smem_u32(smem + stage * kStageBytes);
+          const uint64_t a_desc = ptx::smem_desc(p.a_desc_hi, a_addr);
+          const uint64_t b_desc = ptx::smem_desc(p.b_desc_hi, a_addr + kABytes);
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk)
+            ptx::umma_f16(d_tmem, a_desc + static_cast<uint64_t>(kk * p.a_kstep),
+                          b_desc + static_cast<uint64_t>(kk * p.b_kstep), p.idesc,
+                          (kb | kk) != 0 ? 1u : 0u);
+          ptx::umma_commit(&empty[stage]);  // frees the smem stage when these MMAs retire
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        ptx::umma_commit(&tfull[acc]);  // accumulator complete -> epilogue
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+      int m_idx, n_idx;
+      tile_coords(p, tile, &m_idx, &n_idx);
+      if (!ptx::mbar_wait(&tfull[acc], acc_phase, cta_abort, p.status, ST_EPILOGUE)) break;
+      ptx::tcgen05_fence_after_sync();
+      const uint32_t taddr =
+          tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      const int64_t row = static_cast<int64_t>(m_idx) * BM + quarter * 32 + lane;
+      if (EPI == EPI_PLAIN) epi_plain<T>(p, taddr, row, n_idx * BN);
+      if (EPI == EPI_SWIGLU_FWD) epi_swiglu_fwd<T>(p, taddr, row, n_idx * (BN / 2));
+      if (EPI == EPI_SWIGLU_BWD) epi_swiglu_bwd<T>(p, taddr, row, n_idx * BN);
+      if (EPI == EPI_LCE) epi_lce<T>(p, taddr, row, n_idx * BN, n_idx);
+      ptx::tcgen05_fence_before_sync();
+      ptx::mbar_arrive(&tempty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  ptx::tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tcgen05_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ----------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// One operand as the caller describes it.
+struct Operand {
+  const void* ptr = nullptr;
+  int kmajor = 1;    // 1: [mn, k] rows with k contiguous; 0: [k, mn] rows with mn contiguous
+  int64_t mn = 0;    // extent along M (A) or N (B)
+  int64_t k = 0;
+  int64_t ld = 0;    // row stride in elements
+  int box_mn = 0;    // rows of the K-major box (BM, BN or BN/2)
+};
+
+inline int make_tmap(CUtensorMap* tm, const Operand& o, bool bf16, const char* what) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return BT_ERR_DRIVER;
+  }
+  if (!aligned16(o.ptr) || (o.ld * 2) % 16 != 0) {
+    set_error("%s: operand must be 16-byte aligned with a row stride that is a multiple of 8 elements",
+              what);
+    return BT_ERR_ARG;
+  }
+  cuuint64_t dims[2];
+  cuuint32_t box[2];
+  if (o.kmajor) {
+    dims[0] = static_cast<cuuint64_t>(o.k);
+    dims[1] = static_cast<cuuint64_t>(o.mn);
+    box[0] = BK;
+    box[1] = static_cast<cuuint32_t>(o.box_mn);
+  } else {
+    dims[0] = static_cast<cuuint64_t>(o.mn);
+    dims[1] = static_cast<cuuint64_t>(o.k);
+    box[0] = 64;
+    box[1] = BK;
+  }
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(o.ld) * 2};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                        2, const_cast<void*>(o.ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("%s: cuTensorMapEncodeTiled failed with CUresult %d (dims %llu x %llu, ld %lld)", what,
+              static_cast<int>(r), (unsigned long long)dims[0], (unsigned long long)dims[1],
+              (long long)o.ld);
+    return BT_ERR_DRIVER;
+  }
+  return BT_OK;
+}
+
+template <int EPI, typename T>
+int launch_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1,
+             const CUtensorMap& b1, const Params& p, cudaStream_t s) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  auto* kern = gemm_kernel<EPI, T>;
+  std::call_once(once, [&] {
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) {
+    set_error("gemm: cannot reserve %d bytes of shared memory: %s", kSmemBytes,
+              cudaGetErrorString(attr_err));
+    return BT_ERR_LAUNCH;
+  }
+  const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  kern<<<grid, kThreads, kSmemBytes, s>>>(a0, b0, a1, b1, p);
+  BT_CHECK_LAUNCH("gemm_kernel");
+  return BT_OK;
+}
+
+// Describes one GEMM launch; pair 1 and b1 are optional.
+struct Launch {
+  Operand a0, b0, a1, b1;
+  bool dual_b = false;    // b1 is the second half of the B tile (same K range as pair 0)
+  bool two_pairs = false; // (a1, b1) is a second contraction into the same accumulator
+  bool bf16 = true;
+  Params p{};
+};
+
+// cuTensorMapEncodeTiled is a driver call and wants a current context on the calling
+// thread; a thread that has made no runtime call yet (an autograd worker, say) has
+// none bound, so bind the primary context of the current device once per thread.
+inline void bind_context_once() {
+  thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
+template <int EPI>
+int launch(Launch& L, cudaStream_t s) {
+  bind_context_once();
+  Params& p = L.p;
+  const int n_tile = L.dual_b ? BN / 2 : BN;
+  p.K0 = static_cast<int>(L.a0.k);
+  p.K1 = L.two_pairs ? static_cast<int>(L.a1.k) : 0;
+  p.tiles_m = static_cast<int>(ceil_div(p.M, BM));
+  p.tiles_n = static_cast<int>(ceil_div(p.N, n_tile));
+  const int64_t nt = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+  if (nt <= 0 || nt > 0x7fffffff || p.K0 <= 0) {
+    set_error("gemm: empty or oversized problem (M=%d N=%d K=%d)", p.M, p.N, p.K0);
+    return BT_ERR_ARG;
+  }
+  p.num_tiles = static_cast<int>(nt);
+  p.a_kmajor = L.a0.kmajor;
+  p.b_kmajor = L.b0.kmajor;
+  p.dual_b = L.dual_b ? 1 : 0;
+  p.idesc = ptx::make_idesc_f16(L.bf16, !L.a0.kmajor, !L.b0.kmajor, BM, BN);
+  p.a_desc_hi = ptx::make_smem_desc_hi(L.a0.kmajor != 0, kBoxBytesMN);
+  p.b_desc_hi = ptx::make_smem_desc_hi(L.b0.kmajor != 0, kBoxBytesMN);
+  p.a_kstep = L.a0.kmajor ? (32u >> 4) : (16u * 128u >> 4);
+  p.b_kstep = L.b0.kmajor ? (32u >> 4) : (16u * 128u >> 4);
+  L.a0.box_mn = BM;
+  L.b0.box_mn = n_tile;
+  CUtensorMap ta0, tb0, ta1, tb1;
+  int rc;
+  if ((rc = make_tmap(&ta0, L.a0, L.bf16, "gemm A")) != BT_OK) return rc;
+  if ((rc = make_tmap(&tb0, L.b0, L.bf16, "gemm B")) != BT_OK) return rc;
+  ta1 = ta0;
+  tb1 = tb0;
+  if (L.two_pairs) {
+    if (L.a1.kmajor != L.a0.kmajor || L.b1.kmajor != L.b0.kmajor) {
+      set_error("gemm: both operand pairs must share their layouts");
+      return BT_ERR_ARG;
+    }
+    L.a1.box_mn = BM;
+    L.b1.box_mn = n_tile;
+    if ((rc = make_tmap(&ta1, L.a1, L.bf16, "gemm A1")) != BT_OK) return rc;
+    if ((rc = make_tmap(&tb1, L.b1, L.bf16, "gemm B1")) != BT_OK) return rc;
+  } else if (L.dual_b) {
+    if (!L.b0.kmajor || !L.b1.kmajor) {
+      set_error("gemm: dual-B mode needs K-major B operands");
+      return BT_ERR_ARG;
+    }
+    L.b1.box_mn = n_tile;
+    if ((rc = make_tmap(&tb1, L.b1, L.bf16, "gemm B1")) != BT_OK) return rc;
+  }
+  return L.bf16 ? launch_t<EPI, __nv_bfloat16>(ta0, tb0, ta1, tb1, p, s)
+                : launch_t<EPI, __half>(ta0, tb0, ta1, tb1, p, s);
+}
+
+}  // namespace gemm
+}  // namespace bt

@@ -1,0 +1,202 @@
+// C entry points that run on the tcgen05 GEMM core: the plain GEMM, the fused
+// SwiGLU MLP forward / backward and the logits + softmax-statistics step of the
+// fused cross-entropy.
+#include "gemm_sm100.cuh"
+
+namespace bt {
+namespace {
+
+using gemm::Launch;
+using gemm::Operand;
+
+bool is16(int dtype) { return dtype == BT_BF16 || dtype == BT_FP16; }
+
+Operand operand(const void* ptr, bool kmajor, int64_t mn, int64_t k, int64_t ld) {
+  Operand o;
+  o.ptr = ptr;
+  o.kmajor = kmajor ? 1 : 0;
+  o.mn = mn;
+  o.k = k;
+  o.ld = ld;
+  return o;
+}
+
+bool rows_aligned(const void* p, int64_t ld, int elem_bytes) {
+  return p == nullptr || (aligned16(p) && (ld * elem_bytes) % 16 == 0);
+}
+
+int check_dims(const char* what, int64_t m, int64_t n, int64_t k) {
+  if (m <= 0 || n <= 0 || k <= 0 || m > 0x7fffffffll || n > 0x7fffffffll || k > 0x7fffffffll) {
+    set_error("%s: bad extents M=%lld N=%lld K=%lld", what, (long long)m, (long long)n, (long long)k);
+    return BT_ERR_ARG;
+  }
+  return BT_OK;
+}
+
+// out[M,N] = T(alpha * (op(A) op(B) + addend))
+int plain_gemm(const void* A, bool a_kmajor, int64_t lda, const void* B, bool b_kmajor, int64_t ldb,
+               const void* A1, int64_t lda1, const void* B1, int64_t ldb1, int64_t K1, void* D,
+               int64_t ldd, int64_t M, int64_t N, int64_t K, bool bf16, bool out_fp32,
+               const float* addend, int64_t ld_add, const float* alpha, int32_t* status,
+               cudaStream_t s) {
+  Launch L;
+  L.bf16 = bf16;
+  L.a0 = operand(A, a_kmajor, M, K, lda);
+  L.b0 = operand(B, b_kmajor, N, K, ldb);
+  if (A1 != nullptr) {
+    L.two_pairs = true;
+    L.a1 = operand(A1, a_kmajor, M, K1, lda1);
+    L.b1 = operand(B1, b_kmajor, N, K1, ldb1);
+  }
+  L.p.M = static_cast<int>(M);
+  L.p.N = static_cast<int>(N);
+  L.p.status = status;
+  L.p.out = D;
+  L.p.ldo = ldd;
+  L.p.out_fp32 = out_fp32 ? 1 : 0;
+  L.p.addend = addend;
+  L.p.ld_add = ld_add;
+  L.p.alpha = alpha;
+  L.p.vec_ok = rows_aligned(D, ldd, out_fp32 ? 4 : 2) && rows_aligned(addend, ld_add, 4);
+  return gemm::launch<gemm::EPI_PLAIN>(L, s);
+}
+
+}  // namespace
+}  // namespace bt
+
+extern "C" int bt_gemm(const void* A, const void* B, void* D, int64_t M, int64_t N, int64_t K,
+                       int64_t lda, int64_t ldb, int64_t ldd, int a_kmajor, int b_kmajor,
+                       int in_dtype, int out_dtype, const float* addend, int64_t ld_addend,
+                       const float* alpha, int32_t* status, void* stream) {
+  using namespace bt;
+  BT_CHECK_ARG(is16(in_dtype), "gemm: operands must be bf16 or fp16 (got dtype %d)", in_dtype);
+  BT_CHECK_ARG(out_dtype == in_dtype || out_dtype == BT_FP32,
+               "gemm: result must have the operand dtype or be fp32");
+  BT_CHECK_ARG(A && B && D, "gemm: null pointer");
+  if (int rc = check_dims("gemm", M, N, K)) return rc;
+  BT_CHECK_ARG(ldd >= N && (addend == nullptr || ld_addend >= N), "gemm: result stride too small");
+  return plain_gemm(A, a_kmajor != 0, lda, B, b_kmajor != 0, ldb, nullptr, 0, nullptr, 0, 0, D, ldd,
+                    M, N, K, in_dtype == BT_BF16, out_dtype == BT_FP32, addend, ld_addend, alpha,
+                    status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bt_mlp_fwd(const void* x, const void* wg, const void* wu, const void* wd, void* gate,
+                          void* up, void* h, void* y, int64_t T, int64_t H, int64_t I, int64_t ld_x,
+                          int dtype, int32_t* status, void* stream) {
+  using namespace bt;
+  BT_CHECK_ARG(is16(dtype), "mlp_fwd: bf16 or fp16 only (got dtype %d)", dtype);
+  BT_CHECK_ARG(T >= 0, "mlp_fwd: negative T");
+  if (T == 0) return BT_OK;
+  BT_CHECK_ARG(x && wg && wu && wd && gate && up && h && y, "mlp_fwd: null pointer");
+  if (int rc = check_dims("mlp_fwd", T, I, H)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool bf16 = dtype == BT_BF16;
+  {
+    // gate | up = x [Wg ; Wu]^T with the SwiGLU epilogue
+    gemm::Launch L;
+    L.bf16 = bf16;
+    L.dual_b = true;
+    L.a0 = operand(x, true, T, H, ld_x);
+    L.b0 = operand(wg, true, I, H, H);
+    L.b1 = operand(wu, true, I, H, H);
+    L.p.M = static_cast<int>(T);
+    L.p.N = static_cast<int>(I);
+    L.p.status = status;
+    L.p.gate = gate;
+    L.p.up = up;
+    L.p.h = h;
+    L.p.ld_act = I;
+    L.p.vec_ok = rows_aligned(gate, I, 2) && rows_aligned(up, I, 2) && rows_aligned(h, I, 2);
+    if (int rc = gemm::launch<gemm::EPI_SWIGLU_FWD>(L, s)) return rc;
+  }
+  // y = h Wd^T
+  return plain_gemm(h, true, I, wd, true, I, nullptr, 0, nullptr, 0, 0, y, H, T, H, I, bf16, false,
+                    nullptr, 0, nullptr, status, s);
+}
+
+extern "C" int bt_mlp_bwd(const void* dy, const void* x, const void* wg, const void* wu,
+                          const void* wd, const void* gate, const void* up, const void* h,
+                          void* dgate, void* dup, void* dx, void* dwg, void* dwu, void* dwd,
+                          int64_t T, int64_t H, int64_t I, int64_t ld_x, int64_t ld_dy, int dtype,
+                          int32_t* status, void* stream) {
+  using namespace bt;
+  BT_CHECK_ARG(is16(dtype), "mlp_bwd: bf16 or fp16 only (got dtype %d)", dtype);
+  BT_CHECK_ARG(T > 0, "mlp_bwd: T must be positive");
+  BT_CHECK_ARG(dy && x && wg && wu && wd && gate && up && h && dgate && dup, "mlp_bwd: null pointer");
+  if (int rc = check_dims("mlp_bwd", T, I, H)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool bf16 = dtype == BT_BF16;
+  {
+    // dh = dy Wd (Wd stored [H, I] = [K, N]); epilogue -> dgate, dup
+    gemm::Launch L;
+    L.bf16 = bf16;
+    L.a0 = operand(dy, true, T, H, ld_dy);
+    L.b0 = operand(wd, false, I, H, I);
+    L.p.M = static_cast<int>(T);
+    L.p.N = static_cast<int>(I);
+    L.p.status = status;
+    L.p.gate = const_cast<void*>(gate);
+    L.p.up = const_cast<void*>(up);
+    L.p.out = dgate;
+    L.p.h = dup;
+    L.p.ld_act = I;
+    L.p.vec_ok = rows_aligned(gate, I, 2) && rows_aligned(up, I, 2) && rows_aligned(dgate, I, 2) &&
+                 rows_aligned(dup, I, 2);
+    if (int rc = gemm::launch<gemm::EPI_SWIGLU_BWD>(L, s)) return rc;
+  }
+  if (dwd != nullptr) {  // dWd[H, I] = dy^T h
+    if (int rc = plain_gemm(dy, false, ld_dy, h, false, I, nullptr, 0, nullptr, 0, 0, dwd, I, H, I, T,
+                            bf16, false, nullptr, 0, nullptr, status, s))
+      return rc;
+  }
+  if (dwg != nullptr) {  // dWg[I, H] = dgate^T x
+    if (int rc = plain_gemm(dgate, false, I, x, false, ld_x, nullptr, 0, nullptr, 0, 0, dwg, H, I, H,
+                            T, bf16, false, nullptr, 0, nullptr, status, s))
+      return rc;
+  }
+  if (dwu != nullptr) {  // dWu[I, H] = dup^T x
+    if (int rc = plain_gemm(dup, false, I, x, false, ld_x, nullptr, 0, nullptr, 0, 0, dwu, H, I, H, T,
+                            bf16, false, nullptr, 0, nullptr, status, s))
+      return rc;
+  }
+  if (dx != nullptr) {  // dx[T, H] = dgate Wg + dup Wu  (one accumulator, two K ranges)
+    if (int rc = plain_gemm(dgate, true, I, wg, false, H, dup, I, wu, H, I, dx, H, T, H, I, bf16,
+                            false, nullptr, 0, nullptr, status, s))
+      return rc;
+  }
+  return BT_OK;
+}
+
+extern "C" int64_t bt_lce_num_vtiles(int64_t V) { return (V + bt::gemm::BN - 1) / bt::gemm::BN; }
+
+extern "C" int bt_lce_logits_stats(const void* hidden, const void* W, const int64_t* labels,
+                                   void* logits, float* tile_stats, float* tgt_logit, int64_t rows,
+                                   int64_t H, int64_t V, int64_t ld_hidden, int64_t ld_logits,
+                                   int64_t v_offset, int64_t ignore_index, int dtype,
+                                   int32_t* status, void* stream) {
+  using namespace bt;
+  BT_CHECK_ARG(is16(dtype), "lce_logits_stats: bf16 or fp16 only (got dtype %d)", dtype);
+  BT_CHECK_ARG(rows >= 0, "lce_logits_stats: negative rows");
+  if (rows == 0) return BT_OK;
+  BT_CHECK_ARG(hidden && W && labels && logits && tile_stats && tgt_logit,
+               "lce_logits_stats: null pointer");
+  if (int rc = check_dims("lce_logits_stats", rows, V, H)) return rc;
+  BT_CHECK_ARG(ld_logits >= V, "lce_logits_stats: logits stride smaller than V");
+  gemm::Launch L;
+  L.bf16 = dtype == BT_BF16;
+  L.a0 = operand(hidden, true, rows, H, ld_hidden);
+  L.b0 = operand(W, true, V, H, H);
+  L.p.M = static_cast<int>(rows);
+  L.p.N = static_cast<int>(V);
+  L.p.status = status;
+  L.p.out = logits;
+  L.p.ldo = ld_logits;
+  L.p.labels = labels;
+  L.p.tile_stats = tile_stats;
+  L.p.tgt_logit = tgt_logit;
+  L.p.v_offset = v_offset;
+  L.p.ignore_index = ignore_index;
+  L.p.n_vtiles = static_cast<int>(bt_lce_num_vtiles(V));
+  L.p.vec_ok = rows_aligned(logits, ld_logits, 2);
+  return gemm::launch<gemm::EPI_LCE>(L, static_cast<cudaStream_t>(stream));
+}

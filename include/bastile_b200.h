@@ -110,8 +110,10 @@ int bt_swiglu_bwd(const void* dy, const void* gate, const void* up,
  *   a_kmajor = 0: A is stored [K,M] with M contiguous (row stride lda)
  *   b_kmajor = 1: B is stored [N,K] with K contiguous (row stride ldb)
  *   b_kmajor = 0: B is stored [K,N] with N contiguous (row stride ldb)
- * out_dtype selects the storage of D (row stride ldd); accumulate != 0 adds the
- * product to the existing fp32 D (requires out_dtype = BT_FP32).
+ * The epilogue computes D = T_out(alpha[0] * (A*B + addend)): out_dtype selects
+ * the storage of D (the operand dtype or BT_FP32, row stride ldd); `addend` is
+ * an optional fp32 [M,N] matrix (row stride ld_addend; may alias an fp32 D to
+ * accumulate in place); `alpha` is an optional DEVICE scalar (NULL = 1).
  * `status` points at a caller-owned, zero-initialised int32 device word that a
  * kernel sets non-zero if one of its bounded barrier waits runs out.
  * This is the library GEMM that the reference takes from cuBLAS through
@@ -121,7 +123,8 @@ int bt_gemm(const void* A, const void* B, void* D,
             int64_t M, int64_t N, int64_t K,
             int64_t lda, int64_t ldb, int64_t ldd,
             int a_kmajor, int b_kmajor, int in_dtype, int out_dtype,
-            int accumulate, int32_t* status, void* stream);
+            const float* addend, int64_t ld_addend, const float* alpha,
+            int32_t* status, void* stream);
 
 /* ------------------------------------------------------ SwiGLU MLP (fused)  */
 

@@ -1,0 +1,207 @@
+"""The tcgen05 GEMM core and the fused SwiGLU MLP through the C ABI, against the oracle."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import BF16_TOL, assert_close, load_golden
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _gemm(A, B, M, N, K, ak, bk, out_dtype=None, addend=None, alpha=None):
+    from bastile_b200 import _lib
+
+    lib = _lib.get_lib()
+    dev = A.device
+    out_dtype = out_dtype or A.dtype
+    D = torch.full((M, N), float("nan"), device=dev, dtype=out_dtype)
+    st = _lib.status_word(dev)
+    rc = lib.bt_gemm(A.data_ptr(), B.data_ptr(), D.data_ptr(), M, N, K, A.stride(0), B.stride(0), N, int(ak), int(bk),
+                     _lib.dtype_code(A.dtype), _lib.dtype_code(out_dtype),
+                     addend.data_ptr() if addend is not None else None, N,
+                     alpha.data_ptr() if alpha is not None else None, st.data_ptr(), _lib.stream_ptr(dev))
+    _lib.check(rc, "bt_gemm")
+    _lib.check_status(dev, "bt_gemm")
+    return D
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("ak,bk", [(1, 1), (1, 0), (0, 1), (0, 0)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (136, 264, 72), (8, 8, 8), (300, 520, 1000), (1, 1000, 130),
+                                   (640, 1024, 520)])
+def test_gemm_layouts_and_ragged_shapes(M, N, K, ak, bk, dtype):
+    if (ak or bk) and K % 8:
+        pytest.skip("K-major operands need a row stride that is a multiple of 8 elements")
+    torch.manual_seed(M + N + K)
+    A = torch.randn((M, K) if ak else (K, (M + 7) // 8 * 8), device=DEV).to(dtype)
+    B = torch.randn((N, K) if bk else (K, (N + 7) // 8 * 8), device=DEV).to(dtype)
+    Af = A.float().cpu().numpy() if ak else A.float().cpu().numpy().T[:M]
+    Bf = B.float().cpu().numpy() if bk else B.float().cpu().numpy().T[:N]
+    ref = Af.astype(np.float64) @ Bf.astype(np.float64).T
+    D = _gemm(A, B, M, N, K, ak, bk)
+    tol = dict(rtol=2e-2, atol=2e-2 * max(1.0, np.sqrt(K) / 4))
+    assert_close(D, ref, what="D", **tol)
+
+
+def test_gemm_fp32_out_addend_alpha_and_inplace_accumulate():
+    torch.manual_seed(0)
+    M, N, K = 200, 328, 264
+    A = torch.randn(M, K, device=DEV).bfloat16()
+    B = torch.randn(N, K, device=DEV).bfloat16()
+    add = torch.randn(M, N, device=DEV)
+    alpha = torch.tensor([0.25], device=DEV)
+    ref = (A.float() @ B.float().T + add) * 0.25
+    D = _gemm(A, B, M, N, K, 1, 1, out_dtype=torch.float32, addend=add, alpha=alpha)
+    assert_close(D, ref, what="fp32 out", rtol=1e-4, atol=1e-3)
+    D16 = _gemm(A, B, M, N, K, 1, 1, addend=add, alpha=alpha)
+    assert_close(D16, ref, what="bf16 out", **BF16_TOL)
+    # accumulate in place: addend aliases the fp32 result
+    from bastile_b200 import _lib
+
+    lib = _lib.get_lib()
+    acc = add.clone()
+    st = _lib.status_word(acc.device)
+    for _ in range(2):
+        _lib.check(lib.bt_gemm(A.data_ptr(), B.data_ptr(), acc.data_ptr(), M, N, K, K, K, N, 1, 1, 0, 2, acc.data_ptr(),
+                               N, None, st.data_ptr(), _lib.stream_ptr(acc.device)), "bt_gemm")
+    _lib.check_status(acc.device, "bt_gemm")
+    assert_close(acc, add + 2 * (A.float() @ B.float().T), what="accumulate", rtol=1e-4, atol=2e-3)
+
+
+def test_gemm_persistent_many_tiles_matches_fp32_reference():
+    """More tiles than SMs (several per CTA, both accumulator buffers, ring wrap-around)."""
+    torch.manual_seed(1)
+    M, N, K = 2048, 5120, 1024
+    A = (torch.randn(M, K, device=DEV) * 0.1).bfloat16()
+    B = (torch.randn(N, K, device=DEV) * 0.1).bfloat16()
+    D = _gemm(A, B, M, N, K, 1, 1)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ref = A.float() @ B.float().T
+    assert_close(D, ref, what="D", **BF16_TOL)
+
+
+def test_gemm_rejects_bad_arguments():
+    from bastile_b200 import _lib
+
+    lib = _lib.get_lib()
+    A = torch.randn(16, 20, device=DEV).bfloat16()  # row stride 20: not a multiple of 8
+    B = torch.randn(16, 20, device=DEV).bfloat16()
+    D = torch.empty(16, 16, device=DEV).bfloat16()
+    st = _lib.status_word(A.device)
+    rc = lib.bt_gemm(A.data_ptr(), B.data_ptr(), D.data_ptr(), 16, 16, 20, 20, 20, 16, 1, 1, 0, 0, None, 0, None,
+                     st.data_ptr(), _lib.stream_ptr(A.device))
+    assert rc == -1 and b"multiple of 8" in lib.bt_last_error()
+    rc = lib.bt_gemm(A.data_ptr(), B.data_ptr(), D.data_ptr(), 16, 16, 16, 24, 24, 16, 1, 1, 2, 2, None, 0, None,
+                     st.data_ptr(), _lib.stream_ptr(A.device))
+    assert rc == -1  # fp32 operands are not supported by the tensor-core path
+
+
+# ------------------------------------------------------------------------------ MLP
+def _mlp_case(t, hidden, inter, dtype, seed=0, w_std=0.05):
+    torch.manual_seed(seed)
+    x = torch.randn(t, hidden, device=DEV).to(dtype)
+    wg = (torch.randn(inter, hidden, device=DEV) * w_std).to(dtype)
+    wu = (torch.randn(inter, hidden, device=DEV) * w_std).to(dtype)
+    wd = (torch.randn(hidden, inter, device=DEV) * w_std).to(dtype)
+    dy = torch.randn(t, hidden, device=DEV).to(dtype)
+    return x, wg, wu, wd, dy
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("t,hidden,inter", [(21, 64, 160), (256, 256, 768), (300, 512, 1384), (1, 128, 256)])
+def test_mlp_fwd_bwd_vs_oracle(t, hidden, inter, dtype):
+    from bastile_b200.ops.swiglu import SwiGLUMLPFunction
+
+    x, wg, wu, wd, dy = _mlp_case(t, hidden, inter, dtype)
+    xs, wgs, wus, wds = (a.clone().requires_grad_(True) for a in (x, wg, wu, wd))
+    y = SwiGLUMLPFunction.apply(xs, wgs, wus, wds)
+    y.backward(dy)
+    f = lambda a: a.detach().float().cpu().numpy()  # noqa: E731
+    y_ref, _, _, _ = oracle.mlp_fwd(f(x), f(wg), f(wu), f(wd))
+    dx_ref, dwg_ref, dwu_ref, dwd_ref = oracle.mlp_bwd(f(dy), f(x), f(wg), f(wu), f(wd))
+
+    def tol(ref):
+        s = float(np.abs(ref).max())
+        return dict(rtol=2e-2, atol=2e-2 * max(1.0, s))
+
+    assert_close(y, y_ref, what="y", **tol(y_ref))
+    assert_close(xs.grad, dx_ref, what="dx", **tol(dx_ref))
+    assert_close(wgs.grad, dwg_ref, what="dwg", **tol(dwg_ref))
+    assert_close(wus.grad, dwu_ref, what="dwu", **tol(dwu_ref))
+    assert_close(wds.grad, dwd_ref, what="dwd", **tol(dwd_ref))
+
+
+def test_mlp_golden_hf_fixture():
+    """HF eager Qwen3MLP outputs (fp32) vs the bf16 kernels on the same inputs."""
+    from bastile_b200.ops.swiglu import SwiGLUMLPFunction
+
+    g = load_golden("mlp_hf.npz")
+    t = lambda a: torch.as_tensor(a).to(DEV, torch.bfloat16)  # noqa: E731
+    x, wg, wu, wd = (t(g[k]).requires_grad_(True) for k in ("x", "wg", "wu", "wd"))
+    y = SwiGLUMLPFunction.apply(x, wg, wu, wd)
+    y.backward(t(g["dy"]))
+    assert_close(y, g["y"], what="y", **BF16_TOL)
+    assert_close(x.grad, g["dx"], what="dx", **BF16_TOL)
+    assert_close(wg.grad, g["dwg"], what="dwg", rtol=2e-2, atol=4e-2)
+    assert_close(wu.grad, g["dwu"], what="dwu", rtol=2e-2, atol=4e-2)
+    assert_close(wd.grad, g["dwd"], what="dwd", rtol=2e-2, atol=4e-2)
+
+
+def test_mlp_module_matches_hf_eager_module():
+    """B200SwiGLUMLP against transformers' Qwen3MLP with the same weights (bf16 on the GPU)."""
+    import transformers.models.qwen3.modeling_qwen3 as q3
+    from golden.make_golden import tiny_qwen3_config
+
+    from bastile_b200.ops.swiglu import B200SwiGLUMLP
+
+    import bastile_b200
+
+    bastile_b200.reset()
+    cfg = tiny_qwen3_config()
+    torch.manual_seed(0)
+    hf = q3.Qwen3MLP(cfg).to(DEV, torch.bfloat16)
+    ours = B200SwiGLUMLP(cfg).to(DEV, torch.bfloat16)
+    ours.load_state_dict(hf.state_dict())
+    x = torch.randn(2, 128, cfg.hidden_size, device=DEV, dtype=torch.bfloat16)
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    ya, yb = ours(xa), hf(xb)
+    dy = torch.randn_like(ya)
+    ya.backward(dy)
+    yb.backward(dy)
+    assert_close(ya, yb, what="y", **BF16_TOL)
+    assert_close(xa.grad, xb.grad, what="dx", **BF16_TOL)
+    for (n, pa), (_, pb) in zip(ours.named_parameters(), hf.named_parameters()):
+        assert_close(pa.grad, pb.grad, what=n, rtol=2e-2, atol=5e-2)
+
+
+def test_mlp_full_size_linearity_and_sampled_rows():
+    """BASELINE shape x[8192,4096], intermediate 12288: sampled rows vs the oracle, and the
+    backward's linearity in the upstream gradient."""
+    from bastile_b200.ops.swiglu import SwiGLUMLPFunction
+
+    x, wg, wu, wd, dy = _mlp_case(8192, 4096, 12288, torch.bfloat16, seed=1, w_std=0.02)
+    xs = x.clone().requires_grad_(True)
+    wgs, wus, wds = (a.clone().requires_grad_(True) for a in (wg, wu, wd))
+    y = SwiGLUMLPFunction.apply(xs, wgs, wus, wds)
+    y.backward(dy)
+    rows = torch.tensor([0, 1, 127, 128, 4095, 8191], device=DEV)
+    f = lambda a: a.detach().float().cpu().numpy()  # noqa: E731
+    y_ref, _, _, _ = oracle.mlp_fwd(f(x[rows]), f(wg), f(wu), f(wd))
+    # gate/up/h are rounded to bf16 on the way (as in the op being replaced): scale atol by |y|
+    assert_close(y[rows], y_ref, what="y rows", rtol=2e-2, atol=2e-2 * max(1.0, float(np.abs(y_ref).max()) / 2))
+    # dx rows depend only on their own row of x and dy
+    dx_ref, _, _, _ = oracle.mlp_bwd(f(dy[rows]), f(x[rows]), f(wg), f(wu), f(wd))
+    assert_close(xs.grad[rows], dx_ref, what="dx rows", rtol=2e-2, atol=2e-2 * max(1.0, float(np.abs(dx_ref).max()) / 2))
+    # a slice of dWd = dy^T h against fp32 matmul of the saved bf16 operands
+    torch.backends.cuda.matmul.allow_tf32 = False
+    h = torch.nn.functional.silu(x.float() @ wg.float().T[:, :256]) * (x.float() @ wu.float().T[:, :256])
+    dwd_ref = dy.float().T @ h
+    assert_close(wds.grad[:, :256], dwd_ref, what="dwd slice", rtol=2e-2, atol=2e-2 * float(dwd_ref.abs().max()))
+    # linearity: backward(2*dy) == 2*backward(dy)
+    xs2 = x.clone().requires_grad_(True)
+    y2 = SwiGLUMLPFunction.apply(xs2, wg, wu, wd)
+    y2.backward(dy * 2)
+    assert_close(xs2.grad, xs.grad.float() * 2, what="linearity", rtol=1e-2, atol=1e-2)

@@ -1,0 +1,224 @@
+"""Fused linear + cross-entropy through the C ABI: golden fixtures from the reference's own
+implementation, the reference's unit tests, ragged/edge cases, and the full-size properties."""
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+import oracle
+from conftest import LOSS_REL, assert_close, load_golden
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _run(x, w, t, **kw):
+    from bastile_b200.ops.fused_linear_cross_entropy import fused_linear_cross_entropy
+
+    xs = x.clone().requires_grad_(True)
+    ws = w.clone().requires_grad_(True)
+    loss = fused_linear_cross_entropy(xs, ws, t, **kw)
+    loss.backward()
+    from bastile_b200 import _lib
+
+    _lib.check_status(x.device, "fused_linear_cross_entropy")
+    return loss, xs.grad, ws.grad
+
+
+@pytest.mark.parametrize("name", ["loss_fp32", "grads", "ignore_index", "three_d", "sum", "all_ignored", "ragged"])
+@pytest.mark.parametrize("chunk", [4096, 16])
+def test_lce_golden_reference_fixtures(name, chunk):
+    """Inputs rounded to bf16; expected values recomputed by the oracle on the rounded inputs
+    (the oracle itself is pinned to the reference's fp32 outputs on the unrounded ones)."""
+    g = load_golden(f"lce_{name}.npz")
+    x = torch.as_tensor(g["x"]).to(DEV, torch.bfloat16)
+    w = torch.as_tensor(g["w"]).to(DEV, torch.bfloat16)
+    t = torch.as_tensor(g["t"]).to(DEV)
+    red = str(g["reduction"])
+    if bool(g["three_d"]):
+        xin, tin = x.view(2, -1, x.shape[-1]), t.view(2, -1)
+    else:
+        xin, tin = x, t
+    loss, dx, dw = _run(xin, w, tin, reduction=red, chunk_size=chunk)
+    l_ref, dx_ref, dw_ref = oracle.lce_fwd_bwd(x.float().cpu().numpy(), w.float().cpu().numpy(), g["t"], -100, red)
+    # logits are rounded to bf16 before the softmax (as in the reference), so the loss carries
+    # that rounding: |logit| * 2^-9 per term, averaged
+    assert abs(loss.item() - float(l_ref)) <= 5e-2 * max(1.0, abs(float(l_ref))) if red == "mean" else True
+    assert loss.dtype == torch.float32
+    assert_close(dx.reshape(dx_ref.shape), dx_ref, what="dx", rtol=2e-2, atol=2e-2 * max(1.0, float(np.abs(dx_ref).max())))
+    assert_close(dw, dw_ref, what="dw", rtol=2e-2, atol=2e-2 * max(1.0, float(np.abs(dw_ref).max())))
+
+
+def test_lce_reference_unit_tests_bf16():
+    """tests/ops/test_fused_linear_cross_entropy.py:37-55 (bf16 loss, 5e-2) and the gradient,
+    ignore_index, 3-D and v_chunk_size cases at the same shapes, with bf16 inputs."""
+    torch.manual_seed(42)
+    x = torch.randn(64, 256, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(1024, 256, device=DEV, dtype=torch.bfloat16)
+    t = torch.randint(0, 1024, (64,), device=DEV)
+    ref = F.cross_entropy(F.linear(x.float(), w.float()), t)
+    loss, _, _ = _run(x, w, t)
+    torch.testing.assert_close(loss.float(), ref, rtol=5e-2, atol=5e-2)
+    loss_v, _, _ = _run(x, w, t, v_chunk_size=128)
+    torch.testing.assert_close(loss_v.float(), ref, rtol=5e-2, atol=5e-2)
+    t3 = t.clone()
+    t3[::3] = -100
+    ref3 = F.cross_entropy(F.linear(x.float(), w.float()), t3, ignore_index=-100)
+    loss3, _, _ = _run(x, w, t3)
+    torch.testing.assert_close(loss3.float(), ref3, rtol=5e-2, atol=5e-2)
+
+
+@pytest.mark.parametrize("reduction", ["mean", "sum"])
+@pytest.mark.parametrize("bt,h,v,chunk", [(300, 256, 1000, 128), (1, 64, 8, 4096), (513, 128, 3000, 256),
+                                          (64, 4096, 2048, 4096)])
+def test_lce_small_weights_vs_oracle(bt, h, v, chunk, reduction):
+    """W ~ N(0, 0.02) as in training: loss within 1e-3 relative of the fp32 oracle."""
+    torch.manual_seed(bt + v)
+    x = torch.randn(bt, h, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(v, h, device=DEV) * 0.02).to(torch.bfloat16)
+    t = torch.randint(0, v, (bt,), device=DEV)
+    t[torch.rand(bt, device=DEV) < 0.05] = -100
+    loss, dx, dw = _run(x, w, t, reduction=reduction, chunk_size=chunk)
+    l_ref, dx_ref, dw_ref = oracle.lce_fwd_bwd(x.float().cpu().numpy(), w.float().cpu().numpy(), t.cpu().numpy(), -100,
+                                               reduction)
+    assert abs(loss.item() - float(l_ref)) <= LOSS_REL * abs(float(l_ref)) + 1e-6
+    sx = max(float(np.abs(dx_ref).max()), 1e-6)
+    sw = max(float(np.abs(dw_ref).max()), 1e-6)
+    assert_close(dx, dx_ref, what="dx", rtol=2e-2, atol=2e-2 * sx)
+    assert_close(dw, dw_ref, what="dw", rtol=2e-2, atol=2e-2 * sw)
+
+
+def test_lce_upstream_gradient_scales_both_grads():
+    from bastile_b200.ops.fused_linear_cross_entropy import fused_linear_cross_entropy
+
+    torch.manual_seed(5)
+    x = torch.randn(200, 128, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(600, 128, device=DEV) * 0.05).to(torch.bfloat16)
+    t = torch.randint(0, 600, (200,), device=DEV)
+    grads = []
+    for k in (1.0, 3.0):
+        xs, ws = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        (fused_linear_cross_entropy(xs, ws, t, chunk_size=64) * k).backward()
+        grads.append((xs.grad.float(), ws.grad.float()))
+    assert_close(grads[1][0], grads[0][0] * 3, what="dx", rtol=1e-2, atol=1e-5)
+    assert_close(grads[1][1], grads[0][1] * 3, what="dw", rtol=1e-2, atol=1e-5)
+
+
+def test_lce_bias_falls_back_to_linear_plus_cross_entropy_like_the_reference():
+    from bastile_b200.ops.fused_linear_cross_entropy import fused_linear_cross_entropy
+
+    torch.manual_seed(6)
+    x = torch.randn(16, 64, device=DEV)
+    w = torch.randn(32, 64, device=DEV)
+    b = torch.randn(32, device=DEV)
+    t = torch.randint(0, 32, (16,), device=DEV)
+    torch.testing.assert_close(fused_linear_cross_entropy(x, w, t, bias=b), F.cross_entropy(F.linear(x, w, b), t))
+
+
+def test_lce_fp32_inputs_are_refused_not_silently_downcast():
+    from bastile_b200.ops.fused_linear_cross_entropy import fused_linear_cross_entropy
+
+    with pytest.raises(TypeError):
+        fused_linear_cross_entropy(torch.randn(8, 64, device=DEV), torch.randn(16, 64, device=DEV),
+                                   torch.randint(0, 16, (8,), device=DEV))
+
+
+def test_lce_vocab_shards_emulated_on_one_gpu():
+    """The sharded path's device steps, run shard by shard on one GPU with the exchange done
+    by torch ops: statistics merge, dlogits per shard, dx summed over shards, dW per shard."""
+    from bastile_b200 import _lib
+    from bastile_b200.ops.fused_linear_cross_entropy import merge_shard_stats
+
+    lib = _lib.get_lib()
+    torch.manual_seed(8)
+    bt, h, v, n = 160, 128, 1520, 4  # 380 columns per shard: ragged tiles
+    vs = v // n
+    x = torch.randn(bt, h, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(v, h, device=DEV) * 0.05).to(torch.bfloat16)
+    t = torch.randint(0, v, (bt,), device=DEV)
+    t[::7] = -100
+    dev = x.device
+    st = _lib.status_word(dev)
+    stream = _lib.stream_ptr(dev)
+    ld = (vs + 7) // 8 * 8
+    n_vt = int(lib.bt_lce_num_vtiles(vs))
+    scal = torch.empty(3, device=DEV)
+    _lib.check(lib.bt_lce_count_valid(t.data_ptr(), bt, -100, 1, scal[0:].data_ptr(), scal[1:].data_ptr(), stream), "cv")
+    logits, stats = [], []
+    for r in range(n):
+        lg = torch.empty(bt, ld, device=DEV, dtype=torch.bfloat16)
+        ts = torch.empty(bt, n_vt, 2, device=DEV)
+        tg = torch.empty(bt, device=DEV)
+        rs = torch.empty(bt, 3, device=DEV)
+        wr = w[r * vs:(r + 1) * vs].contiguous()
+        _lib.check(lib.bt_lce_logits_stats(x.data_ptr(), wr.data_ptr(), t.data_ptr(), lg.data_ptr(), ts.data_ptr(),
+                                           tg.data_ptr(), bt, h, vs, h, ld, r * vs, -100, 0, st.data_ptr(), stream), "ls")
+        _lib.check(lib.bt_lce_row_stats(ts.data_ptr(), tg.data_ptr(), rs.data_ptr(), bt, n_vt, stream), "rs")
+        logits.append(lg)
+        stats.append(rs)
+    merged = merge_shard_stats(torch.stack(stats))
+    st_ref = np.stack([oracle.lce_shard_stats(x.float().cpu().numpy(), w[r * vs:(r + 1) * vs].float().cpu().numpy(),
+                                              t.cpu().numpy(), -100, r * vs)[0] for r in range(n)])
+    m_ref = oracle.merge_shard_stats(st_ref)
+    lse = merged[:, 0] + merged[:, 1].log()
+    assert_close(lse, m_ref[:, 0] + np.log(m_ref[:, 1]), what="lse", rtol=2e-3, atol=2e-2)
+    assert_close(merged[:, 2], m_ref[:, 2], what="target logit", rtol=2e-2, atol=2e-2)
+    loss_row = torch.empty(bt, device=DEV)
+    dx = torch.zeros(bt, h, device=DEV)
+    dws = []
+    for r in range(n):
+        wr = w[r * vs:(r + 1) * vs].contiguous()
+        _lib.check(lib.bt_lce_dlogits(logits[r].data_ptr(), merged.data_ptr(), t.data_ptr(), loss_row.data_ptr(),
+                                      scal[1:].data_ptr(), bt, vs, ld, r * vs, -100, 1, 0, stream), "dl")
+        part = torch.empty(bt, h, device=DEV)
+        _lib.check(lib.bt_gemm(logits[r].data_ptr(), wr.data_ptr(), part.data_ptr(), bt, h, vs, ld, h, h, 1, 0, 0, 2,
+                               None, 0, None, st.data_ptr(), stream), "dx")
+        dx += part
+        dwr = torch.empty(vs, h, device=DEV, dtype=torch.bfloat16)
+        _lib.check(lib.bt_gemm(logits[r].data_ptr(), x.data_ptr(), dwr.data_ptr(), vs, h, bt, ld, h, h, 0, 0, 0, 0,
+                               None, 0, None, st.data_ptr(), stream), "dw")
+        dws.append(dwr)
+    _lib.check_status(dev, "sharded lce")
+    l_ref, dx_ref, dw_ref = oracle.lce_fwd_bwd(x.float().cpu().numpy(), w.float().cpu().numpy(), t.cpu().numpy(), -100,
+                                               "mean", n_shards=n)
+    loss = loss_row.sum() * scal[1]
+    assert abs(loss.item() - float(l_ref)) <= 2e-3 * abs(float(l_ref))
+    assert_close(dx, dx_ref, what="dx", rtol=2e-2, atol=2e-2 * float(np.abs(dx_ref).max()))
+    assert_close(torch.cat(dws), dw_ref, what="dw", rtol=2e-2, atol=2e-2 * float(np.abs(dw_ref).max()))
+
+
+def test_lce_full_size_properties():
+    """BASELINE shape hidden[16384,4096] x W[151936,4096], 5 % ignored: loss near ln(V) for
+    small weights, sampled-row loss and dx against the oracle, zero gradient on ignored rows,
+    rows of dW for unused vocabulary entries all <= 0 scaled softmax mass."""
+    torch.manual_seed(2)
+    bt, h, v = 16384, 4096, 151936
+    x = torch.randn(bt, h, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(v, h, device=DEV, dtype=torch.bfloat16) * 0.02)
+    t = torch.randint(0, v, (bt,), device=DEV)
+    t[torch.rand(bt, device=DEV) < 0.05] = -100
+    loss, dx, dw = _run(x, w, t)
+    valid = t != -100
+    assert torch.isfinite(dx).all() and torch.isfinite(dw).all()
+    assert float(dx[~valid].abs().max()) == 0.0
+    rows = torch.tensor([0, 5, 4095, 4096, 9000, 16383], device=DEV)
+    rows = rows[valid[rows]]
+    torch.backends.cuda.matmul.allow_tf32 = False
+    logits = x[rows].float() @ w.float().T
+    lse = torch.logsumexp(logits, dim=-1)
+    row_loss = lse - logits[torch.arange(len(rows)), t[rows]]
+    nv = int(valid.sum())
+    p = torch.softmax(logits, -1)
+    p[torch.arange(len(rows)), t[rows]] -= 1
+    dx_ref = (p / nv) @ w.float()
+    assert_close(dx[rows], dx_ref, what="dx rows", rtol=3e-2, atol=3e-2 * float(dx_ref.abs().max()))
+    # full loss through a chunked fp32 evaluation on the GPU (no [BT,V] fp32 tensor at once)
+    tot = 0.0
+    for s in range(0, bt, 2048):
+        lg = x[s:s + 2048].float() @ w.float().T
+        tot += F.cross_entropy(lg, t[s:s + 2048], ignore_index=-100, reduction="sum").item()
+    assert abs(loss.item() - tot / nv) <= LOSS_REL * tot / nv
+    # gradient of the weight sums to ~0 over the vocabulary for every hidden unit (softmax - onehot sums to 0)
+    col_sum = dw.float().sum(0)
+    assert float(col_sum.abs().max()) < 5e-2

@@ -213,7 +213,8 @@ def test_rope_full_size_roundtrip():
     half = 64
     n0 = q0.float()[..., :half].pow(2) + q0.float()[..., half:].pow(2)
     n1 = q.float()[..., :half].pow(2) + q.float()[..., half:].pow(2)
-    assert float((n1 - n0).abs().max()) < 0.25  # |x|^2 pairs preserved up to bf16 rounding of cos/sin and outputs
+    # |x|^2 of each rotated pair is preserved up to the bf16 rounding of cos/sin and of the outputs
+    assert float(((n1 - n0).abs() - 3e-2 * n0).max()) < 3e-2
     idx = torch.tensor([0, 1, 4095, 8191], device=DEV)
     q_ref, k_ref = oracle.rope(q0[:, :, idx].float().cpu().numpy(), k0[:, :, idx].float().cpu().numpy(),
                                cos[:, idx].float().cpu().numpy(), sin[:, idx].float().cpu().numpy())

@@ -160,6 +160,54 @@ def status_word(dev: torch.device) -> torch.Tensor:
     return buf
 
 
+# ---------------------------------------------------------------------------
+# Instrumentation used by the benchmark: a count of kernels launched by the ops
+# and, when switched on, CUDA-event pairs around the calls into the library
+# (recorded on the stream the kernels run on).  Off by default; the ops pay one
+# attribute test per call.
+class _Instrumentation:
+    def __init__(self):
+        self.enabled = False
+        self.launches = 0
+        self.events: dict[str, list] = {}
+
+    def reset(self, enabled: bool) -> None:
+        self.enabled = enabled
+        self.launches = 0
+        self.events = {}
+
+    def elapsed_ms(self) -> dict[str, tuple[int, float]]:
+        """name -> (calls, total milliseconds); synchronises."""
+        torch.cuda.synchronize()
+        return {k: (len(v), sum(a.elapsed_time(b) for a, b in v)) for k, v in self.events.items()}
+
+
+instr = _Instrumentation()
+
+
+class timed:
+    """``with timed("mlp_fwd", n_kernels, dev):`` around a library call."""
+
+    __slots__ = ("name", "n", "dev", "start")
+
+    def __init__(self, name: str, n_kernels: int, dev: torch.device):
+        self.name, self.n, self.dev, self.start = name, n_kernels, dev, None
+
+    def __enter__(self):
+        if instr.enabled:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record(torch.cuda.current_stream(self.dev))
+        return self
+
+    def __exit__(self, *exc):
+        instr.launches += self.n
+        if self.start is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record(torch.cuda.current_stream(self.dev))
+            instr.events.setdefault(self.name, []).append((self.start, end))
+        return False
+
+
 def check_status(dev: torch.device, what: str) -> None:
     """Synchronising read of the device status word (tests / debugging only)."""
     st = status_word(dev)

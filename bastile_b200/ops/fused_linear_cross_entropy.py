@@ -102,7 +102,8 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             world = dist.get_world_size(group)
             gathered = torch.empty((world, chunk, 3), **f32)
 
-        with _lib.device_of(dev):
+        n_k = 2 + 5 * n_chunks - (1 if n_chunks else 0)
+        with _lib.device_of(dev), _lib.timed("lce_fwd", n_k, dev):
             _lib.check(lib.bt_lce_count_valid(labels.data_ptr(), bt, ignore_index, 1 if reduction == "mean" else 0,
                                               scal[0:].data_ptr(), scal[1:].data_ptr(), stream), "bt_lce_count_valid")
             last_rows = 0
@@ -165,7 +166,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         scale = dloss.detach().to(torch.float32).reshape(1).contiguous()
         need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         dx_out = dw_out = None
-        with _lib.device_of(dev):
+        with _lib.device_of(dev), _lib.timed("lce_bwd", int(need_x) + int(need_w and n_chunks > 0), dev):
             if need_x:
                 dx_out = torch.empty(dx.shape, dtype=x_dtype, device=dev)
                 _lib.check(lib.bt_scale_cast(dx.data_ptr(), dx_out.data_ptr(), dx.numel(), scale.data_ptr(),

@@ -44,7 +44,7 @@ class RMSNormFunction(torch.autograd.Function):
         w = w.contiguous()
         y = torch.empty((m, n), dtype=x.dtype, device=dev)
         rstd = torch.empty((m,), dtype=torch.float32, device=dev)
-        with _lib.device_of(dev):
+        with _lib.device_of(dev), _lib.timed("rmsnorm_fwd", 1, dev):
             rc = lib.bt_rmsnorm_fwd(x2.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), m, n,
                                     x2.stride(0) if m > 1 else n, n, float(eps), code, _lib.stream_ptr(dev))
         _lib.check(rc, "bt_rmsnorm_fwd")
@@ -67,7 +67,7 @@ class RMSNormFunction(torch.autograd.Function):
         dx = torch.empty((m, n), dtype=x2.dtype, device=dev)
         dw = torch.empty((n,), dtype=x2.dtype, device=dev)
         ws = _lib.zero_workspace(dev, int(lib.bt_rmsnorm_bwd_ws_bytes(n)))
-        with _lib.device_of(dev):
+        with _lib.device_of(dev), _lib.timed("rmsnorm_bwd", 1, dev):
             rc = lib.bt_rmsnorm_bwd(dy2.data_ptr(), x2.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
                                     dw.data_ptr(), ws.data_ptr(), m, n, dy2.stride(0) if m > 1 else n,
                                     x2.stride(0) if m > 1 else n, n, code, _lib.stream_ptr(dev))

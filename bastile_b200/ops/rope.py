@@ -38,7 +38,7 @@ def _launch(q_in, k_in, q_out, k_out, cos, sin, negate: bool) -> None:
     if cos.stride(-1) != 1:
         cos, sin = cos.contiguous(), sin.contiguous()
     code = _lib.dtype_code(q_in.dtype)
-    with _lib.device_of(dev):
+    with _lib.device_of(dev), _lib.timed("rope_bwd" if negate else "rope_fwd", 1, dev):
         rc = lib.bt_rope(q_in.data_ptr(), k_in.data_ptr(), q_out.data_ptr(), k_out.data_ptr(), cos.data_ptr(),
                          sin.data_ptr(), b, hq, hk, t, d, _strides3(q_in), _strides3(k_in), _strides3(q_out),
                          _strides3(k_out), _lib.I64x2(cos.stride(0), cos.stride(1)), cos.shape[0],

@@ -43,7 +43,7 @@ class SwiGLUFunction(torch.autograd.Function):
         g2, u2 = _rows(gate), _rows(up)
         rows, cols = g2.shape
         out = torch.empty((rows, cols), dtype=gate.dtype, device=dev)
-        with _lib.device_of(dev):
+        with _lib.device_of(dev), _lib.timed("swiglu_fwd", 1, dev):
             rc = lib.bt_swiglu_fwd(g2.data_ptr(), u2.data_ptr(), out.data_ptr(), rows, cols, _ld(g2), _ld(u2), cols,
                                    _lib.dtype_code(gate.dtype), _lib.stream_ptr(dev))
         _lib.check(rc, "bt_swiglu_fwd")
@@ -62,7 +62,7 @@ class SwiGLUFunction(torch.autograd.Function):
         d2 = _rows(grad_output)
         dg = torch.empty((rows, cols), dtype=g2.dtype, device=dev)
         du = torch.empty((rows, cols), dtype=g2.dtype, device=dev)
-        with _lib.device_of(dev):
+        with _lib.device_of(dev), _lib.timed("swiglu_bwd", 1, dev):
             rc = lib.bt_swiglu_bwd(d2.data_ptr(), g2.data_ptr(), u2.data_ptr(), dg.data_ptr(), du.data_ptr(), rows,
                                    cols, _ld(d2), _ld(g2), _ld(u2), cols, cols, _lib.dtype_code(g2.dtype),
                                    _lib.stream_ptr(dev))
@@ -99,7 +99,7 @@ class SwiGLUMLPFunction(torch.autograd.Function):
         h = torch.empty((t, inter), dtype=x.dtype, device=dev)
         y = torch.empty((t, hidden), dtype=x.dtype, device=dev)
         st = _lib.status_word(dev)
-        with _lib.device_of(dev):
+        with _lib.device_of(dev), _lib.timed("mlp_fwd", 2, dev):
             rc = lib.bt_mlp_fwd(x2.data_ptr(), wgc.data_ptr(), wuc.data_ptr(), wdc.data_ptr(), gate.data_ptr(),
                                 up.data_ptr(), h.data_ptr(), y.data_ptr(), t, hidden, inter, _ld(x2), code,
                                 st.data_ptr(), _lib.stream_ptr(dev))
@@ -131,7 +131,8 @@ class SwiGLUMLPFunction(torch.autograd.Function):
         def p(tensor):
             return tensor.data_ptr() if tensor is not None else None
 
-        with _lib.device_of(dev):
+        n_k = 1 + sum(t is not None for t in (dx, dwg, dwu, dwd))
+        with _lib.device_of(dev), _lib.timed("mlp_bwd", n_k, dev):
             rc = lib.bt_mlp_bwd(dy2.data_ptr(), x2.data_ptr(), wg.data_ptr(), wu.data_ptr(), wd.data_ptr(),
                                 gate.data_ptr(), up.data_ptr(), h.data_ptr(), dgate.data_ptr(), dup.data_ptr(),
                                 p(dx), p(dwg), p(dwu), p(dwd), t, hidden, inter, _ld(x2), _ld(dy2),

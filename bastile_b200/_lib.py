@@ -34,6 +34,8 @@ SIGNATURES = {
     "bt_rmsnorm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "bt_rmsnorm_bwd_ws_bytes": (c_int64, [c_int64]),
+    "bt_rmsnorm_bwd_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                       c_int64, c_int64, c_int64, c_int, c_void_p]),
     "bt_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                         c_int64, c_int64, POINTER(c_int64), POINTER(c_int64), POINTER(c_int64),
                         POINTER(c_int64), POINTER(c_int64), c_int64, c_int, c_int, c_void_p]),

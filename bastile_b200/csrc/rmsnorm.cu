@@ -15,6 +15,8 @@
 // dw is accumulated as fp32 partial sums: registers -> shared -> one global
 // atomic per column per CTA into a zeroed scratch row; the last CTA to finish
 // converts the row to the weight dtype and zeroes the scratch again.
+#include <mutex>
+
 #include "bt_common.cuh"
 
 namespace bt {
@@ -590,4 +592,81 @@ extern "C" int bt_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
   }
   set_error("rmsnorm_bwd: unknown dtype %d", dtype);
   return BT_ERR_ARG;
+}
+
+// ---------------------------------------------------------------------------
+// bt_rmsnorm_bwd_noalloc: the same backward for callers that have no scratch
+// buffer to hand over and no way to get one.
+//
+// Who that is: a host program that embeds this library behind an FFI and owns no
+// device allocator of its own (it receives its tensors from a framework and may
+// not call cudaMalloc behind that framework's back, because the framework has
+// reserved the device memory for its own pool), and code on a latency-critical
+// path where the implicit device-wide synchronisation of cudaMalloc / cudaFree is
+// not acceptable.  For them the column-sum scratch lives in the library image
+// itself, in the fixed-size device array below.  The price: every GPU that loads
+// the library carries the array until the process exits, N is capped at
+// BT_RMSNORM_NOALLOC_MAX_N, and all calls on one GPU share the one array.
+namespace bt {
+namespace {
+
+constexpr int kNoAllocMaxN = BT_RMSNORM_NOALLOC_MAX_N;
+
+// Column sums (fp32) followed by the arrival counter used by dw_finalize.
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocMaxN + 64];
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not an
+// address a kernel may dereference: the device address has to be asked for, per
+// device, with that device current.  Cached after the first successful query.
+std::mutex g_noalloc_mu;
+float* g_noalloc_ptr[64] = {nullptr};
+
+int noalloc_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("rmsnorm_bwd_noalloc: cudaGetDevice failed: %s", cudaGetErrorString(e));
+    return BT_ERR_LAUNCH;
+  }
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_error("rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev,
+                cudaGetErrorString(e));
+      return BT_ERR_LAUNCH;
+    }
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  return BT_OK;
+}
+
+}  // namespace
+}  // namespace bt
+
+extern "C" int bt_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w,
+                                      const float* rstd, void* dx, void* dw, int64_t M, int64_t N,
+                                      int64_t ld_dy, int64_t ld_x, int64_t ld_dx, int dtype,
+                                      void* stream) {
+  using namespace bt;
+  if (N > kNoAllocMaxN) {
+    set_error("rmsnorm_bwd_noalloc: N = %lld exceeds the built-in scratch (max %d columns); "
+              "use bt_rmsnorm_bwd with a caller-owned scratch buffer",
+              (long long)N, kNoAllocMaxN);
+    return BT_ERR_LIMIT;
+  }
+  BT_CHECK_ARG(N > 0, "rmsnorm_bwd_noalloc: N must be positive");
+  float* scratch = nullptr;
+  if (int rc = noalloc_scratch(&scratch)) return rc;
+  // The array keeps whatever the previous call (or a call that was cut short) left in
+  // it; the kernels need zeros in the N sums and in the counter.
+  cudaError_t e = cudaMemsetAsync(scratch, 0, static_cast<size_t>(N + 1) * sizeof(float),
+                                  static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    set_error("rmsnorm_bwd_noalloc: clearing the scratch failed: %s", cudaGetErrorString(e));
+    return BT_ERR_LAUNCH;
+  }
+  return bt_rmsnorm_bwd(dy, x, w, rstd, dx, dw, scratch, M, N, ld_dy, ld_x, ld_dx, dtype, stream);
 }

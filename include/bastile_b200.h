@@ -67,6 +67,28 @@ int bt_rmsnorm_bwd(const void* dy, const void* x, const void* w,
                    int64_t ld_dx, int dtype, void* stream);
 int64_t bt_rmsnorm_bwd_ws_bytes(int64_t N);
 
+/* bt_rmsnorm_bwd for callers that cannot provide scratch memory.  It has no
+ * counterpart in the reference (there, torch allocates the partial-sum tensor).
+ * Meant for hosts that reach this library through an FFI and hold no device
+ * allocator - their tensors come from a framework that has reserved the device
+ * memory for its own pool, so a cudaMalloc of their own is not theirs to make -
+ * and for latency-critical paths that must avoid the device-wide
+ * synchronisation of cudaMalloc/cudaFree.  The scratch is a fixed array inside
+ * the library image: every GPU that loads the library holds it (about 64 KB)
+ * until the process exits, and N may not exceed BT_RMSNORM_NOALLOC_MAX_N
+ * (larger N returns BT_ERR_LIMIT).  The call allocates and frees nothing.
+ * The first call on each device looks up the array's device address; make that
+ * first call outside any stream capture.  All calls on a device share the one
+ * array (it is cleared on the stream at the start of every call): two calls
+ * whose kernels can overlap on the GPU - different streams, no ordering between
+ * them - race on it and give wrong dw.  Arguments and results are otherwise
+ * those of bt_rmsnorm_bwd. */
+#define BT_RMSNORM_NOALLOC_MAX_N 16384
+int bt_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w,
+                           const float* rstd, void* dx, void* dw,
+                           int64_t M, int64_t N, int64_t ld_dy, int64_t ld_x,
+                           int64_t ld_dx, int dtype, void* stream);
+
 /* --------------------------------------------------------------------- RoPE */
 
 /* Rotate-half rotary embedding of q [B,Hq,T,D] and k [B,Hk,T,D]:

@@ -213,27 +213,40 @@ def run_reference_arm(args):
 
 
 # ------------------------------------------------------------------ per-op microbench
-def _median_ms(fn, flush, iters=20, warm=5):
+def _kernel_ms(fn, flush, iters, warm):
+    """Median over `iters` calls of the device time spent inside the library calls that `fn`
+    makes (CUDA events recorded around each call on its stream), L2 flushed before every call."""
     import torch
+
+    from bastile_b200 import _lib
 
     for _ in range(warm):
         fn()
-    ts = []
+    per_iter = []
     for _ in range(iters):
-        flush.zero_()  # evict L2 (256 MiB > 126 MB)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
+        flush.zero_()  # 256 MiB > 126 MB L2
+        _lib.instr.reset(enabled=True)
         fn()
-        b.record()
-        torch.cuda.synchronize()
-        ts.append(a.elapsed_time(b))
-    ts.sort()
-    return ts[len(ts) // 2]
+        per_iter.append(sum(ms for _, ms in _lib.instr.elapsed_ms().values()))
+    _lib.instr.reset(enabled=False)
+    per_iter.sort()
+    return per_iter[len(per_iter) // 2]
 
 
-def per_op_bench(peaks):
-    """Forward+backward of each op at the BASELINE per-op shapes (bf16, seed 1), through the
-    public ops, L2 flushed before every timed call."""
+def _hbm(ms, byts, peaks):
+    g = byts / ms / 1e6
+    return {"ms": ms, "GBps": g, "frac_of_hbm_peak": g / peaks["hbm_gbs"], "algorithmic_MB": byts / 1e6}
+
+
+def _tensor(ms, flops, peaks):
+    t = flops / ms / 1e9
+    return {"ms": ms, "TFLOPs": t, "frac_of_bf16_burst": t / peaks["bf16_tflops"],
+            "frac_of_bf16_sustained": t / peaks["bf16_tflops_sustained"], "algorithmic_TFLOP": flops / 1e12}
+
+
+def per_op_bench(peaks, only=None, iters=None):
+    """Forward+backward of each op at the BASELINE per-op shapes (bf16, seed 1), called through
+    the public ops; the time is that of the kernels (events around the library calls)."""
     import torch
 
     from bastile_b200.ops.fused_linear_cross_entropy import fused_linear_cross_entropy
@@ -246,70 +259,64 @@ def per_op_bench(peaks):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     out = {}
     bf = torch.bfloat16
+    want = lambda name: only is None or only == name  # noqa: E731
 
-    x = torch.randn(8192, 4096, device=dev, dtype=bf).requires_grad_(True)
-    w = (1 + 0.02 * torch.randn(4096, device=dev)).to(bf).requires_grad_(True)
-    dy = torch.randn(8192, 4096, device=dev, dtype=bf)
+    if want("rmsnorm"):
+        for m, n in ((8192, 4096), (262144, 128)):
+            x = torch.randn(m, n, device=dev, dtype=bf).requires_grad_(True)
+            w = (1 + 0.02 * torch.randn(n, device=dev)).to(bf).requires_grad_(True)
+            dy = torch.randn(m, n, device=dev, dtype=bf)
 
-    def rms():
-        x.grad = w.grad = None
-        rms_norm(x, w, 1e-6).backward(dy)
+            def rms():
+                x.grad = w.grad = None
+                rms_norm(x, w, 1e-6).backward(dy)
 
-    ms = _median_ms(rms, flush)
-    byts = 335.63e6
-    out["rmsnorm_8192x4096_fwd_bwd"] = {"ms": ms, "GBps": byts / ms / 1e6, "frac_of_hbm_peak": byts / ms / 1e6 / peaks["hbm_gbs"]}
+            byts = 5 * m * n * 2 + 8 * m + 6 * n
+            out[f"rmsnorm_{m}x{n}_fwd_bwd"] = _hbm(_kernel_ms(rms, flush, iters or 20, 5), byts, peaks)
+            del x, w, dy
 
-    q = torch.randn(1, 32, 8192, 128, device=dev, dtype=bf).requires_grad_(True)
-    k = torch.randn(1, 8, 8192, 128, device=dev, dtype=bf).requires_grad_(True)
-    inv = 1.0 / (1e6 ** (torch.arange(0, 128, 2, dtype=torch.float32) / 128))
-    emb = torch.outer(torch.arange(8192, dtype=torch.float32), inv)
-    emb = torch.cat((emb, emb), -1)
-    cos, sin = emb.cos()[None].to(dev, bf), emb.sin()[None].to(dev, bf)
-    dq, dk = torch.randn_like(q), torch.randn_like(k)
+    if want("rope"):
+        q = torch.randn(1, 32, 8192, 128, device=dev, dtype=bf).requires_grad_(True)
+        k = torch.randn(1, 8, 8192, 128, device=dev, dtype=bf).requires_grad_(True)
+        inv = 1.0 / (1e6 ** (torch.arange(0, 128, 2, dtype=torch.float32) / 128))
+        emb = torch.outer(torch.arange(8192, dtype=torch.float32), inv)
+        emb = torch.cat((emb, emb), -1)
+        cos, sin = emb.cos()[None].to(dev, bf), emb.sin()[None].to(dev, bf)
+        dq, dk = torch.randn_like(q), torch.randn_like(k)
 
-    def rope():
-        q.grad = k.grad = None
-        qo, ko = RoPEFunction.apply(q * 1, k * 1, cos, sin)  # `* 1`: the op rotates its input in place
-        torch.autograd.backward([qo, ko], [dq, dk])
+        def rope():
+            q.grad = k.grad = None
+            qo, ko = RoPEFunction.apply(q * 1, k * 1, cos, sin)  # `* 1`: the op rotates its input in place
+            torch.autograd.backward([qo, ko], [dq, dk])
 
-    def rope_overhead():
-        q.grad = k.grad = None
-        torch.autograd.backward([q * 1, k * 1], [dq, dk])
+        out["rope_q32_k8_8192x128_fwd_bwd"] = _hbm(_kernel_ms(rope, flush, iters or 20, 5), 339.74e6, peaks)
+        del q, k, dq, dk
 
-    ms = _median_ms(rope, flush) - _median_ms(rope_overhead, flush)
-    byts = 339.74e6
-    out["rope_q32_k8_8192x128_fwd_bwd"] = {"ms": ms, "GBps": byts / ms / 1e6, "frac_of_hbm_peak": byts / ms / 1e6 / peaks["hbm_gbs"],
-                                            "note": "time of the copies that protect the leaf inputs subtracted"}
+    if want("mlp"):
+        xm = torch.randn(8192, 4096, device=dev, dtype=bf).requires_grad_(True)
+        wg = (torch.randn(12288, 4096, device=dev) * 0.02).to(bf).requires_grad_(True)
+        wu = (torch.randn(12288, 4096, device=dev) * 0.02).to(bf).requires_grad_(True)
+        wd = (torch.randn(4096, 12288, device=dev) * 0.02).to(bf).requires_grad_(True)
+        dym = torch.randn(8192, 4096, device=dev, dtype=bf)
 
-    xm = torch.randn(8192, 4096, device=dev, dtype=bf).requires_grad_(True)
-    wg = (torch.randn(12288, 4096, device=dev) * 0.02).to(bf).requires_grad_(True)
-    wu = (torch.randn(12288, 4096, device=dev) * 0.02).to(bf).requires_grad_(True)
-    wd = (torch.randn(4096, 12288, device=dev) * 0.02).to(bf).requires_grad_(True)
-    dym = torch.randn(8192, 4096, device=dev, dtype=bf)
+        def mlp():
+            xm.grad = wg.grad = wu.grad = wd.grad = None
+            SwiGLUMLPFunction.apply(xm, wg, wu, wd).backward(dym)
 
-    def mlp():
-        xm.grad = wg.grad = wu.grad = wd.grad = None
-        SwiGLUMLPFunction.apply(xm, wg, wu, wd).backward(dym)
+        out["swiglu_mlp_8192x4096x12288_fwd_bwd"] = _tensor(_kernel_ms(mlp, flush, iters or 10, 3), 7.4217e12, peaks)
+        del xm, wg, wu, wd, dym
 
-    ms = _median_ms(mlp, flush, iters=10, warm=3)
-    fl = 7.4217e12
-    out["swiglu_mlp_8192x4096x12288_fwd_bwd"] = {"ms": ms, "TFLOPs": fl / ms / 1e9, "frac_of_bf16_burst": fl / ms / 1e9 / peaks["bf16_tflops"],
-                                                  "frac_of_bf16_sustained": fl / ms / 1e9 / peaks["bf16_tflops_sustained"]}
-    del xm, wg, wu, wd, dym
+    if want("lce"):
+        hid = torch.randn(16384, 4096, device=dev, dtype=bf).requires_grad_(True)
+        wl = (torch.randn(151936, 4096, device=dev, dtype=bf) * 0.02).requires_grad_(True)
+        lab = torch.randint(0, 151936, (16384,), device=dev)
+        lab[torch.rand(16384, device=dev) < 0.05] = -100
 
-    hid = torch.randn(16384, 4096, device=dev, dtype=bf).requires_grad_(True)
-    wl = (torch.randn(151936, 4096, device=dev, dtype=bf) * 0.02).requires_grad_(True)
-    lab = torch.randint(0, 151936, (16384,), device=dev)
-    lab[torch.rand(16384, device=dev) < 0.05] = -100
+        def lce():
+            hid.grad = wl.grad = None
+            fused_linear_cross_entropy(hid, wl, lab).backward()
 
-    def lce():
-        hid.grad = wl.grad = None
-        fused_linear_cross_entropy(hid, wl, lab).backward()
-
-    ms = _median_ms(lce, flush, iters=5, warm=2)
-    fl = 61.1775e12
-    out["fused_linear_ce_16384x4096x151936_fwd_bwd"] = {"ms": ms, "TFLOPs": fl / ms / 1e9, "frac_of_bf16_burst": fl / ms / 1e9 / peaks["bf16_tflops"],
-                                                         "frac_of_bf16_sustained": fl / ms / 1e9 / peaks["bf16_tflops_sustained"]}
+        out["fused_linear_ce_16384x4096x151936_fwd_bwd"] = _tensor(_kernel_ms(lce, flush, iters or 5, 2), 61.1775e12, peaks)
     return out
 
 
@@ -323,6 +330,9 @@ def main():
     ap.add_argument("--seq", type=int, default=SEQ_LEN)
     ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
     ap.add_argument("--no-per-op", action="store_true")
+    ap.add_argument("--only-op", default=None, choices=["rmsnorm", "rope", "mlp", "lce"],
+                    help="run just this op's forward+backward micro-benchmark (small case for profilers)")
+    ap.add_argument("--op-iters", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -347,6 +357,14 @@ def main():
     import bastile_b200
     from bastile_b200 import _lib
     from transformers import Qwen3Config, Qwen3ForCausalLM
+
+    if args.only_op:
+        peaks, peak_kind = load_peaks()
+        res = per_op_bench(peaks, only=args.only_op, iters=args.op_iters)
+        _lib.check_status(dev, "per-op benchmark")
+        if rank == 0:
+            print(json.dumps({"per_op": res, "peaks": peaks, "peak_kind": peak_kind}), flush=True)
+        return
 
     applied = bastile_b200.apply()
     assert applied == ["rms_norm_qwen3", "rope_qwen3", "swiglu_qwen3", "fused_linear_cross_entropy"], applied

@@ -131,6 +131,14 @@ struct Cvt<float> {
   __device__ __forceinline__ static float from_f(float x) { return x; }
 };
 
+// Tells the compiler that a packed 16-byte vector "changed": values unpacked from it before
+// this point cannot be kept alive in registers across it and are recomputed from the packed
+// form instead.  Costs nothing at run time; keeps two-pass row kernels at ~1 register per
+// two elements instead of three.
+__device__ __forceinline__ void forget_unpacked(uint4& v) {
+  asm volatile("" : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w));
+}
+
 // Sum over the G consecutive lanes (G a power of two <= 32) that hold one row.
 template <int G>
 __device__ __forceinline__ float group_sum(float v) {
@@ -140,5 +148,20 @@ __device__ __forceinline__ float group_sum(float v) {
 }
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// RMSNorm backward scratch: K private copies of the N fp32 column sums (CTA b adds into
+// copy b % K, which divides the same-address atomic traffic by K) followed by one arrival
+// counter.  K * N stays within 16384 words.
+__host__ __device__ inline int dw_copies(int64_t N) {
+  const int64_t k = 16384 / (N > 0 ? N : 1);
+  return k < 1 ? 1 : (k > 8 ? 8 : static_cast<int>(k));
+}
+
+// Adds 8 (or 4) consecutive fp32 values with 16-byte vector reductions.
+__device__ __forceinline__ void red_add_v4(float* dst, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c),
+               "f"(d)
+               : "memory");
+}
 
 }  // namespace bt

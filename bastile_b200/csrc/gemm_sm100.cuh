@@ -1,9 +1,9 @@
 // Persistent, warp-specialised tcgen05 GEMM for sm_100a with pluggable epilogues.
 //
-//   CTA tile 128 x 256 x 64 (16-bit operands), one CTA per SM, 192 threads:
+//   CTA tile 128 x 256 x 64 (16-bit operands), one CTA per SM, 320 threads:
 //     warp 0      TMA producer   - one lane issues the tile loads of a 4-stage ring
 //     warp 1      MMA issuer     - owns the 512 TMEM columns, one lane issues tcgen05.mma
-//     warps 2..5  epilogue       - each owns one 32-lane quarter of TMEM
+//     warps 2..9  epilogue       - two per 32-lane quarter of TMEM, half of the columns each
 //   The fp32 accumulator (128 lanes x 256 columns) is double-buffered in tensor
 //   memory, so the epilogue of tile i overlaps the main loop of tile i+1.
 //
@@ -35,7 +35,8 @@ constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int kStages = 4;
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;  // two warps per 32-lane TMEM quarter, each takes half of the columns
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr int kABytes = BM * BK * 2;
 constexpr int kBBytes = BN * BK * 2;
 constexpr int kStageBytes = kABytes + kBBytes;
@@ -142,11 +143,12 @@ __device__ __forceinline__ void load_row32(const T* src, float (&v)[32], int val
 
 // ------------------------------------------------------------------ epilogues
 template <typename T>
-__device__ __forceinline__ void epi_plain(const Params& p, uint32_t taddr, int64_t row, int n0) {
+__device__ __forceinline__ void epi_plain(const Params& p, uint32_t taddr, int64_t row, int n0,
+                                          int half) {
   const float alpha = p.alpha != nullptr ? __ldg(p.alpha) : 1.0f;
   const bool row_ok = row < p.M;
 #pragma unroll 1
-  for (int c = 0; c < BN / 32; ++c) {
+  for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
     float v[32];
     ptx::tmem_ld_32cols(taddr + c * 32, v);
     const int col0 = n0 + c * 32;
@@ -182,10 +184,10 @@ __device__ __forceinline__ void epi_plain(const Params& p, uint32_t taddr, int64
 // Accumulator columns [0,128) = gate, [128,256) = up for output columns n0 .. n0+127.
 template <typename T>
 __device__ __forceinline__ void epi_swiglu_fwd(const Params& p, uint32_t taddr, int64_t row,
-                                               int n0) {
+                                               int n0, int half) {
   const bool row_ok = row < p.M;
 #pragma unroll 1
-  for (int c = 0; c < (BN / 2) / 32; ++c) {
+  for (int c = half * (BN / 128); c < (half + 1) * (BN / 128); ++c) {
     float g[32], u[32];
     ptx::tmem_ld_32cols(taddr + c * 32, g);
     ptx::tmem_ld_32cols(taddr + BN / 2 + c * 32, u);
@@ -211,10 +213,10 @@ __device__ __forceinline__ void epi_swiglu_fwd(const Params& p, uint32_t taddr, 
 // Accumulator = dh tile; reads saved gate/up, writes dgate (p.out) and dup (p.h).
 template <typename T>
 __device__ __forceinline__ void epi_swiglu_bwd(const Params& p, uint32_t taddr, int64_t row,
-                                               int n0) {
+                                               int n0, int half) {
   const bool row_ok = row < p.M;
 #pragma unroll 1
-  for (int c = 0; c < BN / 32; ++c) {
+  for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
     float d[32];
     ptx::tmem_ld_32cols(taddr + c * 32, d);
     const int col0 = n0 + c * 32;
@@ -227,7 +229,8 @@ __device__ __forceinline__ void epi_swiglu_bwd(const Params& p, uint32_t taddr, 
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const float dh = round_through<T>(d[j]);
-        const float sg = 1.0f / (1.0f + expf(-g[j]));
+        // results are rounded to 16 bits: the approximate exp / reciprocal are far inside that
+        const float sg = __fdividef(1.0f, 1.0f + __expf(-g[j]));
         d[j] = dh * (sg * (1.0f + g[j] * (1.0f - sg))) * u[j];  // dgate
         g[j] = dh * (g[j] * sg);                                 // dup
       }
@@ -241,7 +244,7 @@ __device__ __forceinline__ void epi_swiglu_bwd(const Params& p, uint32_t taddr, 
 // the logits themselves rounded to T.
 template <typename T>
 __device__ __forceinline__ void epi_lce(const Params& p, uint32_t taddr, int64_t row, int n0,
-                                        int n_idx) {
+                                        int n_idx, int half) {
   const bool row_ok = row < p.M;
   constexpr float kNegBig = -1e30f;
   int tgt_col = -1;  // column of the label inside this tile, if it is here
@@ -250,11 +253,12 @@ __device__ __forceinline__ void epi_lce(const Params& p, uint32_t taddr, int64_t
     const int64_t label = p.labels[row];
     const int64_t loc = label - p.v_offset;
     owned = (label != p.ignore_index) && loc >= 0 && loc < p.N;
-    if (owned && loc >= n0 && loc < n0 + BN) tgt_col = static_cast<int>(loc - n0);
+    if (owned && loc >= n0 + half * (BN / 2) && loc < n0 + (half + 1) * (BN / 2))
+      tgt_col = static_cast<int>(loc - n0);
   }
   float mx = kNegBig, sum = 0.f, tgt = 0.f;
 #pragma unroll 1
-  for (int c = 0; c < BN / 32; ++c) {
+  for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
     float v[32];
     ptx::tmem_ld_32cols(taddr + c * 32, v);
     const int col0 = n0 + c * 32;
@@ -283,11 +287,12 @@ __device__ __forceinline__ void epi_lce(const Params& p, uint32_t taddr, int64_t
     }
   }
   if (row_ok) {
-    *reinterpret_cast<float2*>(p.tile_stats + (row * p.n_vtiles + n_idx) * 2) =
+    // one statistics entry per 128 columns (a half tile); an all-padding half stays (-1e30, 0)
+    *reinterpret_cast<float2*>(p.tile_stats + (row * p.n_vtiles + n_idx * 2 + half) * 2) =
         make_float2(mx, sum);
     if (tgt_col >= 0)
       p.tgt_logit[row] = tgt;
-    else if (n_idx == 0 && !owned)
+    else if (n_idx == 0 && half == 0 && !owned)
       p.tgt_logit[row] = 0.f;
   }
 }
@@ -318,7 +323,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     }
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&tfull[i], 1);
-      ptx::mbar_init(&tempty[i], 128);
+      ptx::mbar_init(&tempty[i], 32 * kEpiWarps);
     }
     *cta_abort = 0;
     ptx::fence_mbar_init();
@@ -432,6 +437,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    const int half = (warp - 2) >> 2;  // which half of the accumulator columns
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
@@ -442,10 +448,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
       const uint32_t taddr =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
       const int64_t row = static_cast<int64_t>(m_idx) * BM + quarter * 32 + lane;
-      if (EPI == EPI_PLAIN) epi_plain<T>(p, taddr, row, n_idx * BN);
-      if (EPI == EPI_SWIGLU_FWD) epi_swiglu_fwd<T>(p, taddr, row, n_idx * (BN / 2));
-      if (EPI == EPI_SWIGLU_BWD) epi_swiglu_bwd<T>(p, taddr, row, n_idx * BN);
-      if (EPI == EPI_LCE) epi_lce<T>(p, taddr, row, n_idx * BN, n_idx);
+      if (EPI == EPI_PLAIN) epi_plain<T>(p, taddr, row, n_idx * BN, half);
+      if (EPI == EPI_SWIGLU_FWD) epi_swiglu_fwd<T>(p, taddr, row, n_idx * (BN / 2), half);
+      if (EPI == EPI_SWIGLU_BWD) epi_swiglu_bwd<T>(p, taddr, row, n_idx * BN, half);
+      if (EPI == EPI_LCE) epi_lce<T>(p, taddr, row, n_idx * BN, n_idx, half);
       ptx::tcgen05_fence_before_sync();
       ptx::mbar_arrive(&tempty[acc]);
       acc ^= 1;

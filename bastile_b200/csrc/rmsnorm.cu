@@ -18,6 +18,7 @@
 #include <mutex>
 
 #include "bt_common.cuh"
+#include "rmsnorm_staged.cuh"
 
 namespace bt {
 namespace {
@@ -26,7 +27,7 @@ constexpr int kThreads = 256;
 
 // ------------------------------------------------------------------ forward
 template <typename T, int VPT, int LPR, int RPI>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, (VPT >= 16 ? 2 : (VPT >= 8 ? 3 : 4)))
 rms_fwd_rows(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
              float* __restrict__ rstd, int64_t M, int N, int64_t ld_x, int64_t ld_y, float eps) {
   constexpr int E = Cvt<T>::N;
@@ -63,6 +64,8 @@ rms_fwd_rows(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y
       }
       ss = group_sum<LPR>(ss);
       const float rs = rsqrtf(ss * inv_n + eps);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) forget_unpacked(xv[r][i]);
       if (row < M) {
         if (lane == 0) rstd[row] = rs;
 #pragma unroll
@@ -115,31 +118,36 @@ rms_fwd_generic(const T* __restrict__ x, const T* __restrict__ w, T* __restrict_
 }
 
 // ----------------------------------------------------------------- backward
-// Scratch layout: float acc[N] followed by one uint32 arrival counter.
+// Scratch layout: dw_copies(N) x float acc[N], then one uint32 arrival counter.
 template <typename T>
-__device__ __forceinline__ void dw_finalize(float* __restrict__ ws, T* __restrict__ dw, int N) {
+__device__ __forceinline__ void dw_finalize(float* __restrict__ ws, T* __restrict__ dw, int N,
+                                            unsigned int total_ctas, int tid, int nthreads) {
   __shared__ bool s_last;
+  const int K = dw_copies(N);
+  unsigned int* counter = reinterpret_cast<unsigned int*>(ws + static_cast<int64_t>(K) * N);
   __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) {
-    unsigned int* counter = reinterpret_cast<unsigned int*>(ws + N);
+  if (tid == 0) {
     const unsigned int ticket = atomicAdd(counter, 1u);
-    s_last = (ticket == gridDim.x - 1);
+    s_last = (ticket == total_ctas - 1);
   }
   __syncthreads();
   if (s_last) {
     __threadfence();
-    for (int c = threadIdx.x; c < N; c += blockDim.x) {
-      const float v = __ldcg(ws + c);
+    for (int c = tid; c < N; c += nthreads) {
+      float v = 0.f;
+      for (int k = 0; k < K; ++k) {
+        v += __ldcg(ws + static_cast<int64_t>(k) * N + c);
+        ws[static_cast<int64_t>(k) * N + c] = 0.f;
+      }
       dw[c] = Cvt<T>::from_f(v);
-      ws[c] = 0.f;
     }
-    if (threadIdx.x == 0) *reinterpret_cast<unsigned int*>(ws + N) = 0u;
+    if (tid == 0) *counter = 0u;
   }
 }
 
 template <typename T, int VPT, int LPR, int RPI>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 3)
 rms_bwd_rows(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
              const float* __restrict__ rstd, T* __restrict__ dx, T* __restrict__ dw,
              float* __restrict__ ws, int64_t M, int N, int64_t ld_dy, int64_t ld_x,
@@ -187,7 +195,6 @@ rms_bwd_rows(const T* __restrict__ dy, const T* __restrict__ x, const T* __restr
 #pragma unroll
     for (int r = 0; r < RPI; ++r) {
       const int64_t row = base + r * kGroups + group;
-      float xh[VPT][E], wdy[VPT][E];
       float dot = 0.f;
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
@@ -196,21 +203,28 @@ rms_bwd_rows(const T* __restrict__ dy, const T* __restrict__ x, const T* __restr
         Cvt<T>::unpack(gv[r][i], gf);
 #pragma unroll
         for (int e = 0; e < E; ++e) {
-          xh[i][e] = xf[e] * rs[r];
-          wdy[i][e] = gf[e] * wf[i][e];
-          dot = fmaf(xh[i][e], wdy[i][e], dot);
-          acc[i][e] = fmaf(gf[e], xh[i][e], acc[i][e]);
+          const float xh = xf[e] * rs[r];
+          dot = fmaf(xh, gf[e] * wf[i][e], dot);
+          acc[i][e] = fmaf(gf[e], xh, acc[i][e]);
         }
       }
       dot = group_sum<LPR>(dot) * inv_n;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        forget_unpacked(xv[r][i]);
+        forget_unpacked(gv[r][i]);
+      }
       if (row < M) {
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
           const int v = lane + i * LPR;
           if (v < nv) {
-            float o[E];
+            float xf[E], gf[E], o[E];
+            Cvt<T>::unpack(xv[r][i], xf);
+            Cvt<T>::unpack(gv[r][i], gf);
 #pragma unroll
-            for (int e = 0; e < E; ++e) o[e] = (wdy[i][e] - xh[i][e] * dot) * rs[r];
+            for (int e = 0; e < E; ++e)
+              o[e] = (gf[e] * wf[i][e] - xf[e] * rs[r] * dot) * rs[r];
             st_global_v4(dx + row * ld_dx + static_cast<int64_t>(v) * E, Cvt<T>::pack(o));
           }
         }
@@ -228,13 +242,14 @@ rms_bwd_rows(const T* __restrict__ dy, const T* __restrict__ x, const T* __restr
     }
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < N; c += kThreads) atomicAdd(ws + c, s_dw[c]);
-  dw_finalize<T>(ws, dw, N);
+  float* my_ws = ws + static_cast<int64_t>(blockIdx.x % dw_copies(N)) * N;
+  for (int c = threadIdx.x; c < N; c += kThreads) atomicAdd(my_ws + c, s_dw[c]);
+  dw_finalize<T>(ws, dw, N, gridDim.x, threadIdx.x, kThreads);
 }
 
 // Wide rows: one row is spread over the whole CTA, R rows per iteration.
 template <typename T, int VPT, int R>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
 rms_bwd_block(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
               const float* __restrict__ rstd, T* __restrict__ dx, T* __restrict__ dw,
               float* __restrict__ ws, int64_t M, int N, int64_t ld_dy, int64_t ld_x,
@@ -302,6 +317,11 @@ rms_bwd_block(const T* __restrict__ dy, const T* __restrict__ x, const T* __rest
 #pragma unroll
       for (int k = 0; k < kWarps; ++k) d += s_red[buf][k][r];
       dot[r] = d * inv_n;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        forget_unpacked(xv[r][i]);
+        forget_unpacked(gv[r][i]);
+      }
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -330,10 +350,12 @@ rms_bwd_block(const T* __restrict__ dy, const T* __restrict__ x, const T* __rest
     const int v = threadIdx.x + i * kThreads;
     if (v < nv) {
 #pragma unroll
-      for (int e = 0; e < E; ++e) atomicAdd(ws + v * E + e, acc[i][e]);
+      float* d = ws + static_cast<int64_t>(blockIdx.x % dw_copies(N)) * N + v * E;
+#pragma unroll
+      for (int e = 0; e < E; e += 4) red_add_v4(d + e, acc[i][e], acc[i][e + 1], acc[i][e + 2], acc[i][e + 3]);
     }
   }
-  dw_finalize<T>(ws, dw, N);
+  dw_finalize<T>(ws, dw, N, gridDim.x, threadIdx.x, kThreads);
 }
 
 // Generic backward, part 1: dx, one CTA per row (scalar).
@@ -381,26 +403,9 @@ __global__ void rms_bwd_dw_generic(const T* __restrict__ dy, const T* __restrict
     for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < M;
          row += static_cast<int64_t>(gridDim.y) * blockDim.y)
       a = fmaf(Cvt<T>::to_f(dy[row * ld_dy + c]), Cvt<T>::to_f(x[row * ld_x + c]) * rstd[row], a);
-    atomicAdd(ws + c, a);
+    atomicAdd(ws + static_cast<int64_t>(blockIdx.y % dw_copies(N)) * N + c, a);
   }
-  // dw_finalize counts CTAs through gridDim.x only: fold the 2-D grid into it.
-  __shared__ bool s_last;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0 && threadIdx.y == 0) {
-    unsigned int* counter = reinterpret_cast<unsigned int*>(ws + N);
-    const unsigned int ticket = atomicAdd(counter, 1u);
-    s_last = (ticket == gridDim.x * gridDim.y - 1);
-  }
-  __syncthreads();
-  if (s_last) {
-    __threadfence();
-    for (int i = threadIdx.y * 32 + threadIdx.x; i < N; i += 32 * blockDim.y) {
-      dw[i] = Cvt<T>::from_f(__ldcg(ws + i));
-      ws[i] = 0.f;
-    }
-    if (threadIdx.x == 0 && threadIdx.y == 0) *reinterpret_cast<unsigned int*>(ws + N) = 0u;
-  }
+  dw_finalize<T>(ws, dw, N, gridDim.x * gridDim.y, threadIdx.y * 32 + threadIdx.x, 32 * blockDim.y);
 }
 
 // ------------------------------------------------------------ host dispatch
@@ -442,8 +447,29 @@ int fwd_t(const void* x, const void* w, void* y, float* rstd, int64_t M, int64_t
     BT_CHECK_LAUNCH("rms_fwd_generic");
     return BT_OK;
   }
+  if (N / E > 128 && N / E <= 4 * staged::kThreads) {
+    const int64_t nv = N / E;
+    const int vpt = nv <= staged::kThreads ? 1 : (nv <= 2 * staged::kThreads ? 2 : 4);
+#define BT_FWDS(V, R)                                                                            \
+  if (vpt == V) {                                                                                \
+    static const cudaError_t attr = cudaFuncSetAttribute(                                        \
+        staged::rms_fwd_staged<T, V, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+    (void)attr;                                                                                  \
+    const size_t smem = staged::smem_bytes(static_cast<int>(N), sizeof(T), R, false);            \
+    const int grid = grid_for(ceil_div(M, R), 2);                                                \
+    staged::rms_fwd_staged<T, V, R><<<grid, staged::kThreads, smem, s>>>(                        \
+        xp, wp, yp, rstd, M, static_cast<int>(N), ld_x, ld_y, eps);                              \
+    BT_CHECK_LAUNCH("rms_fwd_staged");                                                           \
+    return BT_OK;                                                                                \
+  }
+    BT_FWDS(1, 8)
+    BT_FWDS(2, 4)
+    BT_FWDS(4, 2)
+#undef BT_FWDS
+  }
   const int64_t rows_per_iter = static_cast<int64_t>(kThreads / c.lpr) * c.rpi;
-  const int grid = grid_for(ceil_div(M, rows_per_iter), c.vpt >= 16 ? 2 : 4);
+  // many short-lived CTAs: the hardware scheduler evens out the tail better than a fixed split
+  const int grid = grid_for(ceil_div(M, rows_per_iter), 32);
 #define BT_FWD(L, V, R)                                                                         \
   if (c.lpr == L && c.vpt == V) {                                                               \
     rms_fwd_rows<T, V, L, R><<<grid, kThreads, 0, s>>>(xp, wp, yp, rstd, M, static_cast<int>(N), \
@@ -478,6 +504,25 @@ int bwd_t(const void* dy, const void* x, const void* w, const float* rstd, void*
                       aligned16(x) && aligned16(w) && aligned16(dy) && aligned16(dx);
   const int64_t nv = vec_ok ? N / E : 0;
   RowCfg c{};
+  if (vec_ok && nv > 128 && nv <= 4 * staged::kThreads) {
+    const int vpt = nv <= staged::kThreads ? 1 : (nv <= 2 * staged::kThreads ? 2 : 4);
+#define BT_BWDS(V, R)                                                                            \
+  if (vpt == V) {                                                                                \
+    static const cudaError_t attr = cudaFuncSetAttribute(                                        \
+        staged::rms_bwd_staged<T, V, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+    (void)attr;                                                                                  \
+    const size_t smem = staged::smem_bytes(static_cast<int>(N), sizeof(T), R, true);             \
+    const int grid = grid_for(ceil_div(M, R), 2);                                                \
+    staged::rms_bwd_staged<T, V, R><<<grid, staged::kThreads, smem, s>>>(                        \
+        gp, xp, wp, rstd, dxp, dwp, wsp, M, static_cast<int>(N), ld_dy, ld_x, ld_dx);            \
+    BT_CHECK_LAUNCH("rms_bwd_staged");                                                           \
+    return BT_OK;                                                                                \
+  }
+    BT_BWDS(1, 4)
+    BT_BWDS(2, 2)
+    BT_BWDS(4, 1)
+#undef BT_BWDS
+  }
   if (vec_ok && pick_rows(nv, 4, &c)) {
     const int64_t rows_per_iter = static_cast<int64_t>(kThreads / c.lpr) * c.rpi;
     const int grid = grid_for(ceil_div(M, rows_per_iter), 4);
@@ -545,7 +590,19 @@ extern "C" int bt_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd
   return BT_ERR_ARG;
 }
 
-extern "C" int64_t bt_rmsnorm_bwd_ws_bytes(int64_t N) { return (N + 1) * 4; }
+extern "C" int64_t bt_rmsnorm_bwd_ws_bytes(int64_t N) {
+  return (static_cast<int64_t>(bt::dw_copies(N)) * N + 1) * 4;
+}
+
+extern "C" int bt_device_wait_errors(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, bt::staged::g_wait_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(bt::staged::g_wait_error, &zero, sizeof(int));
+  }
+  return v;
+}
 
 extern "C" int bt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
                               void* dx, void* dw, void* ws, int64_t M, int64_t N, int64_t ld_dy,
@@ -662,7 +719,7 @@ extern "C" int bt_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void*
   if (int rc = noalloc_scratch(&scratch)) return rc;
   // The array keeps whatever the previous call (or a call that was cut short) left in
   // it; the kernels need zeros in the N sums and in the counter.
-  cudaError_t e = cudaMemsetAsync(scratch, 0, static_cast<size_t>(N + 1) * sizeof(float),
+  cudaError_t e = cudaMemsetAsync(scratch, 0, static_cast<size_t>(bt_rmsnorm_bwd_ws_bytes(N)),
                                   static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) {
     set_error("rmsnorm_bwd_noalloc: clearing the scratch failed: %s", cudaGetErrorString(e));

@@ -167,7 +167,10 @@ extern "C" int bt_mlp_bwd(const void* dy, const void* x, const void* wg, const v
   return BT_OK;
 }
 
-extern "C" int64_t bt_lce_num_vtiles(int64_t V) { return (V + bt::gemm::BN - 1) / bt::gemm::BN; }
+// Two statistics entries per 256-column tile (one per 128-column half).
+extern "C" int64_t bt_lce_num_vtiles(int64_t V) {
+  return 2 * ((V + bt::gemm::BN - 1) / bt::gemm::BN);
+}
 
 extern "C" int bt_lce_logits_stats(const void* hidden, const void* W, const int64_t* labels,
                                    void* logits, float* tile_stats, float* tgt_logit, int64_t rows,

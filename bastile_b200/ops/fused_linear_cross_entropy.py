@@ -35,6 +35,14 @@ from .. import _lib
 
 _GEMM_DTYPES = (torch.bfloat16, torch.float16)
 
+# With the default chunk_size the op may work on up to this many rows at a time as long as
+# the 16-bit logits chunk stays under AUTO_CHUNK_BYTES: 8192 rows x 4096 hidden is a whole
+# number of waves of 128x256 tiles on 148 SMs for the dx GEMM, and fewer chunks mean fewer
+# read-modify-write passes over the fp32 dW accumulator.  An explicit chunk_size is obeyed.
+DEFAULT_CHUNK = 4096
+AUTO_CHUNK_ROWS = 8192
+AUTO_CHUNK_BYTES = 3 << 30
+
 
 def merge_shard_stats(gathered: Tensor) -> Tensor:
     """[n_shards, rows, 3] (max, sum-exp, target logit) -> [rows, 3] for the full vocabulary."""
@@ -78,9 +86,12 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         if labels.numel() != bt:
             raise ValueError("fused_linear_cross_entropy: target does not match hidden_states")
 
-        chunk = max(1, min(int(chunk_size), bt)) if bt > 0 else 1
-        n_chunks = (bt + chunk - 1) // chunk if bt > 0 else 0
         ld_logits = (vloc + 7) // 8 * 8
+        rows_wanted = int(chunk_size)
+        if rows_wanted == DEFAULT_CHUNK and AUTO_CHUNK_ROWS * ld_logits * 2 <= AUTO_CHUNK_BYTES:
+            rows_wanted = AUTO_CHUNK_ROWS
+        chunk = max(1, min(rows_wanted, bt)) if bt > 0 else 1
+        n_chunks = (bt + chunk - 1) // chunk if bt > 0 else 0
         n_vt = int(lib.bt_lce_num_vtiles(vloc))
         stream = _lib.stream_ptr(dev)
         st = _lib.status_word(dev)

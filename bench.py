@@ -225,6 +225,8 @@ def _kernel_ms(fn, flush, iters, warm):
     per_iter = []
     for _ in range(iters):
         flush.zero_()  # 256 MiB > 126 MB L2
+        torch.cuda._sleep(600_000)  # keep the GPU busy while the host queues the op, so that the
+        # events bracket kernels that are already waiting in the stream (no host gaps inside)
         _lib.instr.reset(enabled=True)
         fn()
         per_iter.append(sum(ms for _, ms in _lib.instr.elapsed_ms().values()))

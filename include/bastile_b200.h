@@ -45,6 +45,11 @@ const char* bt_last_error(void);
 /* Number of SMs of the current device (src/bastile/ops/utils.py:8-13). */
 int bt_sm_count(void);
 
+/* Synchronising read-and-clear of the device word in which the RMSNorm kernels
+ * record a bulk-copy wait that ran out (0 = none, -1 = the read failed).  For
+ * tests and debugging; no reference counterpart. */
+int bt_device_wait_errors(void);
+
 /* ------------------------------------------------------------------ RMSNorm */
 
 /* y[m,:] = x[m,:] * rsqrt(mean(x[m,:]^2) + eps) * w, rounded once to `dtype`;
@@ -176,7 +181,7 @@ int bt_mlp_bwd(const void* dy, const void* x, const void* wg, const void* wu,
 
 /* Step 1 of the fused loss for one chunk of rows and one vocabulary shard:
  * logits = hidden W^T on the tensor cores; the epilogue keeps, per row and per
- * 256-column tile, (max, sum exp(logit-max)) and the target's logit, and writes
+ * 128-column block, (max, sum exp(logit-max)) and the target's logit, and writes
  * the logits once as 16-bit values into `logits` [rows, ld_logits] (the chunk
  * buffer, never [tokens, V]).  `tile_stats` has rows * bt_lce_num_vtiles(V)
  * float2 entries, `tgt_logit` one float per row (0 when the label is ignored or

@@ -119,33 +119,6 @@ rms_fwd_generic(const T* __restrict__ x, const T* __restrict__ w, T* __restrict_
 
 // ----------------------------------------------------------------- backward
 // Scratch layout: dw_copies(N) x float acc[N], then one uint32 arrival counter.
-template <typename T>
-__device__ __forceinline__ void dw_finalize(float* __restrict__ ws, T* __restrict__ dw, int N,
-                                            unsigned int total_ctas, int tid, int nthreads) {
-  __shared__ bool s_last;
-  const int K = dw_copies(N);
-  unsigned int* counter = reinterpret_cast<unsigned int*>(ws + static_cast<int64_t>(K) * N);
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const unsigned int ticket = atomicAdd(counter, 1u);
-    s_last = (ticket == total_ctas - 1);
-  }
-  __syncthreads();
-  if (s_last) {
-    __threadfence();
-    for (int c = tid; c < N; c += nthreads) {
-      float v = 0.f;
-      for (int k = 0; k < K; ++k) {
-        v += __ldcg(ws + static_cast<int64_t>(k) * N + c);
-        ws[static_cast<int64_t>(k) * N + c] = 0.f;
-      }
-      dw[c] = Cvt<T>::from_f(v);
-    }
-    if (tid == 0) *counter = 0u;
-  }
-}
-
 template <typename T, int VPT, int LPR, int RPI>
 __global__ void __launch_bounds__(kThreads, 3)
 rms_bwd_rows(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,

@@ -468,6 +468,194 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
   }
 }
 
+// ------------------------------------------------------- kernel, CTA pairs
+// Same roles and epilogues, but two CTAs of a 2-CTA cluster work on one 256 x 256 tile with
+// tcgen05.mma.cta_group::2: each CTA stages its own 128 rows of A and its own 128 columns
+// of B (32 KB per stage instead of 48 KB, so the ring is 6 deep), the leader CTA's MMA lane
+// issues for both, and each CTA's epilogue drains its own 128 accumulator rows.
+//   full[s]    lives in the leader: armed by the leader's producer with the bytes of BOTH
+//              CTAs; each CTA's tile loads credit it (plain loads, no multicast).
+//   empty[s], tfull[a]  live in both CTAs; the leader's commit arrives on both copies.
+//   tempty[a]  lives in the leader; epilogue threads of both CTAs arrive on it.
+constexpr int kStages2 = 6;
+constexpr int kStageBytes2 = kABytes + kBBytes / 2;
+constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + 1024 + 256;
+
+template <int EPI, typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
+                 const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
+                 const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages2 * kStageBytes2);
+  uint64_t* empty = full + kStages2;
+  uint64_t* tfull = empty + kStages2;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();  // 0 = leader
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages2; ++i) {
+      ptx::mbar_init(&full[i], 1);
+      ptx::mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&tfull[i], 1);
+      ptx::mbar_init(&tempty[i], 2 * 32 * kEpiWarps);
+    }
+    *cta_abort = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tmA0);
+    ptx::prefetch_tensormap(&tmB0);
+    if (p.K1 > 0 || p.dual_b) ptx::prefetch_tensormap(&tmB1);
+    if (p.K1 > 0) ptx::prefetch_tensormap(&tmA1);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish_alloc_permit_pair();
+  }
+  ptx::tcgen05_fence_before_sync();
+  __syncthreads();
+  ptx::cluster_sync_all();  // the peer's barriers exist before anything signals them
+  ptx::tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int nkb0 = (p.K0 + BK - 1) / BK;
+  const int nkb1 = (p.K1 + BK - 1) / BK;
+  const int nkb = nkb0 + nkb1;
+  const int pair = blockIdx.x >> 1;
+  const int npairs = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < p.num_tiles; tile += npairs) {
+        int m_idx, n_idx;
+        tile_coords(p, tile, &m_idx, &n_idx);
+        const int m0 = m_idx * (2 * BM) + static_cast<int>(rank) * BM;
+        const int n0 = p.dual_b ? n_idx * (BN / 2) : n_idx * BN + static_cast<int>(rank) * (BN / 2);
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!ptx::mbar_wait(&empty[stage], phase ^ 1u, cta_abort, p.status, ST_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          if (leader) ptx::mbar_arrive_expect_tx(&full[stage], 2 * kStageBytes2);
+          const bool second = kb >= nkb0;
+          const int k0 = (second ? kb - nkb0 : kb) * BK;
+          const CUtensorMap* ta = second ? &tmA1 : &tmA0;
+          const CUtensorMap* tb = p.dual_b ? (rank ? &tmB1 : &tmB0) : (second ? &tmB1 : &tmB0);
+          uint8_t* sa = smem + stage * kStageBytes2;
+          uint8_t* sb = sa + kABytes;
+          if (p.a_kmajor) {
+            ptx::tma_load_2d_pair(sa, ta, k0, m0, &full[stage]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              ptx::tma_load_2d_pair(sa + j * kBoxBytesMN, ta, m0 + j * 64, k0, &full[stage]);
+          }
+          if (p.b_kmajor) {
+            ptx::tma_load_2d_pair(sb, tb, k0, n0, &full[stage]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j)
+              ptx::tma_load_2d_pair(sb + j * kBoxBytesMN, tb, n0 + j * 64, k0, &full[stage]);
+          }
+          if (++stage == kStages2) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok || *cta_abort != 0) {
+        const uint64_t t0 = ptx::globaltimer_ns();
+        while (ptx::globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------- MMA issuer (leader only)
+    if (lane == 0 && leader) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < p.num_tiles; tile += npairs) {
+        if (!ptx::mbar_wait(&tempty[acc], acc_phase ^ 1u, cta_abort, p.status, ST_MMA_ACC)) break;
+        ptx::tcgen05_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!ptx::mbar_wait(&full[stage], phase, cta_abort, p.status, ST_MMA_FULL)) {
+            ok = false;
+            break;
+          }
+          ptx::tcgen05_fence_after_sync();
+          const uint32_t a_addr = ptx::smem_u32(smem + stage * kStageBytes2);
+          const uint64_t a_desc = ptx::smem_desc(p.a_desc_hi, a_addr);
+          const uint64_t b_desc = ptx::smem_desc(p.b_desc_hi, a_addr + kABytes);
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk)
+            ptx::umma_f16_pair(d_tmem, a_desc + static_cast<uint64_t>(kk * p.a_kstep),
+                               b_desc + static_cast<uint64_t>(kk * p.b_kstep), p.idesc,
+                               (kb | kk) != 0 ? 1u : 0u);
+          ptx::umma_commit_pair(&empty[stage]);
+          if (++stage == kStages2) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        ptx::umma_commit_pair(&tfull[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = pair; tile < p.num_tiles; tile += npairs) {
+      int m_idx, n_idx;
+      tile_coords(p, tile, &m_idx, &n_idx);
+      if (!ptx::mbar_wait(&tfull[acc], acc_phase, cta_abort, p.status, ST_EPILOGUE)) break;
+      ptx::tcgen05_fence_after_sync();
+      const uint32_t taddr =
+          tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      const int64_t row =
+          static_cast<int64_t>(m_idx) * (2 * BM) + static_cast<int64_t>(rank) * BM + quarter * 32 + lane;
+      if (EPI == EPI_PLAIN) epi_plain<T>(p, taddr, row, n_idx * BN, half);
+      if (EPI == EPI_SWIGLU_FWD) epi_swiglu_fwd<T>(p, taddr, row, n_idx * (BN / 2), half);
+      if (EPI == EPI_SWIGLU_BWD) epi_swiglu_bwd<T>(p, taddr, row, n_idx * BN, half);
+      if (EPI == EPI_LCE) epi_lce<T>(p, taddr, row, n_idx * BN, n_idx, half);
+      ptx::tcgen05_fence_before_sync();
+      if (leader)
+        ptx::mbar_arrive(&tempty[acc]);
+      else
+        ptx::mbar_arrive_cluster(&tempty[acc], 0);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  ptx::tcgen05_fence_before_sync();
+  __syncthreads();
+  ptx::cluster_sync_all();  // both CTAs are done with tensor memory and with each other's barriers
+  if (warp == 1) {
+    ptx::tcgen05_fence_after_sync();
+    ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
 // ----------------------------------------------------------------------- host
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -557,6 +745,48 @@ int launch_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1
   return BT_OK;
 }
 
+template <int EPI, typename T>
+int launch_pair_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1,
+                  const CUtensorMap& b1, const Params& p, cudaStream_t s) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  auto* kern = gemm_kernel_pair<EPI, T>;
+  std::call_once(once, [&] {
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2);
+  });
+  if (attr_err != cudaSuccess) {
+    set_error("gemm: cannot reserve %d bytes of shared memory: %s", kSmemBytes2,
+              cudaGetErrorString(attr_err));
+    return BT_ERR_LAUNCH;
+  }
+  const int max_pairs = sm_count() / 2;
+  const int pairs = p.num_tiles < max_pairs ? p.num_tiles : max_pairs;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmemBytes2;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a0, b0, a1, b1, p);
+  if (e != cudaSuccess) {
+    set_error("gemm_kernel_pair: %s", cudaGetErrorString(e));
+    return BT_ERR_LAUNCH;
+  }
+  return BT_OK;
+}
+
+// 0: one CTA per 128 x 256 tile (cta_group::1); 1: CTA pairs on 256 x 256 tiles (cta_group::2).
+inline int& pair_mode() {
+  static int mode = 1;
+  return mode;
+}
+
 // Describes one GEMM launch; pair 1 and b1 are optional.
 struct Launch {
   Operand a0, b0, a1, b1;
@@ -581,10 +811,11 @@ template <int EPI>
 int launch(Launch& L, cudaStream_t s) {
   bind_context_once();
   Params& p = L.p;
+  const bool pair = pair_mode() != 0;
   const int n_tile = L.dual_b ? BN / 2 : BN;
   p.K0 = static_cast<int>(L.a0.k);
   p.K1 = L.two_pairs ? static_cast<int>(L.a1.k) : 0;
-  p.tiles_m = static_cast<int>(ceil_div(p.M, BM));
+  p.tiles_m = static_cast<int>(ceil_div(p.M, pair ? 2 * BM : BM));
   p.tiles_n = static_cast<int>(ceil_div(p.N, n_tile));
   const int64_t nt = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
   if (nt <= 0 || nt > 0x7fffffff || p.K0 <= 0) {
@@ -595,13 +826,15 @@ int launch(Launch& L, cudaStream_t s) {
   p.a_kmajor = L.a0.kmajor;
   p.b_kmajor = L.b0.kmajor;
   p.dual_b = L.dual_b ? 1 : 0;
-  p.idesc = ptx::make_idesc_f16(L.bf16, !L.a0.kmajor, !L.b0.kmajor, BM, BN);
+  p.idesc = ptx::make_idesc_f16(L.bf16, !L.a0.kmajor, !L.b0.kmajor, pair ? 2 * BM : BM, BN);
   p.a_desc_hi = ptx::make_smem_desc_hi(L.a0.kmajor != 0, kBoxBytesMN);
   p.b_desc_hi = ptx::make_smem_desc_hi(L.b0.kmajor != 0, kBoxBytesMN);
   p.a_kstep = L.a0.kmajor ? (32u >> 4) : (16u * 128u >> 4);
   p.b_kstep = L.b0.kmajor ? (32u >> 4) : (16u * 128u >> 4);
+  // K-major boxes: a CTA of a pair stages 128 rows of A and 128 of the tile's 256 B rows
+  const int b_box = pair ? BN / 2 : n_tile;
   L.a0.box_mn = BM;
-  L.b0.box_mn = n_tile;
+  L.b0.box_mn = b_box;
   CUtensorMap ta0, tb0, ta1, tb1;
   int rc;
   if ((rc = make_tmap(&ta0, L.a0, L.bf16, "gemm A")) != BT_OK) return rc;
@@ -614,7 +847,7 @@ int launch(Launch& L, cudaStream_t s) {
       return BT_ERR_ARG;
     }
     L.a1.box_mn = BM;
-    L.b1.box_mn = n_tile;
+    L.b1.box_mn = b_box;
     if ((rc = make_tmap(&ta1, L.a1, L.bf16, "gemm A1")) != BT_OK) return rc;
     if ((rc = make_tmap(&tb1, L.b1, L.bf16, "gemm B1")) != BT_OK) return rc;
   } else if (L.dual_b) {
@@ -622,9 +855,12 @@ int launch(Launch& L, cudaStream_t s) {
       set_error("gemm: dual-B mode needs K-major B operands");
       return BT_ERR_ARG;
     }
-    L.b1.box_mn = n_tile;
+    L.b1.box_mn = b_box;
     if ((rc = make_tmap(&tb1, L.b1, L.bf16, "gemm B1")) != BT_OK) return rc;
   }
+  if (pair)
+    return L.bf16 ? launch_pair_t<EPI, __nv_bfloat16>(ta0, tb0, ta1, tb1, p, s)
+                  : launch_pair_t<EPI, __half>(ta0, tb0, ta1, tb1, p, s);
   return L.bf16 ? launch_t<EPI, __nv_bfloat16>(ta0, tb0, ta1, tb1, p, s)
                 : launch_t<EPI, __half>(ta0, tb0, ta1, tb1, p, s);
 }

@@ -206,17 +206,29 @@ rms_bwd_rows(const T* __restrict__ dy, const T* __restrict__ x, const T* __restr
   }
 
   __syncthreads();  // s_dw zeroed
+  // Row groups that share a warp hold the same columns: fold them together first.
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int v = lane + i * LPR;
-    if (v < nv) {
+  for (int o = LPR; o < 32; o <<= 1) {
 #pragma unroll
-      for (int e = 0; e < E; ++e) atomicAdd(&s_dw[v * E + e], acc[i][e]);
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[i][e] += __shfl_xor_sync(0xffffffffu, acc[i][e], o);
+  }
+  // s_dw is kept element-major (index e * nv + v) so that the lanes of one instruction,
+  // which differ in v, fall into different banks.
+  if ((threadIdx.x & 31) < LPR) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = lane + i * LPR;
+      if (v < nv) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) atomicAdd(&s_dw[e * nv + v], acc[i][e]);
+      }
     }
   }
   __syncthreads();
   float* my_ws = ws + static_cast<int64_t>(blockIdx.x % dw_copies(N)) * N;
-  for (int c = threadIdx.x; c < N; c += kThreads) atomicAdd(my_ws + c, s_dw[c]);
+  for (int c = threadIdx.x; c < N; c += kThreads) atomicAdd(my_ws + c, s_dw[(c % E) * nv + c / E]);
   dw_finalize<T>(ws, dw, N, gridDim.x, threadIdx.x, kThreads);
 }
 

@@ -458,8 +458,8 @@ def main():
     mlp_flops = 9 * 2.0 * seq * hdim * inter * (mlp_calls // 2)
     achieved = mlp_flops / (mlp_ms / 1e3) / 1e12 if mlp_ms > 0 else None
     peak_tf = peaks["bf16_tflops_sustained"]
-    roofline = {"bound": "tensor", "kernel": "bt::gemm::gemm_kernel (7 launches per MLP block: gate|up fused, down, "
-                                             "dh->dgate/dup, dWd, dWg, dWu, dx)",
+    roofline = {"bound": "tensor", "kernel": "bt::gemm::gemm_kernel_pair, tcgen05 cta_group::2 (7 launches per MLP block: gate|up fused, "
+                                             "down, dh->dgate/dup, dWd, dWg, dWu, dx)",
                 "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf if achieved else None,
                 "peak_kind": f"{peak_kind} cuBLAS bf16, sustained (kernel timed inside a long step); burst {peaks['bf16_tflops']}",
                 "frac_of_burst": achieved / peaks["bf16_tflops"] if achieved else None,

@@ -153,6 +153,13 @@ int bt_gemm(const void* A, const void* B, void* D,
             const float* addend, int64_t ld_addend, const float* alpha,
             int32_t* status, void* stream);
 
+/* Selects how the tensor-core kernels tile their work: 0 = one CTA per 128x256
+ * output tile (tcgen05 cta_group::1), 1 = pairs of CTAs in a 2-CTA cluster on
+ * 256x256 tiles (cta_group::2).  A negative argument only queries.  Returns the
+ * previous setting.  Process-wide; not a per-call option.  No reference
+ * counterpart (cuBLAS picks its own kernels). */
+int bt_set_gemm_cta_pairs(int enable);
+
 /* ------------------------------------------------------ SwiGLU MLP (fused)  */
 
 /* Forward of CuTileSwiGLUMLP (src/bastile/ops/swiglu.py:170-187):

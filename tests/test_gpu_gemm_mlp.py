@@ -11,6 +11,18 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+@pytest.fixture(params=[1, 0], ids=["cta_pairs", "single_cta"])
+def gemm_mode(request):
+    """Run a test under both tilings of the tensor-core kernels (cta_group::2 pairs, the default,
+    and one CTA per tile)."""
+    from bastile_b200 import _lib
+
+    lib = _lib.get_lib()
+    prev = lib.bt_set_gemm_cta_pairs(request.param)
+    yield request.param
+    lib.bt_set_gemm_cta_pairs(prev)
+
+
 def _gemm(A, B, M, N, K, ak, bk, out_dtype=None, addend=None, alpha=None):
     from bastile_b200 import _lib
 
@@ -32,7 +44,7 @@ def _gemm(A, B, M, N, K, ak, bk, out_dtype=None, addend=None, alpha=None):
 @pytest.mark.parametrize("ak,bk", [(1, 1), (1, 0), (0, 1), (0, 0)])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (136, 264, 72), (8, 8, 8), (300, 520, 1000), (1, 1000, 130),
                                    (640, 1024, 520)])
-def test_gemm_layouts_and_ragged_shapes(M, N, K, ak, bk, dtype):
+def test_gemm_layouts_and_ragged_shapes(M, N, K, ak, bk, dtype, gemm_mode):
     if (ak or bk) and K % 8:
         pytest.skip("K-major operands need a row stride that is a multiple of 8 elements")
     torch.manual_seed(M + N + K)
@@ -71,7 +83,7 @@ def test_gemm_fp32_out_addend_alpha_and_inplace_accumulate():
     assert_close(acc, add + 2 * (A.float() @ B.float().T), what="accumulate", rtol=1e-4, atol=2e-3)
 
 
-def test_gemm_persistent_many_tiles_matches_fp32_reference():
+def test_gemm_persistent_many_tiles_matches_fp32_reference(gemm_mode):
     """More tiles than SMs (several per CTA, both accumulator buffers, ring wrap-around)."""
     torch.manual_seed(1)
     M, N, K = 2048, 5120, 1024
@@ -112,7 +124,7 @@ def _mlp_case(t, hidden, inter, dtype, seed=0, w_std=0.05):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("t,hidden,inter", [(21, 64, 160), (256, 256, 768), (300, 512, 1384), (1, 128, 256)])
-def test_mlp_fwd_bwd_vs_oracle(t, hidden, inter, dtype):
+def test_mlp_fwd_bwd_vs_oracle(t, hidden, inter, dtype, gemm_mode):
     from bastile_b200.ops.swiglu import SwiGLUMLPFunction
 
     x, wg, wu, wd, dy = _mlp_case(t, hidden, inter, dtype)

@@ -13,6 +13,16 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+@pytest.fixture(params=[1, 0], ids=["cta_pairs", "single_cta"])
+def gemm_mode(request):
+    from bastile_b200 import _lib
+
+    lib = _lib.get_lib()
+    prev = lib.bt_set_gemm_cta_pairs(request.param)
+    yield request.param
+    lib.bt_set_gemm_cta_pairs(prev)
+
+
 def _run(x, w, t, **kw):
     from bastile_b200.ops.fused_linear_cross_entropy import fused_linear_cross_entropy
 
@@ -72,7 +82,7 @@ def test_lce_reference_unit_tests_bf16():
 @pytest.mark.parametrize("reduction", ["mean", "sum"])
 @pytest.mark.parametrize("bt,h,v,chunk", [(300, 256, 1000, 128), (1, 64, 8, 4096), (513, 128, 3000, 256),
                                           (64, 4096, 2048, 4096)])
-def test_lce_small_weights_vs_oracle(bt, h, v, chunk, reduction):
+def test_lce_small_weights_vs_oracle(bt, h, v, chunk, reduction, gemm_mode):
     """W ~ N(0, 0.02) as in training: loss within 1e-3 relative of the fp32 oracle."""
     torch.manual_seed(bt + v)
     x = torch.randn(bt, h, device=DEV, dtype=torch.bfloat16)

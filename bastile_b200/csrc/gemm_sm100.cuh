@@ -23,6 +23,7 @@
 //   frees its tensor memory before exiting.
 #pragma once
 
+#include <cstdlib>
 #include <mutex>
 
 #include "bt_common.cuh"
@@ -54,6 +55,7 @@ struct Params {
   int M, N;        // output extent; with dual_b, N is the width of ONE of the two outputs
   int K0, K1;      // contraction lengths of pair 0 and pair 1 (K1 = 0: single pair)
   int tiles_m, tiles_n, num_tiles;
+  int group_m;     // rasterisation: row-tiles walked per column-tile before moving on
   int a_kmajor, b_kmajor, dual_b;
   uint32_t idesc;
   uint64_t a_desc_hi, b_desc_hi;
@@ -81,10 +83,10 @@ struct Params {
 };
 
 __device__ __forceinline__ void tile_coords(const Params& p, int tile, int* m_idx, int* n_idx) {
-  const int per_group = kGroupM * p.tiles_n;
+  const int per_group = p.group_m * p.tiles_n;
   const int g = tile / per_group;
-  const int first_m = g * kGroupM;
-  const int gs = min(p.tiles_m - first_m, kGroupM);
+  const int first_m = g * p.group_m;
+  const int gs = min(p.tiles_m - first_m, p.group_m);
   const int r = tile - g * per_group;
   *m_idx = first_m + r % gs;
   *n_idx = r / gs;
@@ -823,6 +825,13 @@ int launch(Launch& L, cudaStream_t s) {
     return BT_ERR_ARG;
   }
   p.num_tiles = static_cast<int>(nt);
+  {
+    static const int env_group = [] {
+      const char* e = getenv("BT_GEMM_GROUP_M");
+      return e ? atoi(e) : 0;
+    }();
+    p.group_m = env_group > 0 ? env_group : kGroupM;
+  }
   p.a_kmajor = L.a0.kmajor;
   p.b_kmajor = L.b0.kmajor;
   p.dual_b = L.dual_b ? 1 : 0;

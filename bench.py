@@ -364,6 +364,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seq", type=int, default=SEQ_LEN)
     ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
+    ap.add_argument("--intermediate", type=int, default=QWEN3_8B["intermediate_size"],
+                    help="MLP width (the reference's chart used 14336; BASELINE.json and Qwen3-8B use 12288)")
     ap.add_argument("--no-per-op", action="store_true")
     ap.add_argument("--only-op", default=None, choices=["rmsnorm", "rope", "mlp", "lce"],
                     help="run just this op's forward+backward micro-benchmark (small case for profilers)")
@@ -408,7 +410,7 @@ def main():
     assert applied == ["rms_norm_qwen3", "rope_qwen3", "swiglu_qwen3", "fused_linear_cross_entropy"], applied
     peaks, peak_kind = load_peaks()
 
-    cfg = Qwen3Config(**{**QWEN3_8B, "num_hidden_layers": args.layers})
+    cfg = Qwen3Config(**{**QWEN3_8B, "num_hidden_layers": args.layers, "intermediate_size": args.intermediate})
     cfg._attn_implementation = "sdpa"
     torch.manual_seed(1234 + rank)
     prev = torch.get_default_dtype()
@@ -506,7 +508,7 @@ def main():
     line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_value / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"qwen3-8b ({args.layers} layers, hidden 4096, intermediate 12288, vocab 151936) seq {seq} "
+            "config": {"workload": f"qwen3-8b ({args.layers} layers, hidden 4096, intermediate {args.intermediate}, vocab 151936) seq {seq} "
                                    "batch 1 fwd+bwd+AdamW, random init",
                        "global_batch_tokens": seq * world, "seq_len": seq,
                        "parallelism": "single GPU" if world == 1 else f"dp{world} (DistributedDataParallel, NCCL)",

@@ -56,7 +56,7 @@ def merge_shard_stats(gathered: Tensor) -> Tensor:
 class LinearCrossEntropyFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, target, ignore_index, reduction, chunk_size, v_chunk_size,
-                group=None, vocab_start=0):
+                group=None, vocab_start=0, shard_tokens=False, grad_hidden_scale=1.0):
         dev = _lib.require_cuda(x, weight, target)
         lib = _lib.get_lib()
         if x.dtype not in _GEMM_DTYPES:
@@ -71,6 +71,18 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         xf = x.reshape(-1, hdim)
         if xf.stride(-1) != 1 or (xf.shape[0] > 1 and xf.stride(0) % 8 != 0):
             xf = xf.contiguous()
+        bt_local = xf.shape[0]
+        if group is not None and shard_tokens:
+            # every rank brought its own rows: assemble all rows of all ranks (same count each)
+            import torch.distributed as dist
+
+            world_sz = dist.get_world_size(group)
+            x_all = torch.empty((world_sz * bt_local, hdim), dtype=x.dtype, device=dev)
+            dist.all_gather_into_tensor(x_all, xf.contiguous(), group=group)
+            t_local = target.reshape(-1).to(torch.int64).contiguous()
+            t_all = torch.empty(world_sz * bt_local, dtype=torch.int64, device=dev)
+            dist.all_gather_into_tensor(t_all, t_local, group=group)
+            xf, target = x_all, t_all
         bt = xf.shape[0]
         w = weight.detach()
         if w.dtype != x.dtype:
@@ -157,12 +169,19 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         if group is not None and bt > 0:
             import torch.distributed as dist
 
-            dist.all_reduce(dx, group=group)
+            if shard_tokens:  # each rank only needs the gradient of its own rows
+                dx_local = torch.empty((bt_local, hdim), dtype=dx.dtype, device=dev)
+                dist.reduce_scatter_tensor(dx_local, dx, group=group)
+                dx = dx_local
+                batch_shape = x.shape[:-1]
+            else:
+                dist.all_reduce(dx, group=group)
 
         ctx.save_for_backward(dx, w, logits_buf, x_last if x_last is not None else xf[:0],
                               dw_acc if dw_acc is not None else scal[:0])
         ctx.meta = (batch_shape, hdim, vloc, last_rows, ld_logits, x.dtype, weight.dtype, n_chunks,
                     xf.stride(0) if bt > 1 else hdim)
+        ctx.grad_hidden_scale = float(grad_hidden_scale)
         return scal[2].clone()
 
     @staticmethod
@@ -180,7 +199,8 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         with _lib.device_of(dev), _lib.timed("lce_bwd", int(need_x) + int(need_w and n_chunks > 0), dev):
             if need_x:
                 dx_out = torch.empty(dx.shape, dtype=x_dtype, device=dev)
-                _lib.check(lib.bt_scale_cast(dx.data_ptr(), dx_out.data_ptr(), dx.numel(), scale.data_ptr(),
+                scale_x = scale if ctx.grad_hidden_scale == 1.0 else scale * ctx.grad_hidden_scale
+                _lib.check(lib.bt_scale_cast(dx.data_ptr(), dx_out.data_ptr(), dx.numel(), scale_x.data_ptr(),
                                              _lib.dtype_code(dx.dtype), code, stream), "bt_scale_cast(dx)")
                 dx_out = dx_out.view(*batch_shape, hdim)
             if need_w:
@@ -195,7 +215,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
                                            st.data_ptr(), stream), "bt_gemm(dW last)")
                 if dw_out.dtype != w_dtype:
                     dw_out = dw_out.to(w_dtype)
-        return dx_out, dw_out, None, None, None, None, None, None, None
+        return dx_out, dw_out, None, None, None, None, None, None, None, None, None
 
 
 ChunkedLinearCrossEntropyFunction = LinearCrossEntropyFunction
@@ -204,14 +224,20 @@ ChunkedLinearCrossEntropyFunction = LinearCrossEntropyFunction
 def fused_linear_cross_entropy(hidden_states: Tensor, weight: Tensor, target: Tensor, bias=None,
                                ignore_index: int = -100, chunk_size: int = 4096, reduction: str = "mean",
                                v_chunk_size: int | None = None, vocab_parallel_group=None,
-                               vocab_start: int = 0) -> Tensor:
+                               vocab_start: int = 0, shard_tokens: bool = False,
+                               grad_hidden_scale: float = 1.0) -> Tensor:
     """Loss of ``cross_entropy(hidden_states @ weight.T, target)`` without ever holding
     ``[tokens, vocab]`` logits; same arguments as the reference (:405-438).
 
     ``v_chunk_size`` is accepted for compatibility: the kernels already tile the
     vocabulary, so it selects nothing.  ``vocab_parallel_group`` / ``vocab_start``
     are additions for the vocabulary-sharded form (``weight`` is then the local
-    slice of rows starting at ``vocab_start``; ``target`` holds global ids).
+    slice of rows starting at ``vocab_start``; ``target`` holds global ids).  By default
+    every rank passes the SAME ``hidden_states``; with ``shard_tokens=True`` every rank passes
+    its own rows (equal counts), the op all-gathers them, the loss is the mean over all ranks'
+    tokens, and each rank gets the gradient of its own rows back (reduce-scatter), multiplied
+    by ``grad_hidden_scale`` (set it to the world size under data-parallel wrappers that
+    average gradients over ranks).
     """
     if hidden_states.ndim == 3:
         hidden_states = hidden_states.reshape(-1, hidden_states.shape[-1])
@@ -222,7 +248,18 @@ def fused_linear_cross_entropy(hidden_states: Tensor, weight: Tensor, target: Te
         logits = F.linear(hidden_states, weight, bias)
         return F.cross_entropy(logits, target, ignore_index=ignore_index, reduction=reduction)
     return LinearCrossEntropyFunction.apply(hidden_states, weight, target, ignore_index, reduction, chunk_size,
-                                            v_chunk_size, vocab_parallel_group, vocab_start)
+                                            v_chunk_size, vocab_parallel_group, vocab_start, shard_tokens,
+                                            grad_hidden_scale)
+
+
+# Set by set_vocab_parallel(): the model forward then treats ``lm_head.weight`` as this rank's
+# slice of vocabulary rows and the ranks' tokens as shards of one batch.
+_VOCAB_PARALLEL = {"group": None, "vocab_start": 0, "grad_hidden_scale": 1.0}
+
+
+def set_vocab_parallel(group, vocab_start: int = 0, grad_hidden_scale: float = 1.0) -> None:
+    """Switch ``bastile_lce_forward`` to the vocabulary-parallel loss (``group=None`` switches back)."""
+    _VOCAB_PARALLEL.update(group=group, vocab_start=int(vocab_start), grad_hidden_scale=float(grad_hidden_scale))
 
 
 def bastile_lce_forward(self, input_ids=None, attention_mask=None, position_ids=None, past_key_values=None,
@@ -256,8 +293,14 @@ def bastile_lce_forward(self, input_ids=None, attention_mask=None, position_ids=
         # flattened view non-uniform.
         shift_hidden = hidden_states[..., :-1, :]
         shift_labels = labels[..., 1:]
-        loss = fused_linear_cross_entropy(shift_hidden, self.lm_head.weight, shift_labels,
-                                          bias=getattr(self.lm_head, "bias", None), ignore_index=-100)
+        vp = _VOCAB_PARALLEL
+        if vp["group"] is None:
+            loss = fused_linear_cross_entropy(shift_hidden, self.lm_head.weight, shift_labels,
+                                              bias=getattr(self.lm_head, "bias", None), ignore_index=-100)
+        else:
+            loss = fused_linear_cross_entropy(shift_hidden, self.lm_head.weight, shift_labels, ignore_index=-100,
+                                              vocab_parallel_group=vp["group"], vocab_start=vp["vocab_start"],
+                                              shard_tokens=True, grad_hidden_scale=vp["grad_hidden_scale"])
     else:
         keep = slice(-logits_to_keep, None) if isinstance(logits_to_keep, int) else logits_to_keep
         logits = self.lm_head(hidden_states[:, keep, :])

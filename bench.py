@@ -366,6 +366,14 @@ def main():
     ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
     ap.add_argument("--intermediate", type=int, default=QWEN3_8B["intermediate_size"],
                     help="MLP width (the reference's chart used 14336; BASELINE.json and Qwen3-8B use 12288)")
+    ap.add_argument("--fsdp", action="store_true",
+                    help="N > 1: FullyShardedDataParallel FULL_SHARD with bf16 mixed precision, wrapped per decoder layer "
+                         "(the reference's tests/benchmarks/e2e/qwen_8b_fsdp.py:161-168) instead of DDP")
+    ap.add_argument("--vocab-parallel", action="store_true",
+                    help="with --fsdp: lm_head rows sharded over ranks and the fused loss run vocabulary-parallel")
+    ap.add_argument("--grad-checkpoint", action="store_true",
+                    help="recompute each decoder layer in the backward (needed for seq 32768 per rank: the saved "
+                         "activations of 36 layers alone would exceed 180 GB)")
     ap.add_argument("--no-per-op", action="store_true")
     ap.add_argument("--only-op", default=None, choices=["rmsnorm", "rope", "mlp", "lce"],
                     help="run just this op's forward+backward micro-benchmark (small case for profilers)")
@@ -412,20 +420,51 @@ def main():
 
     cfg = Qwen3Config(**{**QWEN3_8B, "num_hidden_layers": args.layers, "intermediate_size": args.intermediate})
     cfg._attn_implementation = "sdpa"
-    torch.manual_seed(1234 + rank)
+    torch.manual_seed(1234)  # same initial weights on every rank
     prev = torch.get_default_dtype()
     torch.set_default_dtype(torch.bfloat16)
     with torch.device(dev):
         model = Qwen3ForCausalLM(cfg)
     torch.set_default_dtype(prev)
     model.train()
+    if args.grad_checkpoint or args.seq >= 32768:
+        args.grad_checkpoint = True
+        model.gradient_checkpointing_enable(gradient_checkpointing_kwargs={"use_reentrant": False})
     net = model
-    if world > 1:
+    parallelism = "single GPU"
+    if world > 1 and args.fsdp:
+        import functools
+
+        from torch.distributed.fsdp import FullyShardedDataParallel as FSDP
+        from torch.distributed.fsdp import MixedPrecision, ShardingStrategy
+        from torch.distributed.fsdp.wrap import transformer_auto_wrap_policy
+        from transformers.models.qwen3.modeling_qwen3 import Qwen3DecoderLayer
+
+        ignored = None
+        if args.vocab_parallel:
+            # this rank keeps rows [rank*V/n, (rank+1)*V/n) of lm_head as an ordinary local parameter
+            from bastile_b200.ops.fused_linear_cross_entropy import set_vocab_parallel
+
+            vloc = cfg.vocab_size // world
+            shard = model.lm_head.weight.data[rank * vloc:(rank + 1) * vloc].clone()
+            model.lm_head.weight = torch.nn.Parameter(shard)
+            set_vocab_parallel(dist.group.WORLD, vocab_start=rank * vloc, grad_hidden_scale=float(world))
+            ignored = [model.lm_head]
+        mp = MixedPrecision(param_dtype=torch.bfloat16, reduce_dtype=torch.bfloat16, buffer_dtype=torch.bfloat16)
+        net = FSDP(model, sharding_strategy=ShardingStrategy.FULL_SHARD, mixed_precision=mp,
+                   auto_wrap_policy=functools.partial(transformer_auto_wrap_policy,
+                                                      transformer_layer_cls={Qwen3DecoderLayer}),
+                   use_orig_params=True, device_id=dev, ignored_modules=ignored)
+        parallelism = (f"fsdp{world} FULL_SHARD bf16, per-layer wrap" +
+                       (", lm_head vocabulary-parallel" if args.vocab_parallel else ""))
+    elif world > 1:
         from torch.nn.parallel import DistributedDataParallel as DDP
 
         net = DDP(model, device_ids=[local], gradient_as_bucket_view=True, bucket_cap_mb=256)
-    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True)
+        parallelism = f"dp{world} (DistributedDataParallel, NCCL)"
+    opt = torch.optim.AdamW(net.parameters(), lr=1e-4, fused=True)
 
+    torch.manual_seed(4321 + rank)  # different tokens per rank
     seq = args.seq
     n_bufs = 4
     host_ids = [torch.randint(0, cfg.vocab_size, (1, seq)).pin_memory() for _ in range(n_bufs)]
@@ -511,8 +550,8 @@ def main():
             "config": {"workload": f"qwen3-8b ({args.layers} layers, hidden 4096, intermediate {args.intermediate}, vocab 151936) seq {seq} "
                                    "batch 1 fwd+bwd+AdamW, random init",
                        "global_batch_tokens": seq * world, "seq_len": seq,
-                       "parallelism": "single GPU" if world == 1 else f"dp{world} (DistributedDataParallel, NCCL)",
-                       "attention": "torch SDPA", "optimizer": "torch.optim.AdamW(fused=True), bf16 params and state",
+                       "parallelism": parallelism,
+                       "attention": "torch SDPA", "activation_checkpointing": bool(args.grad_checkpoint), "optimizer": "torch.optim.AdamW(fused=True), bf16 params and state",
                        "l2": "each step streams ~65 GB of weights, gradients and optimizer state: far larger than the 126 MB L2"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": seq * 8, "d2h_bytes_per_step": 4,
                     "ms_per_step": ms_e2e / args.steps},

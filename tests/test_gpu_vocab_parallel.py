@@ -49,6 +49,19 @@ def _worker(rank, world, port, q):
         ok_loss = abs(loss.item() - float(l_ref)) <= 2e-3 * abs(float(l_ref))
         ok_dx = np.allclose(xs.grad.float().cpu().numpy(), dx_ref, rtol=2e-2, atol=2e-2 * sx)
         ok_dw = np.allclose(wl.grad.float().cpu().numpy(), dw_ref[rank * vs:(rank + 1) * vs], rtol=2e-2, atol=2e-2 * sw)
+        # token-sharded form: every rank brings its own half of the rows
+        half = bt // world
+        xs2 = x[rank * half:(rank + 1) * half].clone().requires_grad_(True)
+        wl2 = w[rank * vs:(rank + 1) * vs].clone().requires_grad_(True)
+        loss2 = fused_linear_cross_entropy(xs2, wl2, t[rank * half:(rank + 1) * half], chunk_size=256,
+                                           vocab_parallel_group=dist.group.WORLD, vocab_start=rank * vs,
+                                           shard_tokens=True, grad_hidden_scale=2.0)
+        loss2.backward()
+        _lib.check_status(dev, "token-sharded vocab-parallel loss")
+        ok_loss &= abs(loss2.item() - float(l_ref)) <= 2e-3 * abs(float(l_ref))
+        ok_dx &= np.allclose(xs2.grad.float().cpu().numpy(), 2.0 * dx_ref[rank * half:(rank + 1) * half], rtol=2e-2,
+                             atol=4e-2 * sx)
+        ok_dw &= np.allclose(wl2.grad.float().cpu().numpy(), dw_ref[rank * vs:(rank + 1) * vs], rtol=2e-2, atol=2e-2 * sw)
         q.put((rank, ok_loss, ok_dx, ok_dw, loss.item(), float(l_ref)))
     finally:
         dist.destroy_process_group()

@@ -542,7 +542,8 @@ def main():
                 "frac_of_burst": achieved / peaks["bf16_tflops"] if achieved else None,
                 "flops_per_launch": mlp_flops / gemm_launches if gemm_launches else None,
                 "avg_launch_ms": mlp_ms / gemm_launches if gemm_launches else None, "launches_timed": gemm_launches,
-                "traffic": None}
+                "traffic": 1.31e9, "traffic_note": "dram read+write bytes per launch, mean of the 7 launches of a block, ncu --set full "
+                                                        "capture of bench.py --only-op mlp (profiles/gemm_kernel_pair_mlp_8192x4096x12288.md)"}
 
     line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_value / args.steps, "higher_is_better": True, "scaling": "weak",

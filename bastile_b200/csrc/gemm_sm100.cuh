@@ -23,7 +23,6 @@
 //   frees its tensor memory before exiting.
 #pragma once
 
-#include <cstdlib>
 #include <mutex>
 
 #include "bt_common.cuh"
@@ -825,13 +824,7 @@ int launch(Launch& L, cudaStream_t s) {
     return BT_ERR_ARG;
   }
   p.num_tiles = static_cast<int>(nt);
-  {
-    static const int env_group = [] {
-      const char* e = getenv("BT_GEMM_GROUP_M");
-      return e ? atoi(e) : 0;
-    }();
-    p.group_m = env_group > 0 ? env_group : kGroupM;
-  }
+  p.group_m = kGroupM;
   p.a_kmajor = L.a0.kmajor;
   p.b_kmajor = L.b0.kmajor;
   p.dual_b = L.dual_b ? 1 : 0;

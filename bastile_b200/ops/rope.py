@@ -46,6 +46,19 @@ def _launch(q_in, k_in, q_out, k_out, cos, sin, negate: bool) -> None:
     _lib.check(rc, "bt_rope")
 
 
+def _dense(layout) -> bool:
+    """True when (shape, strides) is a permutation of a contiguous tensor (no gaps, no overlap)."""
+    shape, strides = layout
+    expect = 1
+    for size, stride in sorted(zip(shape, strides), key=lambda p: p[1]):
+        if size == 1:
+            continue
+        if stride != expect:
+            return False
+        expect *= size
+    return True
+
+
 class RoPEFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, cos, sin, position_ids=None, unsqueeze_dim=1):
@@ -61,6 +74,11 @@ class RoPEFunction(torch.autograd.Function):
         k_src = k if k.stride(-1) == 1 else k.contiguous()
         _launch(q_src, k_src, q_dst, k_dst, cos, sin, negate=False)
         ctx.save_for_backward(cos, sin)
+        # the gradients are handed back in the memory layout of the inputs, so that whatever
+        # produced q / k (a transposed view of [B, T, H, D] storage in HF attention) gets a
+        # gradient it can flatten without a copy
+        ctx.q_layout = (tuple(q.shape), tuple(q.stride())) if q.stride(-1) == 1 else None
+        ctx.k_layout = (tuple(k.shape), tuple(k.stride())) if k.stride(-1) == 1 else None
         return q_dst.view(q_dst.shape), k_dst.view(k_dst.shape)
 
     @staticmethod
@@ -70,8 +88,13 @@ class RoPEFunction(torch.autograd.Function):
             dq = dq.contiguous()
         if dk.stride(-1) != 1:
             dk = dk.contiguous()
-        dq_out = torch.empty(dq.shape, dtype=dq.dtype, device=dq.device)
-        dk_out = torch.empty(dk.shape, dtype=dk.dtype, device=dk.device)
+        def like_input(grad, layout):
+            if layout is not None and _dense(layout):
+                return torch.empty_strided(layout[0], layout[1], dtype=grad.dtype, device=grad.device)
+            return torch.empty(grad.shape, dtype=grad.dtype, device=grad.device)
+
+        dq_out = like_input(dq, ctx.q_layout)
+        dk_out = like_input(dk, ctx.k_layout)
         _launch(dq, dk, dq_out, dk_out, cos, sin, negate=True)
         return dq_out, dk_out, None, None, None, None
 

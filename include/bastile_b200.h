@@ -236,6 +236,23 @@ int bt_lce_reduce_loss(const float* loss_row, int64_t n, const float* grad_scale
 int bt_scale_cast(const void* in, void* out, int64_t n, const float* scale,
                   int in_dtype, int out_dtype, void* stream);
 
+/* ------------------------------------------------------------------ AdamW  */
+
+/* One AdamW step (decoupled weight decay, bias correction; the update rule of
+ * torch.optim.AdamW) over a list of tensors that share one storage dtype for
+ * parameter, gradient and both moments.  The four tables are HOST arrays of
+ * n_tensors device pointers, `numel` a host array of element counts.  fp32
+ * arithmetic, one rounding to the storage type.  `step` is the 1-based step
+ * count used for the bias corrections.  The reference has no optimizer of its
+ * own: its benchmark loop runs torch.optim.AdamW inside the timed region
+ * (tests/benchmarks/e2e/qwen_8b_seqlen.py:122-125, 154-158); this is that step
+ * as one streaming pass per tensor. */
+int bt_adamw_step(void* const* params, const void* const* grads,
+                  void* const* exp_avg, void* const* exp_avg_sq,
+                  const int64_t* numel, int n_tensors,
+                  float lr, float beta1, float beta2, float eps,
+                  float weight_decay, int64_t step, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

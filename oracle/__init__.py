@@ -21,6 +21,7 @@ only pin for them.
 """
 
 from .ops import (  # noqa: F401
+    adamw_step,
     lce_fwd_bwd,
     lce_shard_stats,
     merge_shard_stats,

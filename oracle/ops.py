@@ -181,3 +181,18 @@ def lce_fwd_bwd(x, w, target, ignore_index=-100, reduction="mean", n_shards=1):
     probs[~valid] = 0.0
     dlogits = probs * scale
     return F32(loss), (dlogits @ w).astype(F32), (dlogits.T @ x).astype(F32)
+
+
+# ----------------------------------------------------------------------- AdamW
+def adamw_step(p, g, m, v, step, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=1e-2):
+    """One AdamW step in float64; returns (p, m, v).  The update rule of torch.optim.AdamW, which
+    the reference's benchmark loop runs (tests/benchmarks/e2e/qwen_8b_seqlen.py:122-125, 154-158):
+    decoupled decay, bias-corrected moments, eps added after the square root."""
+    p, g, m, v = (np.asarray(t, F64) for t in (p, g, m, v))
+    p = p * (1.0 - lr * weight_decay)
+    m = beta1 * m + (1.0 - beta1) * g
+    v = beta2 * v + (1.0 - beta2) * g * g
+    bc1 = 1.0 - beta1 ** step
+    bc2 = 1.0 - beta2 ** step
+    p = p - (lr / bc1) * m / (np.sqrt(v) / np.sqrt(bc2) + eps)
+    return p, m, v

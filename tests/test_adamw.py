@@ -1,0 +1,53 @@
+"""AdamW: the numpy oracle against torch.optim.AdamW on CPU, and the CUDA kernel against both."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import assert_close
+
+
+def test_oracle_matches_torch_adamw_cpu():
+    torch.manual_seed(0)
+    p = torch.randn(257, dtype=torch.float64, requires_grad=True)
+    opt = torch.optim.AdamW([p], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    pn, m, v = p.detach().numpy().copy(), np.zeros(257), np.zeros(257)
+    for step in range(1, 5):
+        g = torch.randn(257, dtype=torch.float64)
+        p.grad = g.clone()
+        opt.step()
+        pn, m, v = oracle.adamw_step(pn, g.numpy(), m, v, step, 1e-2, 0.9, 0.95, 1e-8, 0.1)
+        np.testing.assert_allclose(p.detach().numpy(), pn, rtol=1e-12, atol=1e-12)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_cuda_adamw_matches_oracle_and_torch(dtype):
+    from bastile_b200.optim import AdamW
+
+    torch.manual_seed(1)
+    shapes = [(4096,), (128,), (300, 1000), (1024, 4096), (7,), (65536,), (65537,)]
+    params = [torch.randn(s, device="cuda").to(dtype).requires_grad_(True) for s in shapes]
+    ref_params = [p.detach().clone().requires_grad_(True) for p in params]
+    hp = dict(lr=3e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.05)
+    ours, ref = AdamW(params, **hp), torch.optim.AdamW(ref_params, **hp)
+    state = [(p.detach().double().cpu().numpy(), np.zeros(s), np.zeros(s)) for p, s in zip(params, shapes)]
+    for step in range(1, 4):
+        for i, (p, r) in enumerate(zip(params, ref_params)):
+            g = torch.randn_like(p)
+            p.grad, r.grad = g.clone(), g.clone()
+            if dtype == torch.float32:
+                state[i] = oracle.adamw_step(*state[i][:1], g.double().cpu().numpy(), *state[i][1:], step, hp["lr"], 0.9,
+                                             0.95, 1e-8, 0.05)
+        ours.step()
+        ref.step()
+    for i, (p, r) in enumerate(zip(params, ref_params)):
+        if dtype == torch.float32:
+            assert_close(p, state[i][0], what=f"param {i} vs oracle", rtol=1e-5, atol=1e-6)
+            assert_close(ours.state[p]["exp_avg_sq"], state[i][2], what=f"v {i}", rtol=1e-5, atol=1e-7)
+            assert_close(p, r, what=f"param {i} vs torch", rtol=1e-5, atol=1e-6)
+        else:  # bf16 storage: one ulp of rounding per step on both sides
+            assert_close(p, r, what=f"param {i} vs torch", rtol=2e-2, atol=2e-2)
+            assert_close(ours.state[p]["exp_avg"], ref.state[r]["exp_avg"], what=f"m {i}", rtol=2e-2, atol=2e-3)
+    assert set(ours.state[params[0]]) == {"step", "exp_avg", "exp_avg_sq"}

@@ -38,12 +38,6 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 int sm_count();  // cached per device (c_api.cu)
 
 // ---------------------------------------------------------------- 16-byte vectors
-template <typename T>
-struct Vec16 {
-  static constexpr int kElems = 16 / sizeof(T);
-  uint4 raw;
-};
-
 __device__ __forceinline__ uint4 ld_global_v4(const void* p) {
   return *reinterpret_cast<const uint4*>(p);
 }

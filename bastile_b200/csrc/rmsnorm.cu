@@ -3,14 +3,14 @@
 // scaled write-back.
 //
 // Layouts
-//   rows kernel : a group of LPR lanes (8..32) owns one row, VPT 16-byte vectors
-//                 per lane; a 256-thread CTA works on 256/LPR rows x RPI at a
-//                 time and strides over the matrix persistently.  Row sums are
-//                 warp shuffles only - no shared memory, no __syncthreads.
-//   block kernel: (backward, wide rows) all 256 threads share one row so that a
-//                 thread owns a fixed set of columns and can keep its slice of
-//                 dw in registers across the rows it visits.
-//   generic     : any N / alignment, scalar accesses; correctness net only.
+//   rows kernel  : (rows of up to 2 KB, e.g. the 128-wide q/k norms) a group of LPR
+//                  lanes (8..32) owns one row, VPT 16-byte vectors per lane in
+//                  registers; a 256-thread CTA works on 256/LPR rows x RPI at a
+//                  time.  Row sums are warp shuffles only.
+//   staged kernel: (rows of 2..16 KB, e.g. hidden 4096) rows stream through a
+//                  shared-memory ring filled by bulk asynchronous copies
+//                  (rmsnorm_staged.cuh).
+//   generic      : any N / alignment, scalar accesses; correctness net only.
 //
 // dw is accumulated as fp32 partial sums: registers -> shared -> one global
 // atomic per column per CTA into a zeroed scratch row; the last CTA to finish
@@ -232,117 +232,6 @@ rms_bwd_rows(const T* __restrict__ dy, const T* __restrict__ x, const T* __restr
   dw_finalize<T>(ws, dw, N, gridDim.x, threadIdx.x, kThreads);
 }
 
-// Wide rows: one row is spread over the whole CTA, R rows per iteration.
-template <typename T, int VPT, int R>
-__global__ void __launch_bounds__(kThreads, 2)
-rms_bwd_block(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
-              const float* __restrict__ rstd, T* __restrict__ dx, T* __restrict__ dw,
-              float* __restrict__ ws, int64_t M, int N, int64_t ld_dy, int64_t ld_x,
-              int64_t ld_dx) {
-  constexpr int E = Cvt<T>::N;
-  constexpr int kWarps = kThreads / 32;
-  __shared__ float s_red[2][kWarps][R];
-  const int nv = N / E;
-  const float inv_n = 1.0f / static_cast<float>(N);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  float wf[VPT][E];
-  float acc[VPT][E];
-#pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int v = threadIdx.x + i * kThreads;
-    uint4 wv = (v < nv) ? ld_global_v4(w + static_cast<int64_t>(v) * E) : make_uint4(0, 0, 0, 0);
-    Cvt<T>::unpack(wv, wf[i]);
-#pragma unroll
-    for (int e = 0; e < E; ++e) acc[i][e] = 0.f;
-  }
-
-  int buf = 0;
-  for (int64_t base = static_cast<int64_t>(blockIdx.x) * R; base < M;
-       base += static_cast<int64_t>(gridDim.x) * R, buf ^= 1) {
-    uint4 xv[R][VPT], gv[R][VPT];
-    float rs[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int64_t row = base + r;
-      rs[r] = (row < M) ? rstd[row] : 0.f;
-#pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int v = threadIdx.x + i * kThreads;
-        const bool ok = (row < M && v < nv);
-        xv[r][i] = ok ? ld_stream_v4(x + row * ld_x + static_cast<int64_t>(v) * E)
-                      : make_uint4(0, 0, 0, 0);
-        gv[r][i] = ok ? ld_stream_v4(dy + row * ld_dy + static_cast<int64_t>(v) * E)
-                      : make_uint4(0, 0, 0, 0);
-      }
-    }
-    float dot[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      float d = 0.f;
-#pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        float xf[E], gf[E];
-        Cvt<T>::unpack(xv[r][i], xf);
-        Cvt<T>::unpack(gv[r][i], gf);
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-          const float xh = xf[e] * rs[r];
-          d = fmaf(xh, gf[e] * wf[i][e], d);
-          acc[i][e] = fmaf(gf[e], xh, acc[i][e]);
-        }
-      }
-      d = group_sum<32>(d);
-      if (lane == 0) s_red[buf][warp][r] = d;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      float d = 0.f;
-#pragma unroll
-      for (int k = 0; k < kWarps; ++k) d += s_red[buf][k][r];
-      dot[r] = d * inv_n;
-#pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        forget_unpacked(xv[r][i]);
-        forget_unpacked(gv[r][i]);
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int64_t row = base + r;
-      if (row < M) {
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-          const int v = threadIdx.x + i * kThreads;
-          if (v < nv) {
-            float xf[E], gf[E], o[E];
-            Cvt<T>::unpack(xv[r][i], xf);
-            Cvt<T>::unpack(gv[r][i], gf);
-#pragma unroll
-            for (int e = 0; e < E; ++e) {
-              const float xh = xf[e] * rs[r];
-              o[e] = (gf[e] * wf[i][e] - xh * dot[r]) * rs[r];
-            }
-            st_global_v4(dx + row * ld_dx + static_cast<int64_t>(v) * E, Cvt<T>::pack(o));
-          }
-        }
-      }
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int v = threadIdx.x + i * kThreads;
-    if (v < nv) {
-#pragma unroll
-      float* d = ws + static_cast<int64_t>(blockIdx.x % dw_copies(N)) * N + v * E;
-#pragma unroll
-      for (int e = 0; e < E; e += 4) red_add_v4(d + e, acc[i][e], acc[i][e + 1], acc[i][e + 2], acc[i][e + 3]);
-    }
-  }
-  dw_finalize<T>(ws, dw, N, gridDim.x, threadIdx.x, kThreads);
-}
-
 // Generic backward, part 1: dx, one CTA per row (scalar).
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
@@ -426,13 +315,14 @@ int fwd_t(const void* x, const void* w, void* y, float* rstd, int64_t M, int64_t
   T* yp = static_cast<T*>(y);
   RowCfg c{};
   const bool vec_ok = (N % E == 0) && (ld_x % E == 0) && (ld_y % E == 0) && aligned16(x) &&
-                      aligned16(w) && aligned16(y) && pick_rows(N / E, 16, &c);
-  if (!vec_ok) {
+                      aligned16(w) && aligned16(y);
+  const bool staged_ok = vec_ok && N / E > 128 && N / E <= 4 * staged::kThreads;
+  if (!vec_ok || (!staged_ok && !pick_rows(N / E, 4, &c))) {
     rms_fwd_generic<T><<<grid_for(M, 8), kThreads, 0, s>>>(xp, wp, yp, rstd, M, N, ld_x, ld_y, eps);
     BT_CHECK_LAUNCH("rms_fwd_generic");
     return BT_OK;
   }
-  if (N / E > 128 && N / E <= 4 * staged::kThreads) {
+  if (staged_ok) {
     const int64_t nv = N / E;
     const int vpt = nv <= staged::kThreads ? 1 : (nv <= 2 * staged::kThreads ? 2 : 4);
 #define BT_FWDS(V, R)                                                                            \
@@ -467,8 +357,6 @@ int fwd_t(const void* x, const void* w, void* y, float* rstd, int64_t M, int64_t
   BT_FWD(32, 1, 4)
   BT_FWD(32, 2, 2)
   BT_FWD(32, 4, 1)
-  BT_FWD(32, 8, 1)
-  BT_FWD(32, 16, 1)
 #undef BT_FWD
   set_error("rmsnorm_fwd: no kernel for lpr=%d vpt=%d", c.lpr, c.vpt);
   return BT_ERR_ARG;
@@ -526,21 +414,6 @@ int bwd_t(const void* dy, const void* x, const void* w, const float* rstd, void*
     BT_BWD(32, 2, 2)
     BT_BWD(32, 4, 1)
 #undef BT_BWD
-  }
-  if (vec_ok && nv <= static_cast<int64_t>(kThreads) * 4) {
-    const int vpt = nv <= kThreads ? 1 : (nv <= 2 * kThreads ? 2 : 4);
-#define BT_BWDB(V, R)                                                                          \
-  if (vpt == V) {                                                                              \
-    const int grid = grid_for(ceil_div(M, R), 2);                                              \
-    rms_bwd_block<T, V, R><<<grid, kThreads, 0, s>>>(gp, xp, wp, rstd, dxp, dwp, wsp, M,       \
-                                                     static_cast<int>(N), ld_dy, ld_x, ld_dx); \
-    BT_CHECK_LAUNCH("rms_bwd_block");                                                          \
-    return BT_OK;                                                                              \
-  }
-    BT_BWDB(1, 4)
-    BT_BWDB(2, 4)
-    BT_BWDB(4, 2)
-#undef BT_BWDB
   }
   rms_bwd_dx_generic<T><<<grid_for(M, 8), kThreads, 0, s>>>(gp, xp, wp, rstd, dxp, M, N, ld_dy,
                                                             ld_x, ld_dx);

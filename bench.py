@@ -3,13 +3,14 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-One "step" is a full training step (forward, backward, AdamW) of a random-init
+One "step" is a full training step (forward, backward, AdamW step) of a random-init
 Qwen3-8B-shaped model (36 layers, hidden 4096, 32/8 heads, head_dim 128,
 intermediate 12288, vocab 151936, bf16) on one sequence of 8192 synthetic tokens,
 with RMSNorm, RoPE, the SwiGLU MLP and the fused lm_head + cross-entropy running on
-the bastile_b200 kernels (everything else - attention, q/k/v/o projections, the
-optimizer - is stock PyTorch, as in the reference's own benchmark
-tests/benchmarks/e2e/qwen_8b_seqlen.py:80-203).  With N > 1 (launched by torchrun,
+the bastile_b200 kernels and the optimizer step on bastile_b200.optim.AdamW (--optimizer torch
+selects torch.optim.AdamW as in the reference's own benchmark,
+tests/benchmarks/e2e/qwen_8b_seqlen.py:80-203); attention and the q/k/v/o projections are
+stock PyTorch.  With N > 1 (launched by torchrun,
 one rank per GPU) every rank steps its own sequence and gradients are averaged by
 DistributedDataParallel over NCCL: weak scaling by tokens.
 
@@ -365,7 +366,7 @@ def main():
     ap.add_argument("--seq", type=int, default=SEQ_LEN)
     ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
     ap.add_argument("--intermediate", type=int, default=QWEN3_8B["intermediate_size"],
-                    help="MLP width (the reference's chart used 14336; BASELINE.json and Qwen3-8B use 12288)")
+                    help="MLP width (the reference's chart used 14336; Qwen3-8B itself has 12288)")
     ap.add_argument("--fsdp", action="store_true",
                     help="N > 1: FullyShardedDataParallel FULL_SHARD with bf16 mixed precision, wrapped per decoder layer "
                          "(the reference's tests/benchmarks/e2e/qwen_8b_fsdp.py:161-168) instead of DDP")

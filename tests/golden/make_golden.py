@@ -1,6 +1,6 @@
 """Generate the golden fixtures in this directory.  Run where the reference checkout
-exists:  ``python tests/golden/make_golden.py [path-to-reference]``
-(default ``/root/reference``).  The fixtures are what the tests read; this script is
+exists:  ``python tests/golden/make_golden.py <path-to-reference-checkout>``
+(or set ``BASTILE_REFERENCE``).  The fixtures are what the tests read; this script is
 kept so that they can be regenerated and audited.
 
 Sources of truth, per fixture
@@ -21,6 +21,7 @@ Sources of truth, per fixture
 from __future__ import annotations
 
 import json
+import os
 import sys
 from pathlib import Path
 
@@ -28,7 +29,7 @@ import numpy as np
 import torch
 
 HERE = Path(__file__).resolve().parent
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("BASTILE_REFERENCE", "reference"))
 
 
 def tiny_qwen3_inputs():

@@ -48,5 +48,17 @@ def warmup_all_kernels(batch_size: int = 4, seq_len: int = 512, hidden_size: int
         for _ in range(3):
             swiglu(gate, up)
         torch.cuda.synchronize()
+        if dtype in (torch.bfloat16, torch.float16):
+            # one small launch of the tensor-core kernels: resolves the tensor-map driver entry
+            # point and sets the shared-memory attributes before the first training step
+            from .ops.fused_linear_cross_entropy import fused_linear_cross_entropy
+            from .ops.swiglu import SwiGLUMLPFunction
+
+            xs = torch.randn(256, 256, dtype=dtype, device=device)
+            wg = torch.randn(512, 256, dtype=dtype, device=device)
+            wd = torch.randn(256, 512, dtype=dtype, device=device)
+            SwiGLUMLPFunction.apply(xs, wg, wg, wd)
+            fused_linear_cross_entropy(xs, wg, torch.zeros(256, dtype=torch.int64, device=device))
+            torch.cuda.synchronize()
     except Exception as exc:
         logging.getLogger(__name__).debug("Warmup skipped: %s", exc)

@@ -129,7 +129,13 @@ def cpu_reference_sample(seq: int = 256, threads: int | None = None):
     import bastile_b200
 
     bastile_b200.reset()  # the path the patches replace: HF eager
-    if threads:
+    if threads is None:
+        # torchrun exports OMP_NUM_THREADS=1; the CPU arm should use every core it may run on
+        try:
+            threads = len(os.sched_getaffinity(0))
+        except AttributeError:
+            threads = os.cpu_count() or 1
+    if threads and threads != torch.get_num_threads():
         torch.set_num_threads(threads)
     cfg = Qwen3Config(**QWEN3_8B)
     cfg._attn_implementation = "sdpa"

@@ -53,6 +53,20 @@ __device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
 __device__ __forceinline__ void st_global_v4(void* p, uint4 v) {
   *reinterpret_cast<uint4*>(p) = v;
 }
+// Cache-streaming forms (evict-first in L1 and L2) for large tensors that a kernel touches
+// once while other data - GEMM operand tiles - should stay resident in L2.
+__device__ __forceinline__ uint4 ld_once_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_once_v4(void* p, uint4 v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
 
 // unpack / pack one 16-byte vector to fp32 lanes
 template <typename T>

@@ -105,7 +105,7 @@ __device__ __forceinline__ void store_row32(T* dst, const float (&v)[32], int va
       float f[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) f[e] = v[i * 8 + e];
-      st_global_v4(dst + i * 8, Cvt<T>::pack(f));
+      st_once_v4(dst + i * 8, Cvt<T>::pack(f));
     }
   } else {
 #pragma unroll
@@ -132,7 +132,7 @@ __device__ __forceinline__ void load_row32(const T* src, float (&v)[32], int val
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       float f[8];
-      Cvt<T>::unpack(ld_global_v4(src + i * 8), f);
+      Cvt<T>::unpack(ld_once_v4(src + i * 8), f);
 #pragma unroll
       for (int e = 0; e < 8; ++e) v[i * 8 + e] = f[e];
     }

@@ -21,28 +21,43 @@ struct Hyper {
   float lr, beta1, beta2, eps, wd, inv_bc1, inv_sqrt_bc2;
 };
 
-template <typename T>
-__device__ __forceinline__ void update_vec(T* __restrict__ p, const T* __restrict__ g,
-                                           T* __restrict__ m, T* __restrict__ v, int64_t off,
-                                           const Hyper& h) {
+// U 16-byte vectors per thread, `stride` vectors apart: all 4*U loads are issued before the
+// first use.
+template <typename T, int U>
+__device__ __forceinline__ void update_vecs(T* __restrict__ p, const T* __restrict__ g,
+                                            T* __restrict__ m, T* __restrict__ v, int64_t first,
+                                            int64_t stride, const Hyper& h) {
   constexpr int E = Cvt<T>::N;
-  float pf[E], gf[E], mf[E], vf[E];
-  Cvt<T>::unpack(ld_stream_v4(p + off), pf);
-  Cvt<T>::unpack(ld_stream_v4(g + off), gf);
-  Cvt<T>::unpack(ld_stream_v4(m + off), mf);
-  Cvt<T>::unpack(ld_stream_v4(v + off), vf);
+  uint4 pr[U], gr[U], mr[U], vr[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int64_t off = (first + u * stride) * E;
+    pr[u] = ld_stream_v4(p + off);
+    gr[u] = ld_stream_v4(g + off);
+    mr[u] = ld_stream_v4(m + off);
+    vr[u] = ld_stream_v4(v + off);
+  }
   const float decay = 1.0f - h.lr * h.wd;
   const float step = h.lr * h.inv_bc1;
 #pragma unroll
-  for (int e = 0; e < E; ++e) {
-    mf[e] = h.beta1 * mf[e] + (1.0f - h.beta1) * gf[e];
-    vf[e] = h.beta2 * vf[e] + (1.0f - h.beta2) * gf[e] * gf[e];
-    const float denom = sqrtf(vf[e]) * h.inv_sqrt_bc2 + h.eps;
-    pf[e] = pf[e] * decay - step * (mf[e] / denom);
+  for (int u = 0; u < U; ++u) {
+    const int64_t off = (first + u * stride) * E;
+    float pf[E], gf[E], mf[E], vf[E];
+    Cvt<T>::unpack(pr[u], pf);
+    Cvt<T>::unpack(gr[u], gf);
+    Cvt<T>::unpack(mr[u], mf);
+    Cvt<T>::unpack(vr[u], vf);
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      mf[e] = h.beta1 * mf[e] + (1.0f - h.beta1) * gf[e];
+      vf[e] = h.beta2 * vf[e] + (1.0f - h.beta2) * gf[e] * gf[e];
+      const float denom = sqrtf(vf[e]) * h.inv_sqrt_bc2 + h.eps;
+      pf[e] = pf[e] * decay - step * (mf[e] / denom);
+    }
+    st_global_v4(p + off, Cvt<T>::pack(pf));
+    st_global_v4(m + off, Cvt<T>::pack(mf));
+    st_global_v4(v + off, Cvt<T>::pack(vf));
   }
-  st_global_v4(p + off, Cvt<T>::pack(pf));
-  st_global_v4(m + off, Cvt<T>::pack(mf));
-  st_global_v4(v + off, Cvt<T>::pack(vf));
 }
 
 template <typename T>
@@ -66,7 +81,9 @@ adamw_one(T* __restrict__ p, const T* __restrict__ g, T* __restrict__ m, T* __re
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
   const int64_t nvec = vec_ok ? n / E : 0;
-  for (int64_t i = tid; i < nvec; i += stride) update_vec<T>(p, g, m, v, i * E, h);
+  int64_t i = tid;
+  for (; i + stride < nvec; i += 2 * stride) update_vecs<T, 2>(p, g, m, v, i, stride, h);
+  for (; i < nvec; i += stride) update_vecs<T, 1>(p, g, m, v, i, stride, h);
   for (int64_t i = nvec * E + tid; i < n; i += stride) update_scalar<T>(p, g, m, v, i, h);
 }
 

@@ -218,15 +218,17 @@ __device__ __forceinline__ void epi_swiglu_bwd(const Params& p, uint32_t taddr, 
   const bool row_ok = row < p.M;
 #pragma unroll 1
   for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
-    float d[32];
-    ptx::tmem_ld_32cols(taddr + c * 32, d);
     const int col0 = n0 + c * 32;
     const int valid = p.N - col0;
-    if (row_ok && valid > 0) {
-      const int64_t off = row * p.ld_act + col0;
-      float g[32], u[32];
+    const bool live = row_ok && valid > 0;
+    const int64_t off = row * p.ld_act + col0;
+    float d[32], g[32], u[32];
+    if (live) {  // the global loads are in flight while the accumulator chunk is fetched
       load_row32<T>(static_cast<const T*>(p.gate) + off, g, valid, p.vec_ok);
       load_row32<T>(static_cast<const T*>(p.up) + off, u, valid, p.vec_ok);
+    }
+    ptx::tmem_ld_32cols(taddr + c * 32, d);
+    if (live) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const float dh = round_through<T>(d[j]);
@@ -235,8 +237,9 @@ __device__ __forceinline__ void epi_swiglu_bwd(const Params& p, uint32_t taddr, 
         d[j] = dh * (sg * (1.0f + g[j] * (1.0f - sg))) * u[j];  // dgate
         g[j] = dh * (g[j] * sg);                                 // dup
       }
-      store_row32<T>(static_cast<T*>(p.out) + off, d, valid, p.vec_ok);
-      store_row32<T>(static_cast<T*>(p.h) + off, g, valid, p.vec_ok);
+      const int64_t off_o = row * p.ldo + col0;  // dgate / dup may live in a wider buffer
+      store_row32<T>(static_cast<T*>(p.out) + off_o, d, valid, p.vec_ok);
+      store_row32<T>(static_cast<T*>(p.h) + off_o, g, valid, p.vec_ok);
     }
   }
 }

@@ -123,13 +123,14 @@ extern "C" int bt_mlp_fwd(const void* x, const void* wg, const void* wu, const v
 extern "C" int bt_mlp_bwd(const void* dy, const void* x, const void* wg, const void* wu,
                           const void* wd, const void* gate, const void* up, const void* h,
                           void* dgate, void* dup, void* dx, void* dwg, void* dwu, void* dwd,
-                          int64_t T, int64_t H, int64_t I, int64_t ld_x, int64_t ld_dy, int dtype,
-                          int32_t* status, void* stream) {
+                          int64_t T, int64_t H, int64_t I, int64_t ld_x, int64_t ld_dy,
+                          int64_t ld_dgate, int dtype, int32_t* status, void* stream) {
   using namespace bt;
   BT_CHECK_ARG(is16(dtype), "mlp_bwd: bf16 or fp16 only (got dtype %d)", dtype);
   BT_CHECK_ARG(T > 0, "mlp_bwd: T must be positive");
   BT_CHECK_ARG(dy && x && wg && wu && wd && gate && up && h && dgate && dup, "mlp_bwd: null pointer");
   if (int rc = check_dims("mlp_bwd", T, I, H)) return rc;
+  BT_CHECK_ARG(ld_dgate >= I, "mlp_bwd: dgate/dup row stride smaller than I");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool bf16 = dtype == BT_BF16;
   {
@@ -146,8 +147,9 @@ extern "C" int bt_mlp_bwd(const void* dy, const void* x, const void* wg, const v
     L.p.out = dgate;
     L.p.h = dup;
     L.p.ld_act = I;
-    L.p.vec_ok = rows_aligned(gate, I, 2) && rows_aligned(up, I, 2) && rows_aligned(dgate, I, 2) &&
-                 rows_aligned(dup, I, 2);
+    L.p.ldo = ld_dgate;
+    L.p.vec_ok = rows_aligned(gate, I, 2) && rows_aligned(up, I, 2) &&
+                 rows_aligned(dgate, ld_dgate, 2) && rows_aligned(dup, ld_dgate, 2);
     if (int rc = gemm::launch<gemm::EPI_SWIGLU_BWD>(L, s)) return rc;
   }
   if (dwd != nullptr) {  // dWd[H, I] = dy^T h
@@ -155,19 +157,31 @@ extern "C" int bt_mlp_bwd(const void* dy, const void* x, const void* wg, const v
                             bf16, false, nullptr, 0, nullptr, status, s))
       return rc;
   }
-  if (dwg != nullptr) {  // dWg[I, H] = dgate^T x
-    if (int rc = plain_gemm(dgate, false, I, x, false, ld_x, nullptr, 0, nullptr, 0, 0, dwg, H, I, H,
-                            T, bf16, false, nullptr, 0, nullptr, status, s))
+  // dgate | dup side by side in one [T, 2I] buffer and dWg | dWu stacked in one [2I, H] buffer:
+  // the two weight gradients are one product [dgate | dup]^T x (twice the tiles per launch,
+  // so the last wave of tiles is fuller).
+  const bool stacked = dwg != nullptr && dwu != nullptr && ld_dgate == 2 * I &&
+                       static_cast<const char*>(dup) == static_cast<const char*>(dgate) + I * 2 &&
+                       static_cast<const char*>(dwu) == static_cast<const char*>(dwg) + I * H * 2;
+  if (stacked) {
+    if (int rc = plain_gemm(dgate, false, ld_dgate, x, false, ld_x, nullptr, 0, nullptr, 0, 0, dwg, H,
+                            2 * I, H, T, bf16, false, nullptr, 0, nullptr, status, s))
       return rc;
-  }
-  if (dwu != nullptr) {  // dWu[I, H] = dup^T x
-    if (int rc = plain_gemm(dup, false, I, x, false, ld_x, nullptr, 0, nullptr, 0, 0, dwu, H, I, H, T,
-                            bf16, false, nullptr, 0, nullptr, status, s))
-      return rc;
+  } else {
+    if (dwg != nullptr) {  // dWg[I, H] = dgate^T x
+      if (int rc = plain_gemm(dgate, false, ld_dgate, x, false, ld_x, nullptr, 0, nullptr, 0, 0, dwg,
+                              H, I, H, T, bf16, false, nullptr, 0, nullptr, status, s))
+        return rc;
+    }
+    if (dwu != nullptr) {  // dWu[I, H] = dup^T x
+      if (int rc = plain_gemm(dup, false, ld_dgate, x, false, ld_x, nullptr, 0, nullptr, 0, 0, dwu, H,
+                              I, H, T, bf16, false, nullptr, 0, nullptr, status, s))
+        return rc;
+    }
   }
   if (dx != nullptr) {  // dx[T, H] = dgate Wg + dup Wu  (one accumulator, two K ranges)
-    if (int rc = plain_gemm(dgate, true, I, wg, false, H, dup, I, wu, H, I, dx, H, T, H, I, bf16,
-                            false, nullptr, 0, nullptr, status, s))
+    if (int rc = plain_gemm(dgate, true, ld_dgate, wg, false, H, dup, ld_dgate, wu, H, I, dx, H, T, H,
+                            I, bf16, false, nullptr, 0, nullptr, status, s))
       return rc;
   }
   return BT_OK;

@@ -120,22 +120,31 @@ class SwiGLUMLPFunction(torch.autograd.Function):
             dy = dy.to(x2.dtype)
         dy2 = _rows(dy)
         need_x, need_g, need_u, need_d = ctx.needs_input_grad
-        dgate = torch.empty_like(gate)
-        dup = torch.empty_like(up)
+        # dgate | dup share one [T, 2I] buffer and dWg | dWu one [2I, H] buffer, so that the
+        # library can compute both weight gradients as a single product
+        dgu = torch.empty((t, 2 * inter), dtype=gate.dtype, device=dev)
+        dgate, dup = dgu[:, :inter], dgu[:, inter:]
         dx = torch.empty_like(x2, memory_format=torch.contiguous_format) if need_x else None
-        dwg = torch.empty_like(wg) if need_g else None
-        dwu = torch.empty_like(wu) if need_u else None
+        dwg = dwu = None
+        if need_g and need_u:
+            dwgu = torch.empty((2 * inter, hidden), dtype=wg.dtype, device=dev)
+            dwg, dwu = dwgu[:inter], dwgu[inter:]
+        elif need_g:
+            dwg = torch.empty_like(wg)
+        elif need_u:
+            dwu = torch.empty_like(wu)
         dwd = torch.empty_like(wd) if need_d else None
         st = _lib.status_word(dev)
 
         def p(tensor):
             return tensor.data_ptr() if tensor is not None else None
 
-        n_k = 1 + sum(t is not None for t in (dx, dwg, dwu, dwd))
+        n_k = 1 + sum(t is not None for t in (dx, dwd)) + (1 if (dwg is not None and dwu is not None) else
+                                                           int(dwg is not None) + int(dwu is not None))
         with _lib.device_of(dev), _lib.timed("mlp_bwd", n_k, dev):
             rc = lib.bt_mlp_bwd(dy2.data_ptr(), x2.data_ptr(), wg.data_ptr(), wu.data_ptr(), wd.data_ptr(),
                                 gate.data_ptr(), up.data_ptr(), h.data_ptr(), dgate.data_ptr(), dup.data_ptr(),
-                                p(dx), p(dwg), p(dwu), p(dwd), t, hidden, inter, _ld(x2), _ld(dy2),
+                                p(dx), p(dwg), p(dwu), p(dwd), t, hidden, inter, _ld(x2), _ld(dy2), 2 * inter,
                                 _lib.dtype_code(x2.dtype), st.data_ptr(), _lib.stream_ptr(dev))
         _lib.check(rc, "bt_mlp_bwd")
         dts = ctx.w_dtypes

@@ -176,13 +176,16 @@ int bt_mlp_fwd(const void* x, const void* wg, const void* wu, const void* wd,
  * plus swiglu_backward_kernel :53-90):
  *   dh = dy Wd (epilogue turns it into dgate, dup using saved gate/up),
  *   dWd = dy^T h, dWg = dgate^T x, dWu = dup^T x, dx = dgate Wg + dup Wu.
- * dgate/dup [T,I] are caller-owned scratch.  Any of dx, dwg, dwu, dwd may be
- * NULL to skip that product. */
+ * dgate/dup [T,I] are caller-owned scratch with row stride ld_dgate.  Any of
+ * dx, dwg, dwu, dwd may be NULL to skip that product.  When dup starts I
+ * elements after dgate in one [T, 2I] buffer (ld_dgate = 2I) and dwu starts
+ * I*H elements after dwg, the two weight gradients are computed as ONE product
+ * [dgate | dup]^T x. */
 int bt_mlp_bwd(const void* dy, const void* x, const void* wg, const void* wu,
                const void* wd, const void* gate, const void* up, const void* h,
                void* dgate, void* dup, void* dx, void* dwg, void* dwu, void* dwd,
                int64_t T, int64_t H, int64_t I, int64_t ld_x, int64_t ld_dy,
-               int dtype, int32_t* status, void* stream);
+               int64_t ld_dgate, int dtype, int32_t* status, void* stream);
 
 /* ------------------------------------------- fused lm_head + cross-entropy  */
 

@@ -217,3 +217,33 @@ def test_mlp_full_size_linearity_and_sampled_rows():
     y2 = SwiGLUMLPFunction.apply(xs2, wg, wu, wd)
     y2.backward(dy * 2)
     assert_close(xs2.grad, xs.grad.float() * 2, what="linearity", rtol=1e-2, atol=1e-2)
+
+
+def test_mlp_bwd_c_abi_with_separate_buffers_and_skipped_outputs():
+    """bt_mlp_bwd called directly: dgate/dup and dWg/dWu in unrelated buffers (no stacked product),
+    dWu skipped with NULL - results must equal the autograd path that uses the stacked buffers."""
+    from bastile_b200 import _lib
+    from bastile_b200.ops.swiglu import SwiGLUMLPFunction
+
+    lib = _lib.get_lib()
+    t, hidden, inter = 200, 256, 640
+    x, wg, wu, wd, dy = _mlp_case(t, hidden, inter, torch.bfloat16, seed=4)
+    xs, wgs, wus, wds = (a.clone().requires_grad_(True) for a in (x, wg, wu, wd))
+    SwiGLUMLPFunction.apply(xs, wgs, wus, wds).backward(dy)
+    dev = x.device
+    gate, up, h = (torch.empty(t, inter, device=dev, dtype=torch.bfloat16) for _ in range(3))
+    y = torch.empty(t, hidden, device=dev, dtype=torch.bfloat16)
+    st = _lib.status_word(dev)
+    stream = _lib.stream_ptr(dev)
+    _lib.check(lib.bt_mlp_fwd(x.data_ptr(), wg.data_ptr(), wu.data_ptr(), wd.data_ptr(), gate.data_ptr(), up.data_ptr(),
+                              h.data_ptr(), y.data_ptr(), t, hidden, inter, hidden, 0, st.data_ptr(), stream), "fwd")
+    dgate, dup = (torch.empty(t, inter, device=dev, dtype=torch.bfloat16) for _ in range(2))
+    dx = torch.empty_like(x)
+    dwg, dwd = torch.empty_like(wg), torch.empty_like(wd)
+    _lib.check(lib.bt_mlp_bwd(dy.data_ptr(), x.data_ptr(), wg.data_ptr(), wu.data_ptr(), wd.data_ptr(), gate.data_ptr(),
+                              up.data_ptr(), h.data_ptr(), dgate.data_ptr(), dup.data_ptr(), dx.data_ptr(),
+                              dwg.data_ptr(), None, dwd.data_ptr(), t, hidden, inter, hidden, hidden, inter, 0,
+                              st.data_ptr(), stream), "bwd")
+    _lib.check_status(dev, "mlp c abi")
+    assert torch.equal(dx, xs.grad) and torch.equal(dwd, wds.grad)
+    assert_close(dwg, wgs.grad, what="dWg", rtol=1e-2, atol=1e-2 * float(wgs.grad.float().abs().max()))

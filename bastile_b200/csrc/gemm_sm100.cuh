@@ -33,7 +33,8 @@ namespace gemm {
 
 constexpr int BM = 128;
 constexpr int BN = 256;
-constexpr int BK = 64;
+constexpr int BK = 64;       // k-block in 16-bit elements; every k-block is 128 bytes of K per row
+constexpr int kRowBytes = 128;
 constexpr int kStages = 4;
 constexpr int kEpiWarps = 8;  // two warps per 32-lane TMEM quarter, each takes half of the columns
 constexpr int kThreads = 64 + 32 * kEpiWarps;
@@ -43,7 +44,6 @@ constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = 512;
 constexpr int kGroupM = 16;  // tile rasterisation: walk 16 row-tiles per column-tile
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr int kBoxBytesMN = BK * 128;  // one MN-major box: 64 K rows x 128 bytes
 
 enum : int { EPI_PLAIN = 0, EPI_SWIGLU_FWD = 1, EPI_SWIGLU_BWD = 2, EPI_LCE = 3 };
 
@@ -58,7 +58,10 @@ struct Params {
   int a_kmajor, b_kmajor, dual_b;
   uint32_t idesc;
   uint64_t a_desc_hi, b_desc_hi;
-  uint32_t a_kstep, b_kstep;  // descriptor address step per 16-element K slice, 16-byte units
+  uint32_t a_kstep, b_kstep;  // descriptor address step per MMA K slice, 16-byte units
+  int bk;          // elements of K per k-block (128 bytes: 64 for 16-bit, 32 for fp32)
+  int mn_box;      // elements of M/N per MN-major box row (128 bytes)
+  int box_bytes;   // bytes of one MN-major box: bk rows of 128 bytes
   int32_t* status;
   // --- plain epilogue: out = T(alpha * (acc + addend))
   void* out;
@@ -97,9 +100,13 @@ __device__ __forceinline__ float round_through(float x) {
 }
 
 // Store 32 consecutive values of one row (vector path when the span is whole and aligned).
+__device__ __forceinline__ void store_row32_f32(float* dst, const float (&v)[32], int valid, bool vec);
+
 template <typename T>
 __device__ __forceinline__ void store_row32(T* dst, const float (&v)[32], int valid, bool vec) {
-  if (vec && valid >= 32) {
+  if constexpr (sizeof(T) == 4) {
+    store_row32_f32(dst, v, valid, vec);
+  } else if (vec && valid >= 32) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       float f[8];
@@ -128,7 +135,21 @@ __device__ __forceinline__ void store_row32_f32(float* dst, const float (&v)[32]
 }
 template <typename T>
 __device__ __forceinline__ void load_row32(const T* src, float (&v)[32], int valid, bool vec) {
-  if (vec && valid >= 32) {
+  if constexpr (sizeof(T) == 4) {
+    if (vec && valid >= 32) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint4 t = ld_once_v4(src + i * 4);
+        v[i * 4] = __uint_as_float(t.x);
+        v[i * 4 + 1] = __uint_as_float(t.y);
+        v[i * 4 + 2] = __uint_as_float(t.z);
+        v[i * 4 + 3] = __uint_as_float(t.w);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = (j < valid) ? src[j] : 0.f;
+    }
+  } else if (vec && valid >= 32) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       float f[8];
@@ -345,8 +366,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
   ptx::tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int nkb0 = (p.K0 + BK - 1) / BK;
-  const int nkb1 = (p.K1 + BK - 1) / BK;
+  const int nkb0 = (p.K0 + p.bk - 1) / p.bk;
+  const int nkb1 = (p.K1 + p.bk - 1) / p.bk;
   const int nkb = nkb0 + nkb1;
 
   if (warp == 0) {
@@ -367,7 +388,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
           }
           ptx::mbar_arrive_expect_tx(&full[stage], kStageBytes);
           const bool second = kb >= nkb0;
-          const int k0 = (second ? kb - nkb0 : kb) * BK;
+          const int k0 = (second ? kb - nkb0 : kb) * p.bk;
           const CUtensorMap* ta = second ? &tmA1 : &tmA0;
           const CUtensorMap* tb = second ? &tmB1 : &tmB0;
           uint8_t* sa = smem + stage * kStageBytes;
@@ -375,9 +396,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
           if (p.a_kmajor) {
             ptx::tma_load_2d(sa, ta, k0, m0, &full[stage]);
           } else {
-#pragma unroll
-            for (int j = 0; j < BM / 64; ++j)
-              ptx::tma_load_2d(sa + j * kBoxBytesMN, ta, m0 + j * 64, k0, &full[stage]);
+            for (int j = 0; j < BM / p.mn_box; ++j)
+              ptx::tma_load_2d(sa + j * p.box_bytes, ta, m0 + j * p.mn_box, k0, &full[stage]);
           }
           if (p.dual_b) {
             ptx::tma_load_2d(sb, &tmB0, k0, n0, &full[stage]);
@@ -385,9 +405,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
           } else if (p.b_kmajor) {
             ptx::tma_load_2d(sb, tb, k0, n0, &full[stage]);
           } else {
-#pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              ptx::tma_load_2d(sb + j * kBoxBytesMN, tb, n0 + j * 64, k0, &full[stage]);
+            for (int j = 0; j < BN / p.mn_box; ++j)
+              ptx::tma_load_2d(sb + j * p.box_bytes, tb, n0 + j * p.mn_box, k0, &full[stage]);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -422,10 +441,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
           const uint64_t a_desc = ptx::smem_desc(p.a_desc_hi, a_addr);
           const uint64_t b_desc = ptx::smem_desc(p.b_desc_hi, a_addr + kABytes);
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk)
-            ptx::umma_f16(d_tmem, a_desc + static_cast<uint64_t>(kk * p.a_kstep),
-                          b_desc + static_cast<uint64_t>(kk * p.b_kstep), p.idesc,
-                          (kb | kk) != 0 ? 1u : 0u);
+          for (int kk = 0; kk < BK / 16; ++kk) {  // 4 K slices of 32 bytes per k-block
+            if constexpr (sizeof(T) == 4)
+              ptx::umma_tf32(d_tmem, a_desc + static_cast<uint64_t>(kk * p.a_kstep),
+                             b_desc + static_cast<uint64_t>(kk * p.b_kstep), p.idesc,
+                             (kb | kk) != 0 ? 1u : 0u);
+            else
+              ptx::umma_f16(d_tmem, a_desc + static_cast<uint64_t>(kk * p.a_kstep),
+                            b_desc + static_cast<uint64_t>(kk * p.b_kstep), p.idesc,
+                            (kb | kk) != 0 ? 1u : 0u);
+          }
           ptx::umma_commit(&empty[stage]);  // frees the smem stage when these MMAs retire
           if (++stage == kStages) {
             stage = 0;
@@ -531,8 +556,8 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
   ptx::tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int nkb0 = (p.K0 + BK - 1) / BK;
-  const int nkb1 = (p.K1 + BK - 1) / BK;
+  const int nkb0 = (p.K0 + p.bk - 1) / p.bk;
+  const int nkb1 = (p.K1 + p.bk - 1) / p.bk;
   const int nkb = nkb0 + nkb1;
   const int pair = blockIdx.x >> 1;
   const int npairs = gridDim.x >> 1;
@@ -555,7 +580,7 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
           }
           if (leader) ptx::mbar_arrive_expect_tx(&full[stage], 2 * kStageBytes2);
           const bool second = kb >= nkb0;
-          const int k0 = (second ? kb - nkb0 : kb) * BK;
+          const int k0 = (second ? kb - nkb0 : kb) * p.bk;
           const CUtensorMap* ta = second ? &tmA1 : &tmA0;
           const CUtensorMap* tb = p.dual_b ? (rank ? &tmB1 : &tmB0) : (second ? &tmB1 : &tmB0);
           uint8_t* sa = smem + stage * kStageBytes2;
@@ -563,16 +588,14 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
           if (p.a_kmajor) {
             ptx::tma_load_2d_pair(sa, ta, k0, m0, &full[stage]);
           } else {
-#pragma unroll
-            for (int j = 0; j < BM / 64; ++j)
-              ptx::tma_load_2d_pair(sa + j * kBoxBytesMN, ta, m0 + j * 64, k0, &full[stage]);
+            for (int j = 0; j < BM / p.mn_box; ++j)
+              ptx::tma_load_2d_pair(sa + j * p.box_bytes, ta, m0 + j * p.mn_box, k0, &full[stage]);
           }
           if (p.b_kmajor) {
             ptx::tma_load_2d_pair(sb, tb, k0, n0, &full[stage]);
           } else {
-#pragma unroll
-            for (int j = 0; j < BN / 128; ++j)
-              ptx::tma_load_2d_pair(sb + j * kBoxBytesMN, tb, n0 + j * 64, k0, &full[stage]);
+            for (int j = 0; j < (BN / 2) / p.mn_box; ++j)
+              ptx::tma_load_2d_pair(sb + j * p.box_bytes, tb, n0 + j * p.mn_box, k0, &full[stage]);
           }
           if (++stage == kStages2) {
             stage = 0;
@@ -605,10 +628,16 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
           const uint64_t a_desc = ptx::smem_desc(p.a_desc_hi, a_addr);
           const uint64_t b_desc = ptx::smem_desc(p.b_desc_hi, a_addr + kABytes);
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk)
-            ptx::umma_f16_pair(d_tmem, a_desc + static_cast<uint64_t>(kk * p.a_kstep),
-                               b_desc + static_cast<uint64_t>(kk * p.b_kstep), p.idesc,
-                               (kb | kk) != 0 ? 1u : 0u);
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            if constexpr (sizeof(T) == 4)
+              ptx::umma_tf32_pair(d_tmem, a_desc + static_cast<uint64_t>(kk * p.a_kstep),
+                                  b_desc + static_cast<uint64_t>(kk * p.b_kstep), p.idesc,
+                                  (kb | kk) != 0 ? 1u : 0u);
+            else
+              ptx::umma_f16_pair(d_tmem, a_desc + static_cast<uint64_t>(kk * p.a_kstep),
+                                 b_desc + static_cast<uint64_t>(kk * p.b_kstep), p.idesc,
+                                 (kb | kk) != 0 ? 1u : 0u);
+          }
           ptx::umma_commit_pair(&empty[stage]);
           if (++stage == kStages2) {
             stage = 0;
@@ -690,15 +719,18 @@ struct Operand {
   int box_mn = 0;    // rows of the K-major box (BM, BN or BN/2)
 };
 
-inline int make_tmap(CUtensorMap* tm, const Operand& o, bool bf16, const char* what) {
+// `dtype`: BT_BF16 / BT_FP16 / BT_FP32 (fp32 operands feed the tensor cores as tf32).
+inline int make_tmap(CUtensorMap* tm, const Operand& o, int dtype, const char* what) {
+  const int esize = dtype == BT_FP32 ? 4 : 2;
+  const int row_elems = kRowBytes / esize;  // elements in one 128-byte row of a tile
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) {
     set_error("cuTensorMapEncodeTiled is not available from this driver");
     return BT_ERR_DRIVER;
   }
-  if (!aligned16(o.ptr) || (o.ld * 2) % 16 != 0) {
-    set_error("%s: operand must be 16-byte aligned with a row stride that is a multiple of 8 elements",
-              what);
+  if (!aligned16(o.ptr) || (o.ld * esize) % 16 != 0) {
+    set_error("%s: operand must be 16-byte aligned with a row stride that is a multiple of %d elements",
+              what, 16 / esize);
     return BT_ERR_ARG;
   }
   cuuint64_t dims[2];
@@ -706,19 +738,23 @@ inline int make_tmap(CUtensorMap* tm, const Operand& o, bool bf16, const char* w
   if (o.kmajor) {
     dims[0] = static_cast<cuuint64_t>(o.k);
     dims[1] = static_cast<cuuint64_t>(o.mn);
-    box[0] = BK;
+    box[0] = static_cast<cuuint32_t>(row_elems);
     box[1] = static_cast<cuuint32_t>(o.box_mn);
   } else {
     dims[0] = static_cast<cuuint64_t>(o.mn);
     dims[1] = static_cast<cuuint64_t>(o.k);
-    box[0] = 64;
-    box[1] = BK;
+    box[0] = static_cast<cuuint32_t>(row_elems);
+    box[1] = static_cast<cuuint32_t>(row_elems);  // k-block = 128 bytes of K as well
   }
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(o.ld) * 2};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(o.ld) * esize};
   const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = fn(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                        2, const_cast<void*>(o.ptr), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+  const CUtensorMapDataType dt = dtype == BT_BF16   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : dtype == BT_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                    : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  const CUresult r = fn(tm, dt, 2, const_cast<void*>(o.ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        (dtype == BT_FP32 && !o.kmajor) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                                        : CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error("%s: cuTensorMapEncodeTiled failed with CUresult %d (dims %llu x %llu, ld %lld)", what,
@@ -796,7 +832,7 @@ struct Launch {
   Operand a0, b0, a1, b1;
   bool dual_b = false;    // b1 is the second half of the B tile (same K range as pair 0)
   bool two_pairs = false; // (a1, b1) is a second contraction into the same accumulator
-  bool bf16 = true;
+  int dtype = BT_BF16;    // storage of the operands: BT_BF16, BT_FP16 or BT_FP32 (tf32 math)
   Params p{};
 };
 
@@ -831,19 +867,28 @@ int launch(Launch& L, cudaStream_t s) {
   p.a_kmajor = L.a0.kmajor;
   p.b_kmajor = L.b0.kmajor;
   p.dual_b = L.dual_b ? 1 : 0;
-  p.idesc = ptx::make_idesc_f16(L.bf16, !L.a0.kmajor, !L.b0.kmajor, pair ? 2 * BM : BM, BN);
-  p.a_desc_hi = ptx::make_smem_desc_hi(L.a0.kmajor != 0, kBoxBytesMN);
-  p.b_desc_hi = ptx::make_smem_desc_hi(L.b0.kmajor != 0, kBoxBytesMN);
-  p.a_kstep = L.a0.kmajor ? (32u >> 4) : (16u * 128u >> 4);
-  p.b_kstep = L.b0.kmajor ? (32u >> 4) : (16u * 128u >> 4);
+  const int esize = L.dtype == BT_FP32 ? 4 : 2;
+  p.bk = kRowBytes / esize;
+  p.mn_box = kRowBytes / esize;
+  p.box_bytes = p.bk * kRowBytes;
+  const uint32_t fmt = L.dtype == BT_FP16 ? 0u : (L.dtype == BT_BF16 ? 1u : 2u);
+  p.idesc = ptx::make_idesc(fmt, !L.a0.kmajor, !L.b0.kmajor, pair ? 2 * BM : BM, BN);
+  p.a_desc_hi = ptx::make_smem_desc_hi(L.a0.kmajor != 0, static_cast<uint32_t>(p.box_bytes),
+                                       esize == 4 && !L.a0.kmajor);
+  p.b_desc_hi = ptx::make_smem_desc_hi(L.b0.kmajor != 0, static_cast<uint32_t>(p.box_bytes),
+                                       esize == 4 && !L.b0.kmajor);
+  // one MMA consumes 32 bytes of K: 32 bytes along a K-major row, or 32/esize rows of 128 bytes
+  const uint32_t mn_step = static_cast<uint32_t>((32 / esize) * kRowBytes) >> 4;
+  p.a_kstep = L.a0.kmajor ? (32u >> 4) : mn_step;
+  p.b_kstep = L.b0.kmajor ? (32u >> 4) : mn_step;
   // K-major boxes: a CTA of a pair stages 128 rows of A and 128 of the tile's 256 B rows
   const int b_box = pair ? BN / 2 : n_tile;
   L.a0.box_mn = BM;
   L.b0.box_mn = b_box;
   CUtensorMap ta0, tb0, ta1, tb1;
   int rc;
-  if ((rc = make_tmap(&ta0, L.a0, L.bf16, "gemm A")) != BT_OK) return rc;
-  if ((rc = make_tmap(&tb0, L.b0, L.bf16, "gemm B")) != BT_OK) return rc;
+  if ((rc = make_tmap(&ta0, L.a0, L.dtype, "gemm A")) != BT_OK) return rc;
+  if ((rc = make_tmap(&tb0, L.b0, L.dtype, "gemm B")) != BT_OK) return rc;
   ta1 = ta0;
   tb1 = tb0;
   if (L.two_pairs) {
@@ -853,21 +898,28 @@ int launch(Launch& L, cudaStream_t s) {
     }
     L.a1.box_mn = BM;
     L.b1.box_mn = b_box;
-    if ((rc = make_tmap(&ta1, L.a1, L.bf16, "gemm A1")) != BT_OK) return rc;
-    if ((rc = make_tmap(&tb1, L.b1, L.bf16, "gemm B1")) != BT_OK) return rc;
+    if ((rc = make_tmap(&ta1, L.a1, L.dtype, "gemm A1")) != BT_OK) return rc;
+    if ((rc = make_tmap(&tb1, L.b1, L.dtype, "gemm B1")) != BT_OK) return rc;
   } else if (L.dual_b) {
     if (!L.b0.kmajor || !L.b1.kmajor) {
       set_error("gemm: dual-B mode needs K-major B operands");
       return BT_ERR_ARG;
     }
     L.b1.box_mn = b_box;
-    if ((rc = make_tmap(&tb1, L.b1, L.bf16, "gemm B1")) != BT_OK) return rc;
+    if ((rc = make_tmap(&tb1, L.b1, L.dtype, "gemm B1")) != BT_OK) return rc;
   }
-  if (pair)
-    return L.bf16 ? launch_pair_t<EPI, __nv_bfloat16>(ta0, tb0, ta1, tb1, p, s)
-                  : launch_pair_t<EPI, __half>(ta0, tb0, ta1, tb1, p, s);
-  return L.bf16 ? launch_t<EPI, __nv_bfloat16>(ta0, tb0, ta1, tb1, p, s)
-                : launch_t<EPI, __half>(ta0, tb0, ta1, tb1, p, s);
+  if (pair) {
+    switch (L.dtype) {
+      case BT_BF16: return launch_pair_t<EPI, __nv_bfloat16>(ta0, tb0, ta1, tb1, p, s);
+      case BT_FP16: return launch_pair_t<EPI, __half>(ta0, tb0, ta1, tb1, p, s);
+      default: return launch_pair_t<EPI, float>(ta0, tb0, ta1, tb1, p, s);
+    }
+  }
+  switch (L.dtype) {
+    case BT_BF16: return launch_t<EPI, __nv_bfloat16>(ta0, tb0, ta1, tb1, p, s);
+    case BT_FP16: return launch_t<EPI, __half>(ta0, tb0, ta1, tb1, p, s);
+    default: return launch_t<EPI, float>(ta0, tb0, ta1, tb1, p, s);
+  }
 }
 
 }  // namespace gemm

@@ -209,9 +209,10 @@ extern "C" int bt_lce_dlogits(void* logits, const float* row_stats, const int64_
   if (rows == 0) return BT_OK;
   BT_CHECK_ARG(logits && row_stats && labels && grad_scale && (!write_loss || loss_row),
                "lce_dlogits: null pointer");
-  BT_CHECK_ARG(dtype == BT_BF16 || dtype == BT_FP16, "lce_dlogits: bf16 or fp16 only");
-  BT_CHECK_ARG(aligned16(logits) && ld_logits % 8 == 0 && ld_logits >= (V + 7) / 8 * 8,
-               "lce_dlogits: logits rows must be 16-byte aligned and padded to 8 elements");
+  BT_CHECK_ARG(dtype == BT_BF16 || dtype == BT_FP16 || dtype == BT_FP32, "lce_dlogits: unknown dtype");
+  const int64_t vec = dtype == BT_FP32 ? 4 : 8;
+  BT_CHECK_ARG(aligned16(logits) && ld_logits % vec == 0 && ld_logits >= (V + vec - 1) / vec * vec,
+               "lce_dlogits: logits rows must be 16-byte aligned and padded to whole 16-byte vectors");
   const int sms = sm_count();
   // enough CTAs for ~8 per SM: split rows into column segments when there are few rows
   int64_t gx = rows < static_cast<int64_t>(sms) * 8 ? rows : static_cast<int64_t>(sms) * 8;
@@ -224,11 +225,16 @@ extern "C" int bt_lce_dlogits(void* logits, const float* row_stats, const int64_
     lce_dlogits_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(
         static_cast<__nv_bfloat16*>(logits), row_stats, labels, loss_row, grad_scale, rows, V,
         ld_logits, v_offset, ignore_index, write_loss);
-  else
+  else if (dtype == BT_FP16)
     lce_dlogits_kernel<__half><<<grid, kThreads, 0, s>>>(static_cast<__half*>(logits), row_stats,
                                                          labels, loss_row, grad_scale, rows, V,
                                                          ld_logits, v_offset, ignore_index,
                                                          write_loss);
+  else
+    lce_dlogits_kernel<float><<<grid, kThreads, 0, s>>>(static_cast<float*>(logits), row_stats,
+                                                        labels, loss_row, grad_scale, rows, V,
+                                                        ld_logits, v_offset, ignore_index,
+                                                        write_loss);
   BT_CHECK_LAUNCH("lce_dlogits");
   return BT_OK;
 }

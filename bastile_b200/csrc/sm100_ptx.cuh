@@ -130,6 +130,16 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same with fp32 operands read as tf32 (K = 8 per instruction).
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on `bar` once every tcgen05.mma issued so far by this thread is done.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
@@ -210,6 +220,15 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, 
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive, once all MMAs issued so far have retired, on the mbarrier at this offset in BOTH
 // CTAs of the pair (an mbarrier arrive fanned out to two CTAs; no data moves).
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
@@ -222,27 +241,32 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 }
 
 // ---------------------------------------------------------------- descriptors
-// Instruction descriptor of tcgen05.mma kind::f16 with fp32 accumulation:
-//   [4,6) D format (1 = f32)   [7,10) A format   [10,13) B format (0 = f16, 1 = bf16)
+// Instruction descriptor of tcgen05.mma kind::f16 / kind::tf32 with fp32 accumulation:
+//   [4,6) D format (1 = f32)   [7,10) A format   [10,13) B format (0 = f16, 1 = bf16, 2 = tf32)
 //   [15] A is MN-major   [16] B is MN-major   [17,23) N >> 3   [24,29) M >> 4
-__host__ __device__ constexpr uint32_t make_idesc_f16(bool bf16, bool a_mn_major, bool b_mn_major,
-                                                      int m, int n) {
-  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) |
+// `fmt`: 0 = f16, 1 = bf16, 2 = tf32 (fp32 storage) for both operands.
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, bool a_mn_major, bool b_mn_major,
+                                                  int m, int n) {
+  return (1u << 4) | (fmt << 7) | (fmt << 10) |
          ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, tile rows of 128 bytes:
 //   [0,14) address >> 4   [16,30) leading byte offset >> 4   [32,46) stride byte offset >> 4
-//   [46,48) version = 1   [61,64) layout = 2 (SWIZZLE_128B)
+//   [46,48) version = 1   [61,64) layout = 2 (SWIZZLE_128B) or 1 (SWIZZLE_128B, 32-byte atoms)
 // K-major tile  (rows = M/N index, 64 K elements per row): 8-row groups 1024 B apart (SBO),
 //               LBO unused.
 // MN-major tile (rows = K index, 64 M/N elements per row): 8-row K groups 1024 B apart (SBO),
 //               64-element M/N blocks `mn_block_bytes` apart (LBO).
-__host__ __device__ constexpr uint64_t make_smem_desc_hi(bool k_major, uint32_t mn_block_bytes) {
+// `fp32_mn_major`: MN-major tiles of 32-bit elements use the "128-byte swizzle with 32-byte
+// atoms" layout (type 1; TMA mode SWIZZLE_128B_ATOM_32B), whose K groups are 4 rows (512 B).
+__host__ __device__ constexpr uint64_t make_smem_desc_hi(bool k_major, uint32_t mn_block_bytes,
+                                                         bool fp32_mn_major = false) {
   const uint64_t lbo = k_major ? 1u : (mn_block_bytes >> 4);
-  const uint64_t sbo = 1024u >> 4;
-  return (lbo << 16) | (sbo << 32) | (1ull << 46) | (2ull << 61);
+  const uint64_t sbo = (fp32_mn_major ? 512u : 1024u) >> 4;
+  const uint64_t layout = fp32_mn_major ? 1u : 2u;
+  return (lbo << 16) | (sbo << 32) | (1ull << 46) | (layout << 61);
 }
 __device__ __forceinline__ uint64_t smem_desc(uint64_t hi, uint32_t smem_addr) {
   return hi | static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);

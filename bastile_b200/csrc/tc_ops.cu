@@ -9,7 +9,9 @@ namespace {
 using gemm::Launch;
 using gemm::Operand;
 
-bool is16(int dtype) { return dtype == BT_BF16 || dtype == BT_FP16; }
+// operand storage the tensor-core kernels take: 16-bit floats, or fp32 read as tf32
+bool is_tc(int dtype) { return dtype == BT_BF16 || dtype == BT_FP16 || dtype == BT_FP32; }
+int esize(int dtype) { return dtype == BT_FP32 ? 4 : 2; }
 
 Operand operand(const void* ptr, bool kmajor, int64_t mn, int64_t k, int64_t ld) {
   Operand o;
@@ -36,11 +38,12 @@ int check_dims(const char* what, int64_t m, int64_t n, int64_t k) {
 // out[M,N] = T(alpha * (op(A) op(B) + addend))
 int plain_gemm(const void* A, bool a_kmajor, int64_t lda, const void* B, bool b_kmajor, int64_t ldb,
                const void* A1, int64_t lda1, const void* B1, int64_t ldb1, int64_t K1, void* D,
-               int64_t ldd, int64_t M, int64_t N, int64_t K, bool bf16, bool out_fp32,
+               int64_t ldd, int64_t M, int64_t N, int64_t K, int dtype, bool out_fp32,
                const float* addend, int64_t ld_add, const float* alpha, int32_t* status,
                cudaStream_t s) {
   Launch L;
-  L.bf16 = bf16;
+  L.dtype = dtype;
+  out_fp32 = out_fp32 || dtype == BT_FP32;
   L.a0 = operand(A, a_kmajor, M, K, lda);
   L.b0 = operand(B, b_kmajor, N, K, ldb);
   if (A1 != nullptr) {
@@ -75,14 +78,14 @@ extern "C" int bt_gemm(const void* A, const void* B, void* D, int64_t M, int64_t
                        int in_dtype, int out_dtype, const float* addend, int64_t ld_addend,
                        const float* alpha, int32_t* status, void* stream) {
   using namespace bt;
-  BT_CHECK_ARG(is16(in_dtype), "gemm: operands must be bf16 or fp16 (got dtype %d)", in_dtype);
+  BT_CHECK_ARG(is_tc(in_dtype), "gemm: operands must be bf16, fp16 or fp32 (got dtype %d)", in_dtype);
   BT_CHECK_ARG(out_dtype == in_dtype || out_dtype == BT_FP32,
                "gemm: result must have the operand dtype or be fp32");
   BT_CHECK_ARG(A && B && D, "gemm: null pointer");
   if (int rc = check_dims("gemm", M, N, K)) return rc;
   BT_CHECK_ARG(ldd >= N && (addend == nullptr || ld_addend >= N), "gemm: result stride too small");
   return plain_gemm(A, a_kmajor != 0, lda, B, b_kmajor != 0, ldb, nullptr, 0, nullptr, 0, 0, D, ldd,
-                    M, N, K, in_dtype == BT_BF16, out_dtype == BT_FP32, addend, ld_addend, alpha,
+                    M, N, K, in_dtype, out_dtype == BT_FP32, addend, ld_addend, alpha,
                     status, static_cast<cudaStream_t>(stream));
 }
 
@@ -90,17 +93,18 @@ extern "C" int bt_mlp_fwd(const void* x, const void* wg, const void* wu, const v
                           void* up, void* h, void* y, int64_t T, int64_t H, int64_t I, int64_t ld_x,
                           int dtype, int32_t* status, void* stream) {
   using namespace bt;
-  BT_CHECK_ARG(is16(dtype), "mlp_fwd: bf16 or fp16 only (got dtype %d)", dtype);
+  BT_CHECK_ARG(is_tc(dtype), "mlp_fwd: unknown dtype %d", dtype);
   BT_CHECK_ARG(T >= 0, "mlp_fwd: negative T");
   if (T == 0) return BT_OK;
   BT_CHECK_ARG(x && wg && wu && wd && gate && up && h && y, "mlp_fwd: null pointer");
   if (int rc = check_dims("mlp_fwd", T, I, H)) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool bf16 = dtype == BT_BF16;
+  const int bf16 = dtype;  // operand storage, passed through to the launches
+  const int es = esize(dtype);
   {
     // gate | up = x [Wg ; Wu]^T with the SwiGLU epilogue
     gemm::Launch L;
-    L.bf16 = bf16;
+    L.dtype = dtype;
     L.dual_b = true;
     L.a0 = operand(x, true, T, H, ld_x);
     L.b0 = operand(wg, true, I, H, H);
@@ -112,7 +116,7 @@ extern "C" int bt_mlp_fwd(const void* x, const void* wg, const void* wu, const v
     L.p.up = up;
     L.p.h = h;
     L.p.ld_act = I;
-    L.p.vec_ok = rows_aligned(gate, I, 2) && rows_aligned(up, I, 2) && rows_aligned(h, I, 2);
+    L.p.vec_ok = rows_aligned(gate, I, es) && rows_aligned(up, I, es) && rows_aligned(h, I, es);
     if (int rc = gemm::launch<gemm::EPI_SWIGLU_FWD>(L, s)) return rc;
   }
   // y = h Wd^T
@@ -126,17 +130,18 @@ extern "C" int bt_mlp_bwd(const void* dy, const void* x, const void* wg, const v
                           int64_t T, int64_t H, int64_t I, int64_t ld_x, int64_t ld_dy,
                           int64_t ld_dgate, int dtype, int32_t* status, void* stream) {
   using namespace bt;
-  BT_CHECK_ARG(is16(dtype), "mlp_bwd: bf16 or fp16 only (got dtype %d)", dtype);
+  BT_CHECK_ARG(is_tc(dtype), "mlp_bwd: unknown dtype %d", dtype);
   BT_CHECK_ARG(T > 0, "mlp_bwd: T must be positive");
   BT_CHECK_ARG(dy && x && wg && wu && wd && gate && up && h && dgate && dup, "mlp_bwd: null pointer");
   if (int rc = check_dims("mlp_bwd", T, I, H)) return rc;
   BT_CHECK_ARG(ld_dgate >= I, "mlp_bwd: dgate/dup row stride smaller than I");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool bf16 = dtype == BT_BF16;
+  const int bf16 = dtype;  // operand storage, passed through to the launches
+  const int es = esize(dtype);
   {
     // dh = dy Wd (Wd stored [H, I] = [K, N]); epilogue -> dgate, dup
     gemm::Launch L;
-    L.bf16 = bf16;
+    L.dtype = dtype;
     L.a0 = operand(dy, true, T, H, ld_dy);
     L.b0 = operand(wd, false, I, H, I);
     L.p.M = static_cast<int>(T);
@@ -148,8 +153,8 @@ extern "C" int bt_mlp_bwd(const void* dy, const void* x, const void* wg, const v
     L.p.h = dup;
     L.p.ld_act = I;
     L.p.ldo = ld_dgate;
-    L.p.vec_ok = rows_aligned(gate, I, 2) && rows_aligned(up, I, 2) &&
-                 rows_aligned(dgate, ld_dgate, 2) && rows_aligned(dup, ld_dgate, 2);
+    L.p.vec_ok = rows_aligned(gate, I, es) && rows_aligned(up, I, es) &&
+                 rows_aligned(dgate, ld_dgate, es) && rows_aligned(dup, ld_dgate, es);
     if (int rc = gemm::launch<gemm::EPI_SWIGLU_BWD>(L, s)) return rc;
   }
   if (dwd != nullptr) {  // dWd[H, I] = dy^T h
@@ -161,8 +166,8 @@ extern "C" int bt_mlp_bwd(const void* dy, const void* x, const void* wg, const v
   // the two weight gradients are one product [dgate | dup]^T x (twice the tiles per launch,
   // so the last wave of tiles is fuller).
   const bool stacked = dwg != nullptr && dwu != nullptr && ld_dgate == 2 * I &&
-                       static_cast<const char*>(dup) == static_cast<const char*>(dgate) + I * 2 &&
-                       static_cast<const char*>(dwu) == static_cast<const char*>(dwg) + I * H * 2;
+                       static_cast<const char*>(dup) == static_cast<const char*>(dgate) + I * es &&
+                       static_cast<const char*>(dwu) == static_cast<const char*>(dwg) + I * H * es;
   if (stacked) {
     if (int rc = plain_gemm(dgate, false, ld_dgate, x, false, ld_x, nullptr, 0, nullptr, 0, 0, dwg, H,
                             2 * I, H, T, bf16, false, nullptr, 0, nullptr, status, s))
@@ -198,7 +203,7 @@ extern "C" int bt_lce_logits_stats(const void* hidden, const void* W, const int6
                                    int64_t v_offset, int64_t ignore_index, int dtype,
                                    int32_t* status, void* stream) {
   using namespace bt;
-  BT_CHECK_ARG(is16(dtype), "lce_logits_stats: bf16 or fp16 only (got dtype %d)", dtype);
+  BT_CHECK_ARG(is_tc(dtype), "lce_logits_stats: unknown dtype %d", dtype);
   BT_CHECK_ARG(rows >= 0, "lce_logits_stats: negative rows");
   if (rows == 0) return BT_OK;
   BT_CHECK_ARG(hidden && W && labels && logits && tile_stats && tgt_logit,
@@ -206,7 +211,7 @@ extern "C" int bt_lce_logits_stats(const void* hidden, const void* W, const int6
   if (int rc = check_dims("lce_logits_stats", rows, V, H)) return rc;
   BT_CHECK_ARG(ld_logits >= V, "lce_logits_stats: logits stride smaller than V");
   gemm::Launch L;
-  L.bf16 = dtype == BT_BF16;
+  L.dtype = dtype;
   L.a0 = operand(hidden, true, rows, H, ld_hidden);
   L.b0 = operand(W, true, V, H, H);
   L.p.M = static_cast<int>(rows);
@@ -220,6 +225,6 @@ extern "C" int bt_lce_logits_stats(const void* hidden, const void* W, const int6
   L.p.v_offset = v_offset;
   L.p.ignore_index = ignore_index;
   L.p.n_vtiles = static_cast<int>(bt_lce_num_vtiles(V));
-  L.p.vec_ok = rows_aligned(logits, ld_logits, 2);
+  L.p.vec_ok = rows_aligned(logits, ld_logits, esize(dtype));
   return gemm::launch<gemm::EPI_LCE>(L, static_cast<cudaStream_t>(stream));
 }

@@ -33,7 +33,8 @@ from torch import Tensor
 
 from .. import _lib
 
-_GEMM_DTYPES = (torch.bfloat16, torch.float16)
+# fp32 tensors are fed to the tensor cores as tf32 (10-bit mantissa products, fp32 accumulation)
+_GEMM_DTYPES = (torch.bfloat16, torch.float16, torch.float32)
 
 # With the default chunk_size the op may work on up to this many rows at a time as long as
 # the 16-bit logits chunk stays under AUTO_CHUNK_BYTES: 8192 rows x 4096 hidden is a whole
@@ -61,7 +62,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         lib = _lib.get_lib()
         if x.dtype not in _GEMM_DTYPES:
             raise TypeError(
-                f"bastile_b200 fused_linear_cross_entropy: tensor-core kernels take bf16/fp16 hidden states, got {x.dtype}"
+                f"bastile_b200 fused_linear_cross_entropy: unsupported hidden-state dtype {x.dtype}"
             )
         if reduction not in ("mean", "sum"):
             raise ValueError(f"reduction must be 'mean' or 'sum', got {reduction!r}")

@@ -75,7 +75,8 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return SwiGLUFunction.apply(gate, up)
 
 
-_GEMM_DTYPES = (torch.bfloat16, torch.float16)
+# fp32 tensors are fed to the tensor cores as tf32 (10-bit mantissa products, fp32 accumulation)
+_GEMM_DTYPES = (torch.bfloat16, torch.float16, torch.float32)
 
 
 class SwiGLUMLPFunction(torch.autograd.Function):
@@ -86,7 +87,7 @@ class SwiGLUMLPFunction(torch.autograd.Function):
         dev = _lib.require_cuda(x, wg, wu, wd)
         lib = _lib.get_lib()
         if x.dtype not in _GEMM_DTYPES:
-            raise TypeError(f"bastile_b200 MLP: tensor-core kernels take bf16/fp16 activations, got {x.dtype}")
+            raise TypeError(f"bastile_b200 MLP: unsupported activation dtype {x.dtype}")
         inter, hidden = wg.shape
         if wu.shape != (inter, hidden) or wd.shape != (hidden, inter) or x.shape[-1] != hidden:
             raise ValueError("bastile_b200 MLP: weight shapes do not match a SwiGLU block")

@@ -131,8 +131,9 @@ int bt_swiglu_bwd(const void* dy, const void* gate, const void* up,
 
 /* ------------------------------------------------------- tcgen05 GEMM core  */
 
-/* D[M,N] = op(A) * op(B) with fp32 accumulation in tensor memory, 16-bit
- * operands (BT_BF16 or BT_FP16) and a 16-bit or fp32 result.
+/* D[M,N] = op(A) * op(B) with fp32 accumulation in tensor memory.  Operands are
+ * BT_BF16 or BT_FP16 (result in the same type or fp32) or BT_FP32 (multiplied as
+ * tf32, fp32 result); row strides must be multiples of 16 bytes.
  *   a_kmajor = 1: A is stored [M,K] with K contiguous (row stride lda)
  *   a_kmajor = 0: A is stored [K,M] with M contiguous (row stride lda)
  *   b_kmajor = 1: B is stored [N,K] with K contiguous (row stride ldb)

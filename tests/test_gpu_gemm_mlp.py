@@ -58,6 +58,36 @@ def test_gemm_layouts_and_ragged_shapes(M, N, K, ak, bk, dtype, gemm_mode):
     assert_close(D, ref, what="D", **tol)
 
 
+@pytest.mark.parametrize("ak,bk", [(1, 1), (1, 0), (0, 1), (0, 0)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 32), (136, 264, 72), (300, 520, 1000), (640, 1024, 516)])
+def test_gemm_fp32_operands_as_tf32(M, N, K, ak, bk, gemm_mode):
+    """fp32 storage, tf32 products, fp32 accumulation: against float64 with a tf32-sized tolerance."""
+    torch.manual_seed(M + N + K)
+    A = torch.randn((M, K) if ak else (K, (M + 3) // 4 * 4), device=DEV)
+    B = torch.randn((N, K) if bk else (K, (N + 3) // 4 * 4), device=DEV)
+    Af = A.double().cpu().numpy() if ak else A.double().cpu().numpy().T[:M]
+    Bf = B.double().cpu().numpy() if bk else B.double().cpu().numpy().T[:N]
+    ref = Af @ Bf.T
+    D = _gemm(A, B, M, N, K, ak, bk, out_dtype=torch.float32)
+    assert_close(D, ref, what="D", rtol=2e-3, atol=2e-3 * np.sqrt(K))
+
+
+def test_mlp_fp32_vs_oracle():
+    from bastile_b200.ops.swiglu import SwiGLUMLPFunction
+
+    x, wg, wu, wd, dy = _mlp_case(200, 256, 640, torch.float32, seed=9)
+    xs, wgs, wus, wds = (a.clone().requires_grad_(True) for a in (x, wg, wu, wd))
+    y = SwiGLUMLPFunction.apply(xs, wgs, wus, wds)
+    y.backward(dy)
+    f = lambda a: a.detach().cpu().numpy()  # noqa: E731
+    y_ref = oracle.mlp_fwd(f(x), f(wg), f(wu), f(wd))[0]
+    dx_ref, dwg_ref, dwu_ref, dwd_ref = oracle.mlp_bwd(f(dy), f(x), f(wg), f(wu), f(wd))
+    for got, want, what in ((y, y_ref, "y"), (xs.grad, dx_ref, "dx"), (wgs.grad, dwg_ref, "dwg"),
+                            (wus.grad, dwu_ref, "dwu"), (wds.grad, dwd_ref, "dwd")):
+        assert got.dtype == torch.float32
+        assert_close(got, want, what=what, rtol=5e-3, atol=5e-3 * max(1.0, float(np.abs(want).max())))
+
+
 def test_gemm_fp32_out_addend_alpha_and_inplace_accumulate():
     torch.manual_seed(0)
     M, N, K = 200, 328, 264
@@ -106,9 +136,9 @@ def test_gemm_rejects_bad_arguments():
     rc = lib.bt_gemm(A.data_ptr(), B.data_ptr(), D.data_ptr(), 16, 16, 20, 20, 20, 16, 1, 1, 0, 0, None, 0, None,
                      st.data_ptr(), _lib.stream_ptr(A.device))
     assert rc == -1 and b"multiple of 8" in lib.bt_last_error()
-    rc = lib.bt_gemm(A.data_ptr(), B.data_ptr(), D.data_ptr(), 16, 16, 16, 24, 24, 16, 1, 1, 2, 2, None, 0, None,
+    rc = lib.bt_gemm(A.data_ptr(), B.data_ptr(), D.data_ptr(), 16, 16, 16, 24, 24, 16, 1, 1, 2, 0, None, 0, None,
                      st.data_ptr(), _lib.stream_ptr(A.device))
-    assert rc == -1  # fp32 operands are not supported by the tensor-core path
+    assert rc == -1  # fp32 operands give an fp32 result, nothing narrower
 
 
 # ------------------------------------------------------------------------------ MLP

@@ -126,12 +126,63 @@ def test_lce_bias_falls_back_to_linear_plus_cross_entropy_like_the_reference():
     torch.testing.assert_close(fused_linear_cross_entropy(x, w, t, bias=b), F.cross_entropy(F.linear(x, w, b), t))
 
 
-def test_lce_fp32_inputs_are_refused_not_silently_downcast():
+def test_lce_reference_unit_tests_fp32_verbatim():
+    """tests/ops/test_fused_linear_cross_entropy.py with its own fp32 inputs, shapes and tolerances
+    (fp32 operands run on the tensor cores as tf32)."""
     from bastile_b200.ops.fused_linear_cross_entropy import fused_linear_cross_entropy
 
-    with pytest.raises(TypeError):
-        fused_linear_cross_entropy(torch.randn(8, 64, device=DEV), torch.randn(16, 64, device=DEV),
-                                   torch.randint(0, 16, (8,), device=DEV))
+    def ref(x, w, t, **kw):
+        return F.cross_entropy(F.linear(x, w), t, **kw)
+
+    # :18-34 forward loss
+    torch.manual_seed(42)
+    x = torch.randn(32, 256, device=DEV, requires_grad=True)
+    w = torch.randn(1024, 256, device=DEV, requires_grad=True)
+    t = torch.randint(0, 1024, (32,), device=DEV)
+    torch.testing.assert_close(fused_linear_cross_entropy(x, w, t), ref(x.detach(), w.detach(), t), rtol=1e-3, atol=1e-3)
+    # :58-88 gradients
+    torch.manual_seed(42)
+    x = torch.randn(16, 128, device=DEV, requires_grad=True)
+    w = torch.randn(512, 128, device=DEV, requires_grad=True)
+    t = torch.randint(0, 512, (16,), device=DEV)
+    xr, wr = x.detach().clone().requires_grad_(True), w.detach().clone().requires_grad_(True)
+    ref(xr, wr, t).backward()
+    fused_linear_cross_entropy(x, w, t).backward()
+    assert torch.isfinite(x.grad).all() and torch.isfinite(w.grad).all()
+    torch.testing.assert_close(x.grad, xr.grad, rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(w.grad, wr.grad, rtol=1e-2, atol=1e-2)
+    # :91-113 ignore_index
+    torch.manual_seed(42)
+    x = torch.randn(48, 128, device=DEV)
+    w = torch.randn(512, 128, device=DEV)
+    t = torch.randint(0, 512, (48,), device=DEV)
+    t[::3] = -100
+    torch.testing.assert_close(fused_linear_cross_entropy(x, w, t, ignore_index=-100), ref(x, w, t, ignore_index=-100),
+                               rtol=1e-3, atol=1e-3)
+    # :116-136 3-D input
+    x3, t3 = torch.randn(2, 16, 128, device=DEV), torch.randint(0, 512, (2, 16), device=DEV)
+    torch.testing.assert_close(fused_linear_cross_entropy(x3, w, t3), ref(x3.view(-1, 128), w, t3.view(-1)),
+                               rtol=1e-3, atol=1e-3)
+    # :139-159 v_chunk_size
+    torch.testing.assert_close(fused_linear_cross_entropy(x, w, t, v_chunk_size=128), ref(x, w, t, ignore_index=-100),
+                               rtol=1e-2, atol=1e-2)
+    from bastile_b200 import _lib
+
+    _lib.check_status(x.device, "fp32 fused loss")
+
+
+@pytest.mark.parametrize("name", ["loss_fp32", "grads", "ignore_index", "sum", "ragged"])
+def test_lce_golden_reference_fixtures_fp32(name):
+    """The reference's own outputs (fp32, CPU) against the kernels fed the same fp32 inputs."""
+    g = load_golden(f"lce_{name}.npz")
+    x = torch.as_tensor(g["x"]).to(DEV)
+    w = torch.as_tensor(g["w"]).to(DEV)
+    t = torch.as_tensor(g["t"]).to(DEV)
+    red = str(g["reduction"])
+    loss, dx, dw = _run(x, w, t, reduction=red)
+    assert abs(loss.item() - float(g["loss"])) <= 1e-3 * max(1.0, abs(float(g["loss"])))
+    assert_close(dx, g["dx"], what="dx", rtol=1e-2, atol=1e-2 * max(1.0, float(np.abs(g["dx"]).max())))
+    assert_close(dw, g["dw"], what="dw", rtol=1e-2, atol=1e-2 * max(1.0, float(np.abs(g["dw"]).max())))
 
 
 def test_lce_vocab_shards_emulated_on_one_gpu():

@@ -70,6 +70,35 @@ def test_tiny_qwen3_loss_and_grads_match_hf_eager_fixture(patched):
         assert_close(got, ref, what=pname, rtol=5e-2, atol=5e-2 * float(np.abs(ref).max()))
 
 
+def test_tiny_qwen3_fp32_on_gpu_matches_hf_eager_fixture(patched):
+    """Same model kept in fp32 on the GPU (tf32 products in the MLP and the fused loss; the
+    projections and attention run torch's fp32 kernels): loss within 1e-3, gradients within 2e-2."""
+    from golden.make_golden import build_tiny_qwen3, tiny_qwen3_config, tiny_qwen3_inputs
+    from transformers import Qwen3ForCausalLM
+
+    import bastile_b200
+
+    g = load_golden("tiny_qwen3.npz")
+    bastile_b200.reset()
+    stock = build_tiny_qwen3()
+    bastile_b200.apply()
+    model = Qwen3ForCausalLM(tiny_qwen3_config())
+    model.load_state_dict(stock.state_dict())
+    model = model.to(DEV).train()
+    ids, labels = tiny_qwen3_inputs()
+    out = model(input_ids=ids.to(DEV), labels=labels.to(DEV))
+    out.loss.backward()
+    assert abs(out.loss.item() - float(g["loss"])) <= 1e-3 * float(g["loss"])
+    grads = dict(model.named_parameters())
+    for name, ref_norm in zip([str(n) for n in g["names"]], g["grad_norms"]):
+        gn = grads[name].grad.float().norm().item()
+        assert abs(gn - ref_norm) <= 2e-2 * ref_norm + 1e-5, f"{name}: grad norm {gn} vs {ref_norm}"
+    for key in g.files:
+        if key.startswith("grad::") and not key.endswith("[:64,:64]"):
+            ref = g[key]
+            assert_close(grads[key[6:]].grad, ref, what=key, rtol=2e-2, atol=2e-2 * float(np.abs(ref).max()))
+
+
 def test_eval_path_returns_logits_like_hf(patched):
     from golden.make_golden import tiny_qwen3_config, tiny_qwen3_inputs
     from transformers import Qwen3ForCausalLM

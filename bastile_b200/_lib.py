@@ -221,3 +221,22 @@ def check_status(dev: torch.device, what: str) -> None:
     if v != 0:
         st.zero_()
         raise BastileB200Error(f"{what}: a bounded device-side wait ran out (status {v:#x})")
+
+
+def check_all_status() -> None:
+    """Synchronising check of every status word the ops have handed to the tensor-core kernels and
+    of the bulk-copy wait flag of the RMSNorm kernels; raises if a bounded device-side wait ever
+    ran out (the results of that call were invalid).  The ops never call this themselves - they
+    do not synchronise - so a training loop can call it at a point where it syncs anyway."""
+    bad = []
+    for (dev_idx, _stream), word in _status.items():
+        v = int(word.item())
+        if v:
+            word.zero_()
+            bad.append(f"cuda:{dev_idx} GEMM status {v:#x}")
+    if _lib is not None and torch.cuda.is_available():
+        v = int(_lib.bt_device_wait_errors())
+        if v:
+            bad.append(f"RMSNorm bulk-copy wait flag {v:#x}")
+    if bad:
+        raise BastileB200Error("a bounded device-side wait ran out: " + "; ".join(bad))

@@ -28,6 +28,7 @@ chunk and one all-reduce of ``d hidden``; ``dW`` stays local.
 from __future__ import annotations
 
 import torch
+import torch.distributed as dist
 import torch.nn.functional as F
 from torch import Tensor
 
@@ -75,8 +76,6 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         bt_local = xf.shape[0]
         if group is not None and shard_tokens:
             # every rank brought its own rows: assemble all rows of all ranks (same count each)
-            import torch.distributed as dist
-
             world_sz = dist.get_world_size(group)
             x_all = torch.empty((world_sz * bt_local, hdim), dtype=x.dtype, device=dev)
             dist.all_gather_into_tensor(x_all, xf.contiguous(), group=group)
@@ -121,8 +120,6 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         dw_acc = torch.empty((vloc, hdim), **f32) if n_chunks > 1 else None
         world = 1
         if group is not None:
-            import torch.distributed as dist
-
             world = dist.get_world_size(group)
             gathered = torch.empty((world, chunk, 3), **f32)
 
@@ -146,8 +143,6 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
                                                 rows, n_vt, stream), "bt_lce_row_stats")
                 stats = row_stats
                 if group is not None:
-                    import torch.distributed as dist
-
                     dist.all_gather_into_tensor(gathered.view(-1), row_stats.view(-1), group=group)
                     stats = merge_shard_stats(gathered[:, :rows])
                 _lib.check(lib.bt_lce_dlogits(logits_buf.data_ptr(), stats.data_ptr(), lc.data_ptr(),
@@ -168,8 +163,6 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             _lib.check(lib.bt_lce_reduce_loss(loss_row.data_ptr(), bt, scal[1:].data_ptr() if reduction == "mean"
                                               else None, scal[2:].data_ptr(), stream), "bt_lce_reduce_loss")
         if group is not None and bt > 0:
-            import torch.distributed as dist
-
             if shard_tokens:  # each rank only needs the gradient of its own rows
                 dx_local = torch.empty((bt_local, hdim), dtype=dx.dtype, device=dev)
                 dist.reduce_scatter_tensor(dx_local, dx, group=group)

@@ -45,6 +45,14 @@ constexpr int kTmemCols = 512;
 constexpr int kGroupM = 16;  // tile rasterisation: walk 16 row-tiles per column-tile
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
+// Tile geometry that depends on the operand element size (all rows are 128 bytes).
+template <typename T>
+struct Geo {
+  static constexpr int kBk = kRowBytes / static_cast<int>(sizeof(T));     // K elements per k-block
+  static constexpr int kMnBox = kRowBytes / static_cast<int>(sizeof(T));  // M/N elements per MN-major box row
+  static constexpr int kBoxBytes = kBk * kRowBytes;                       // one MN-major box
+};
+
 enum : int { EPI_PLAIN = 0, EPI_SWIGLU_FWD = 1, EPI_SWIGLU_BWD = 2, EPI_LCE = 3 };
 
 // Status-word bits set when a bounded wait runs out.
@@ -59,9 +67,6 @@ struct Params {
   uint32_t idesc;
   uint64_t a_desc_hi, b_desc_hi;
   uint32_t a_kstep, b_kstep;  // descriptor address step per MMA K slice, 16-byte units
-  int bk;          // elements of K per k-block (128 bytes: 64 for 16-bit, 32 for fp32)
-  int mn_box;      // elements of M/N per MN-major box row (128 bytes)
-  int box_bytes;   // bytes of one MN-major box: bk rows of 128 bytes
   int32_t* status;
   // --- plain epilogue: out = T(alpha * (acc + addend))
   void* out;
@@ -366,8 +371,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
   ptx::tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int nkb0 = (p.K0 + p.bk - 1) / p.bk;
-  const int nkb1 = (p.K1 + p.bk - 1) / p.bk;
+  constexpr int kBk = Geo<T>::kBk, kMnBox = Geo<T>::kMnBox, kBoxBytes = Geo<T>::kBoxBytes;
+  const int nkb0 = (p.K0 + kBk - 1) / kBk;
+  const int nkb1 = (p.K1 + kBk - 1) / kBk;
   const int nkb = nkb0 + nkb1;
 
   if (warp == 0) {
@@ -388,7 +394,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
           }
           ptx::mbar_arrive_expect_tx(&full[stage], kStageBytes);
           const bool second = kb >= nkb0;
-          const int k0 = (second ? kb - nkb0 : kb) * p.bk;
+          const int k0 = (second ? kb - nkb0 : kb) * kBk;
           const CUtensorMap* ta = second ? &tmA1 : &tmA0;
           const CUtensorMap* tb = second ? &tmB1 : &tmB0;
           uint8_t* sa = smem + stage * kStageBytes;
@@ -396,8 +402,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
           if (p.a_kmajor) {
             ptx::tma_load_2d(sa, ta, k0, m0, &full[stage]);
           } else {
-            for (int j = 0; j < BM / p.mn_box; ++j)
-              ptx::tma_load_2d(sa + j * p.box_bytes, ta, m0 + j * p.mn_box, k0, &full[stage]);
+#pragma unroll
+            for (int j = 0; j < BM / kMnBox; ++j)
+              ptx::tma_load_2d(sa + j * kBoxBytes, ta, m0 + j * kMnBox, k0, &full[stage]);
           }
           if (p.dual_b) {
             ptx::tma_load_2d(sb, &tmB0, k0, n0, &full[stage]);
@@ -405,8 +412,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
           } else if (p.b_kmajor) {
             ptx::tma_load_2d(sb, tb, k0, n0, &full[stage]);
           } else {
-            for (int j = 0; j < BN / p.mn_box; ++j)
-              ptx::tma_load_2d(sb + j * p.box_bytes, tb, n0 + j * p.mn_box, k0, &full[stage]);
+#pragma unroll
+            for (int j = 0; j < BN / kMnBox; ++j)
+              ptx::tma_load_2d(sb + j * kBoxBytes, tb, n0 + j * kMnBox, k0, &full[stage]);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -556,8 +564,9 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
   ptx::tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int nkb0 = (p.K0 + p.bk - 1) / p.bk;
-  const int nkb1 = (p.K1 + p.bk - 1) / p.bk;
+  constexpr int kBk = Geo<T>::kBk, kMnBox = Geo<T>::kMnBox, kBoxBytes = Geo<T>::kBoxBytes;
+  const int nkb0 = (p.K0 + kBk - 1) / kBk;
+  const int nkb1 = (p.K1 + kBk - 1) / kBk;
   const int nkb = nkb0 + nkb1;
   const int pair = blockIdx.x >> 1;
   const int npairs = gridDim.x >> 1;
@@ -580,7 +589,7 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
           }
           if (leader) ptx::mbar_arrive_expect_tx(&full[stage], 2 * kStageBytes2);
           const bool second = kb >= nkb0;
-          const int k0 = (second ? kb - nkb0 : kb) * p.bk;
+          const int k0 = (second ? kb - nkb0 : kb) * kBk;
           const CUtensorMap* ta = second ? &tmA1 : &tmA0;
           const CUtensorMap* tb = p.dual_b ? (rank ? &tmB1 : &tmB0) : (second ? &tmB1 : &tmB0);
           uint8_t* sa = smem + stage * kStageBytes2;
@@ -588,14 +597,16 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
           if (p.a_kmajor) {
             ptx::tma_load_2d_pair(sa, ta, k0, m0, &full[stage]);
           } else {
-            for (int j = 0; j < BM / p.mn_box; ++j)
-              ptx::tma_load_2d_pair(sa + j * p.box_bytes, ta, m0 + j * p.mn_box, k0, &full[stage]);
+#pragma unroll
+            for (int j = 0; j < BM / kMnBox; ++j)
+              ptx::tma_load_2d_pair(sa + j * kBoxBytes, ta, m0 + j * kMnBox, k0, &full[stage]);
           }
           if (p.b_kmajor) {
             ptx::tma_load_2d_pair(sb, tb, k0, n0, &full[stage]);
           } else {
-            for (int j = 0; j < (BN / 2) / p.mn_box; ++j)
-              ptx::tma_load_2d_pair(sb + j * p.box_bytes, tb, n0 + j * p.mn_box, k0, &full[stage]);
+#pragma unroll
+            for (int j = 0; j < (BN / 2) / kMnBox; ++j)
+              ptx::tma_load_2d_pair(sb + j * kBoxBytes, tb, n0 + j * kMnBox, k0, &full[stage]);
           }
           if (++stage == kStages2) {
             stage = 0;
@@ -868,14 +879,12 @@ int launch(Launch& L, cudaStream_t s) {
   p.b_kmajor = L.b0.kmajor;
   p.dual_b = L.dual_b ? 1 : 0;
   const int esize = L.dtype == BT_FP32 ? 4 : 2;
-  p.bk = kRowBytes / esize;
-  p.mn_box = kRowBytes / esize;
-  p.box_bytes = p.bk * kRowBytes;
+  const int box_bytes = (kRowBytes / esize) * kRowBytes;  // one MN-major box: 128-byte rows, 128 bytes of K
   const uint32_t fmt = L.dtype == BT_FP16 ? 0u : (L.dtype == BT_BF16 ? 1u : 2u);
   p.idesc = ptx::make_idesc(fmt, !L.a0.kmajor, !L.b0.kmajor, pair ? 2 * BM : BM, BN);
-  p.a_desc_hi = ptx::make_smem_desc_hi(L.a0.kmajor != 0, static_cast<uint32_t>(p.box_bytes),
+  p.a_desc_hi = ptx::make_smem_desc_hi(L.a0.kmajor != 0, static_cast<uint32_t>(box_bytes),
                                        esize == 4 && !L.a0.kmajor);
-  p.b_desc_hi = ptx::make_smem_desc_hi(L.b0.kmajor != 0, static_cast<uint32_t>(p.box_bytes),
+  p.b_desc_hi = ptx::make_smem_desc_hi(L.b0.kmajor != 0, static_cast<uint32_t>(box_bytes),
                                        esize == 4 && !L.b0.kmajor);
   // one MMA consumes 32 bytes of K: 32 bytes along a K-major row, or 32/esize rows of 128 bytes
   const uint32_t mn_step = static_cast<uint32_t>((32 / esize) * kRowBytes) >> 4;

@@ -515,11 +515,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
 //   empty[s], tfull[a]  live in both CTAs; the leader's commit arrives on both copies.
 //   tempty[a]  lives in the leader; epilogue threads of both CTAs arrive on it.
 constexpr int kStages2 = 6;
+constexpr int kPairProducerB = 2 + kEpiWarps;       // warp index of the second producer
+constexpr int kThreadsPair = kThreads + 32;
 constexpr int kStageBytes2 = kABytes + kBBytes / 2;
 constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + 1024 + 256;
 
 template <int EPI, typename T>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreadsPair, 1)
 gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
                  const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
                  const Params p) {
@@ -571,9 +573,13 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
   const int pair = blockIdx.x >> 1;
   const int npairs = gridDim.x >> 1;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+  if (warp == 0 || warp == kPairProducerB) {
+    // --------------------------------------------- TMA producers (A: warp 0, B: warp 10)
+    // Two lanes in different warps share the issue work of a k-block: with MN-major operands a
+    // k-block takes four tile loads per CTA, and one thread issuing all of them (plus the
+    // barrier traffic) was within a factor ~1.4 of the 512 cycles the MMAs of a k-block take.
     if (lane == 0) {
+      const bool do_a = warp == 0;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -587,26 +593,29 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
             ok = false;
             break;
           }
-          if (leader) ptx::mbar_arrive_expect_tx(&full[stage], 2 * kStageBytes2);
           const bool second = kb >= nkb0;
           const int k0 = (second ? kb - nkb0 : kb) * kBk;
-          const CUtensorMap* ta = second ? &tmA1 : &tmA0;
-          const CUtensorMap* tb = p.dual_b ? (rank ? &tmB1 : &tmB0) : (second ? &tmB1 : &tmB0);
           uint8_t* sa = smem + stage * kStageBytes2;
-          uint8_t* sb = sa + kABytes;
-          if (p.a_kmajor) {
-            ptx::tma_load_2d_pair(sa, ta, k0, m0, &full[stage]);
-          } else {
+          if (do_a) {
+            if (leader) ptx::mbar_arrive_expect_tx(&full[stage], 2 * kStageBytes2);
+            const CUtensorMap* ta = second ? &tmA1 : &tmA0;
+            if (p.a_kmajor) {
+              ptx::tma_load_2d_pair(sa, ta, k0, m0, &full[stage]);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BM / kMnBox; ++j)
-              ptx::tma_load_2d_pair(sa + j * kBoxBytes, ta, m0 + j * kMnBox, k0, &full[stage]);
-          }
-          if (p.b_kmajor) {
-            ptx::tma_load_2d_pair(sb, tb, k0, n0, &full[stage]);
+              for (int j = 0; j < BM / kMnBox; ++j)
+                ptx::tma_load_2d_pair(sa + j * kBoxBytes, ta, m0 + j * kMnBox, k0, &full[stage]);
+            }
           } else {
+            const CUtensorMap* tb = p.dual_b ? (rank ? &tmB1 : &tmB0) : (second ? &tmB1 : &tmB0);
+            uint8_t* sb = sa + kABytes;
+            if (p.b_kmajor) {
+              ptx::tma_load_2d_pair(sb, tb, k0, n0, &full[stage]);
+            } else {
 #pragma unroll
-            for (int j = 0; j < (BN / 2) / kMnBox; ++j)
-              ptx::tma_load_2d_pair(sb + j * kBoxBytes, tb, n0 + j * kMnBox, k0, &full[stage]);
+              for (int j = 0; j < (BN / 2) / kMnBox; ++j)
+                ptx::tma_load_2d_pair(sb + j * kBoxBytes, tb, n0 + j * kMnBox, k0, &full[stage]);
+            }
           }
           if (++stage == kStages2) {
             stage = 0;
@@ -814,7 +823,7 @@ int launch_pair_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMa
   const int pairs = p.num_tiles < max_pairs ? p.num_tiles : max_pairs;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(kThreadsPair, 1, 1);
   cfg.dynamicSmemBytes = kSmemBytes2;
   cfg.stream = s;
   cudaLaunchAttribute attr[1];

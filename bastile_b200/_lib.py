@@ -35,6 +35,12 @@ SIGNATURES = {
     "bt_rmsnorm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "bt_rmsnorm_bwd_ws_bytes": (c_int64, [c_int64]),
+    "bt_add_rmsnorm_fwd": (c_int, [c_void_p] * 6 + [c_int64] * 6 + [c_float, c_int, c_void_p]),
+    "bt_add_rmsnorm_bwd": (c_int, [c_void_p] * 8 + [c_int64] * 6 + [c_int, c_void_p]),
+    "bt_headnorm_rope_fwd": (c_int, [c_void_p] * 6 + [c_int64] * 4 + [POINTER(c_int64)] * 3 +
+                             [c_int64, c_float, c_int, c_void_p]),
+    "bt_headnorm_rope_bwd": (c_int, [c_void_p] * 9 + [c_int64] * 4 + [POINTER(c_int64)] * 4 +
+                             [c_int64, c_int, c_void_p]),
     "bt_rmsnorm_bwd_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                        c_int64, c_int64, c_int64, c_int, c_void_p]),
     "bt_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
@@ -47,7 +53,7 @@ SIGNATURES = {
     "bt_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                         c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "bt_set_gemm_cta_pairs": (c_int, [c_int]),
-    "bt_mlp_fwd": (c_int, [c_void_p] * 8 + [c_int64] * 4 + [c_int, c_void_p, c_void_p]),
+    "bt_mlp_fwd": (c_int, [c_void_p] * 8 + [c_int64] * 4 + [c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "bt_mlp_bwd": (c_int, [c_void_p] * 14 + [c_int64] * 6 + [c_int, c_void_p, c_void_p]),
     "bt_lce_logits_stats": (c_int, [c_void_p] * 6 + [c_int64] * 7 + [c_int, c_void_p, c_void_p]),
     "bt_lce_num_vtiles": (c_int64, [c_int64]),

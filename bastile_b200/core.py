@@ -14,6 +14,13 @@ original ``forward`` is kept and ``reset()`` with no arguments, or with
 ``reset()`` leaves is then the unpatched HF eager model.  The return value of
 ``reset()`` and of ``get_patched_ops()`` still lists registry patches only, as
 in the reference.
+
+One addition, off by default: ``apply(fused_layers=True)`` also replaces
+``Qwen3DecoderLayer.forward`` and ``Qwen3Attention.forward`` with versions that
+fold the residual adds into the norm / down-projection kernels and run
+q/k-norm + RoPE as one kernel (``ops/fused_layers.py``); the names
+``"decoder_layer_qwen3"`` and ``"attention_qwen3"`` are then appended to the
+returned list, and ``reset()`` restores both methods.
 """
 
 from __future__ import annotations
@@ -102,6 +109,15 @@ def apply(rms_norm: bool = True, swiglu: bool = True, rope: bool = True,
         if _switch_for(patch.name, switches) and _install(patch):
             applied.append(patch.name)
 
+    if kwargs.get("fused_layers", False) and rms_norm and (model_type in (None, "qwen3")):
+        try:
+            from .ops import fused_layers
+
+            applied.extend(fused_layers.install(importlib.import_module(_QWEN3), decoder_layer=True,
+                                                attention=bool(rope)))
+        except Exception as exc:  # patch failures are reported, not raised
+            log.warning("Could not apply the fused decoder-layer forwards: %s", exc)
+
     if fused_linear_cross_entropy:
         try:
             qwen3 = importlib.import_module(_QWEN3)
@@ -143,9 +159,19 @@ def _restore_lce_forward() -> None:
     _lce_original_forward = None
 
 
+def _restore_fused_layers(names: list[str] | None) -> None:
+    from .ops import fused_layers
+
+    if fused_layers.installed():
+        qwen3 = _module(_QWEN3)
+        if qwen3 is not None:
+            fused_layers.uninstall(qwen3, names)
+
+
 def reset(names: list[str] | None = None) -> list[str]:
     """Undo patches (all when ``names`` is None); returns the registry names reset."""
     reg = get_registry()
+    _restore_fused_layers(names)
     if names is None:
         _restore_lce_forward()
         names = reg.get_applied()

@@ -172,4 +172,57 @@ __device__ __forceinline__ void red_add_v4(float* dst, float a, float b, float c
                : "memory");
 }
 
+// Last step of every RMSNorm backward kernel.  Each CTA has added its column sums into one
+// of the dw_copies(N) private rows of the scratch; the CTA that draws the last ticket sums
+// the copies into dw and leaves the scratch zeroed for the next call.  The reads are all
+// issued before any of the zeroing stores so that they overlap instead of queueing up
+// behind stores to the same array.
+template <typename T>
+__device__ __forceinline__ void dw_finalize(float* __restrict__ ws, T* __restrict__ dw, int N,
+                                            unsigned int total_ctas, int tid, int nthreads) {
+  __shared__ bool s_last;
+  const int K = dw_copies(N);
+  unsigned int* counter = reinterpret_cast<unsigned int*>(ws + static_cast<int64_t>(K) * N);
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned int ticket = atomicAdd(counter, 1u);
+    s_last = (ticket == total_ctas - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if ((N & 3) == 0) {
+    const float4* ws4 = reinterpret_cast<const float4*>(ws);
+    const int n4 = N >> 2;
+#pragma unroll 2
+    for (int c = tid; c < n4; c += nthreads) {
+      float4 v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        v[k] = k < K ? __ldcg(ws4 + static_cast<int64_t>(k) * n4 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+      float o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        o[0] += v[k].x;
+        o[1] += v[k].y;
+        o[2] += v[k].z;
+        o[3] += v[k].w;
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) dw[c * 4 + e] = Cvt<T>::from_f(o[e]);
+    }
+  } else {
+    for (int c = tid; c < N; c += nthreads) {
+      float v = 0.f;
+      for (int k = 0; k < K; ++k) v += __ldcg(ws + static_cast<int64_t>(k) * N + c);
+      dw[c] = Cvt<T>::from_f(v);
+    }
+  }
+  __syncthreads();
+  const int64_t total = static_cast<int64_t>(K) * N;
+  for (int64_t c = tid; c < total; c += nthreads) ws[c] = 0.f;
+  if (tid == 0) *counter = 0u;
+}
+
 }  // namespace bt

@@ -75,6 +75,8 @@ struct Params {
   int vec_ok;  // rows of every global tensor the epilogue touches are 16-byte aligned
   const float* addend;
   int64_t ld_add;
+  const void* addend_t;  // second addend, stored in the operand type (a residual stream)
+  int64_t ld_add_t;
   const float* alpha;
   // --- SwiGLU epilogues (row stride ld_act)
   void* gate;  // fwd: out, bwd: in
@@ -176,11 +178,19 @@ __device__ __forceinline__ void epi_plain(const Params& p, uint32_t taddr, int64
   const bool row_ok = row < p.M;
 #pragma unroll 1
   for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
-    float v[32];
-    ptx::tmem_ld_32cols(taddr + c * 32, v);
+    float v[32], res[32];
     const int col0 = n0 + c * 32;
     const int valid = p.N - col0;
+    const bool add_res = p.addend_t != nullptr && row_ok && valid > 0;
+    if (add_res)  // in flight while the accumulator chunk is fetched
+      load_row32<T>(static_cast<const T*>(p.addend_t) + row * p.ld_add_t + col0, res, valid,
+                    p.vec_ok);
+    ptx::tmem_ld_32cols(taddr + c * 32, v);
     if (row_ok && valid > 0) {
+      if (add_res) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] += res[j];
+      }
       if (p.addend != nullptr) {
         const float* a = p.addend + row * p.ld_add + col0;
         if (p.vec_ok && valid >= 32) {

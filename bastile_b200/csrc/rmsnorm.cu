@@ -26,10 +26,12 @@ namespace {
 constexpr int kThreads = 256;
 
 // ------------------------------------------------------------------ forward
-template <typename T, int VPT, int LPR, int RPI>
+// ADD: the row that is normalised is T(x + res); it is also written to `sum`.
+template <typename T, int VPT, int LPR, int RPI, bool ADD>
 __global__ void __launch_bounds__(kThreads, (VPT >= 16 ? 2 : (VPT >= 8 ? 3 : 4)))
 rms_fwd_rows(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
-             float* __restrict__ rstd, int64_t M, int N, int64_t ld_x, int64_t ld_y, float eps) {
+             float* __restrict__ rstd, int64_t M, int N, int64_t ld_x, int64_t ld_y, float eps,
+             const T* __restrict__ res, T* __restrict__ sum, int64_t ld_res, int64_t ld_sum) {
   constexpr int E = Cvt<T>::N;
   constexpr int kGroups = kThreads / LPR;
   const int lane = threadIdx.x % LPR;
@@ -49,6 +51,36 @@ rms_fwd_rows(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y
         const int v = lane + i * LPR;
         xv[r][i] = (row < M && v < nv) ? ld_stream_v4(x + row * ld_x + static_cast<int64_t>(v) * E)
                                        : make_uint4(0, 0, 0, 0);
+      }
+    }
+    if constexpr (ADD) {
+      uint4 rv[RPI][VPT];
+#pragma unroll
+      for (int r = 0; r < RPI; ++r) {
+        const int64_t row = base + r * kGroups + group;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+          const int v = lane + i * LPR;
+          rv[r][i] = (row < M && v < nv)
+                         ? ld_stream_v4(res + row * ld_res + static_cast<int64_t>(v) * E)
+                         : make_uint4(0, 0, 0, 0);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < RPI; ++r) {
+        const int64_t row = base + r * kGroups + group;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+          const int v = lane + i * LPR;
+          float a[E], b[E];
+          Cvt<T>::unpack(xv[r][i], a);
+          Cvt<T>::unpack(rv[r][i], b);
+#pragma unroll
+          for (int e = 0; e < E; ++e) a[e] += b[e];
+          xv[r][i] = Cvt<T>::pack(a);
+          if (row < M && v < nv)
+            st_global_v4(sum + row * ld_sum + static_cast<int64_t>(v) * E, xv[r][i]);
+        }
       }
     }
 #pragma unroll
@@ -90,15 +122,27 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 rms_fwd_generic(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
                 float* __restrict__ rstd, int64_t M, int64_t N, int64_t ld_x, int64_t ld_y,
-                float eps) {
+                float eps, const T* __restrict__ res, T* sum, int64_t ld_res, int64_t ld_sum) {
   __shared__ float red[kThreads / 32];
   __shared__ float s_rs;
   for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
     const T* xr = x + row * ld_x;
     float ss = 0.f;
-    for (int64_t c = threadIdx.x; c < N; c += kThreads) {
-      const float f = Cvt<T>::to_f(xr[c]);
-      ss = fmaf(f, f, ss);
+    if (res != nullptr) {
+      // each thread writes and later re-reads its own columns of the summed row
+      T* sr = sum + row * ld_sum;
+      for (int64_t c = threadIdx.x; c < N; c += kThreads) {
+        const T t = Cvt<T>::from_f(Cvt<T>::to_f(xr[c]) + Cvt<T>::to_f(res[row * ld_res + c]));
+        sr[c] = t;
+        const float f = Cvt<T>::to_f(t);
+        ss = fmaf(f, f, ss);
+      }
+      xr = sr;
+    } else {
+      for (int64_t c = threadIdx.x; c < N; c += kThreads) {
+        const float f = Cvt<T>::to_f(xr[c]);
+        ss = fmaf(f, f, ss);
+      }
     }
     ss = group_sum<32>(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
@@ -119,12 +163,13 @@ rms_fwd_generic(const T* __restrict__ x, const T* __restrict__ w, T* __restrict_
 
 // ----------------------------------------------------------------- backward
 // Scratch layout: dw_copies(N) x float acc[N], then one uint32 arrival counter.
-template <typename T, int VPT, int LPR, int RPI>
+// ADD: dx = T(norm backward + dres), dres read where dx is written.
+template <typename T, int VPT, int LPR, int RPI, bool ADD>
 __global__ void __launch_bounds__(kThreads, 3)
 rms_bwd_rows(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
              const float* __restrict__ rstd, T* __restrict__ dx, T* __restrict__ dw,
              float* __restrict__ ws, int64_t M, int N, int64_t ld_dy, int64_t ld_x,
-             int64_t ld_dx) {
+             int64_t ld_dx, const T* __restrict__ dres, int64_t ld_dres) {
   constexpr int E = Cvt<T>::N;
   constexpr int kGroups = kThreads / LPR;
   extern __shared__ float s_dw[];  // N floats
@@ -196,8 +241,15 @@ rms_bwd_rows(const T* __restrict__ dy, const T* __restrict__ x, const T* __restr
             Cvt<T>::unpack(xv[r][i], xf);
             Cvt<T>::unpack(gv[r][i], gf);
 #pragma unroll
-            for (int e = 0; e < E; ++e)
-              o[e] = (gf[e] * wf[i][e] - xf[e] * rs[r] * dot) * rs[r];
+            for (int e = 0; e < E; ++e)  // explicit operations: the fused q/k-norm + RoPE
+              // backward spells out the same ones and stays bit-identical
+              o[e] = fmaf(-(xf[e] * rs[r]), dot, gf[e] * wf[i][e]) * rs[r];
+            if constexpr (ADD) {
+              float a[E];
+              Cvt<T>::unpack(ld_stream_v4(dres + row * ld_dres + static_cast<int64_t>(v) * E), a);
+#pragma unroll
+              for (int e = 0; e < E; ++e) o[e] += a[e];
+            }
             st_global_v4(dx + row * ld_dx + static_cast<int64_t>(v) * E, Cvt<T>::pack(o));
           }
         }
@@ -237,7 +289,8 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 rms_bwd_dx_generic(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
                    const float* __restrict__ rstd, T* __restrict__ dx, int64_t M, int64_t N,
-                   int64_t ld_dy, int64_t ld_x, int64_t ld_dx) {
+                   int64_t ld_dy, int64_t ld_x, int64_t ld_dx, const T* __restrict__ dres,
+                   int64_t ld_dres) {
   __shared__ float red[kThreads / 32];
   __shared__ float s_dot;
   for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
@@ -259,7 +312,9 @@ rms_bwd_dx_generic(const T* __restrict__ dy, const T* __restrict__ x, const T* _
     for (int64_t c = threadIdx.x; c < N; c += kThreads) {
       const float xh = Cvt<T>::to_f(x[row * ld_x + c]) * rs;
       const float wdy = Cvt<T>::to_f(dy[row * ld_dy + c]) * Cvt<T>::to_f(w[c]);
-      dx[row * ld_dx + c] = Cvt<T>::from_f((wdy - xh * dot) * rs);
+      float o = (wdy - xh * dot) * rs;
+      if (dres != nullptr) o += Cvt<T>::to_f(dres[row * ld_dres + c]);
+      dx[row * ld_dx + c] = Cvt<T>::from_f(o);
     }
     __syncthreads();
   }
@@ -306,34 +361,52 @@ int grid_for(int64_t work_items, int ctas_per_sm) {
   return static_cast<int>(work_items < cap ? (work_items < 1 ? 1 : work_items) : cap);
 }
 
-template <typename T>
+// Optional residual operands of the fused add + norm entry points (all null for the plain ones).
+struct Residual {
+  const void* res = nullptr;   // forward: added to x before the norm
+  void* sum = nullptr;         // forward: T(x + res)
+  int64_t ld_res = 0, ld_sum = 0;
+  const void* dres = nullptr;  // backward: added to dx
+  int64_t ld_dres = 0;
+};
+
+template <typename T, bool ADD>
 int fwd_t(const void* x, const void* w, void* y, float* rstd, int64_t M, int64_t N, int64_t ld_x,
-          int64_t ld_y, float eps, cudaStream_t s) {
+          int64_t ld_y, float eps, const Residual& rr, cudaStream_t s) {
   constexpr int E = Cvt<T>::N;
   const T* xp = static_cast<const T*>(x);
   const T* wp = static_cast<const T*>(w);
   T* yp = static_cast<T*>(y);
+  const T* rp = static_cast<const T*>(rr.res);
+  T* sp = static_cast<T*>(rr.sum);
   RowCfg c{};
-  const bool vec_ok = (N % E == 0) && (ld_x % E == 0) && (ld_y % E == 0) && aligned16(x) &&
-                      aligned16(w) && aligned16(y);
+  bool vec_ok = (N % E == 0) && (ld_x % E == 0) && (ld_y % E == 0) && aligned16(x) &&
+                aligned16(w) && aligned16(y);
+  if (ADD)
+    vec_ok = vec_ok && (rr.ld_res % E == 0) && (rr.ld_sum % E == 0) && aligned16(rr.res) &&
+             aligned16(rr.sum);
   const bool staged_ok = vec_ok && N / E > 128 && N / E <= 4 * staged::kThreads;
   if (!vec_ok || (!staged_ok && !pick_rows(N / E, 4, &c))) {
-    rms_fwd_generic<T><<<grid_for(M, 8), kThreads, 0, s>>>(xp, wp, yp, rstd, M, N, ld_x, ld_y, eps);
+    rms_fwd_generic<T><<<grid_for(M, 8), kThreads, 0, s>>>(xp, wp, yp, rstd, M, N, ld_x, ld_y, eps,
+                                                           rp, sp, rr.ld_res, rr.ld_sum);
     BT_CHECK_LAUNCH("rms_fwd_generic");
     return BT_OK;
   }
   if (staged_ok) {
     const int64_t nv = N / E;
     const int vpt = nv <= staged::kThreads ? 1 : (nv <= 2 * staged::kThreads ? 2 : 4);
-#define BT_FWDS(V, R)                                                                            \
+    // a stage of the fused form holds twice the rows, so it takes half as many per tile
+#define BT_FWDS(V, R0)                                                                           \
   if (vpt == V) {                                                                                \
-    static const cudaError_t attr = cudaFuncSetAttribute(                                        \
-        staged::rms_fwd_staged<T, V, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+    constexpr int R = ADD ? R0 / 2 : R0;                                                         \
+    static const cudaError_t attr =                                                              \
+        cudaFuncSetAttribute(staged::rms_fwd_staged<T, V, R, ADD>,                               \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);           \
     (void)attr;                                                                                  \
-    const size_t smem = staged::smem_bytes(static_cast<int>(N), sizeof(T), R, false);            \
+    const size_t smem = staged::smem_bytes(static_cast<int>(N), sizeof(T), R, ADD ? 2 : 1);      \
     const int grid = grid_for(ceil_div(M, R), 2);                                                \
-    staged::rms_fwd_staged<T, V, R><<<grid, staged::kThreads, smem, s>>>(                        \
-        xp, wp, yp, rstd, M, static_cast<int>(N), ld_x, ld_y, eps);                              \
+    staged::rms_fwd_staged<T, V, R, ADD><<<grid, staged::kThreads, smem, s>>>(                   \
+        xp, wp, yp, rstd, M, static_cast<int>(N), ld_x, ld_y, eps, rp, sp, rr.ld_res, rr.ld_sum); \
     BT_CHECK_LAUNCH("rms_fwd_staged");                                                           \
     return BT_OK;                                                                                \
   }
@@ -345,12 +418,12 @@ int fwd_t(const void* x, const void* w, void* y, float* rstd, int64_t M, int64_t
   const int64_t rows_per_iter = static_cast<int64_t>(kThreads / c.lpr) * c.rpi;
   // many short-lived CTAs: the hardware scheduler evens out the tail better than a fixed split
   const int grid = grid_for(ceil_div(M, rows_per_iter), 32);
-#define BT_FWD(L, V, R)                                                                         \
-  if (c.lpr == L && c.vpt == V) {                                                               \
-    rms_fwd_rows<T, V, L, R><<<grid, kThreads, 0, s>>>(xp, wp, yp, rstd, M, static_cast<int>(N), \
-                                                       ld_x, ld_y, eps);                        \
-    BT_CHECK_LAUNCH("rms_fwd_rows");                                                            \
-    return BT_OK;                                                                               \
+#define BT_FWD(L, V, R)                                                                        \
+  if (c.lpr == L && c.vpt == V) {                                                              \
+    rms_fwd_rows<T, V, L, R, ADD><<<grid, kThreads, 0, s>>>(                                   \
+        xp, wp, yp, rstd, M, static_cast<int>(N), ld_x, ld_y, eps, rp, sp, rr.ld_res, rr.ld_sum); \
+    BT_CHECK_LAUNCH("rms_fwd_rows");                                                           \
+    return BT_OK;                                                                              \
   }
   BT_FWD(8, 1, 4)
   BT_FWD(16, 1, 4)
@@ -362,32 +435,36 @@ int fwd_t(const void* x, const void* w, void* y, float* rstd, int64_t M, int64_t
   return BT_ERR_ARG;
 }
 
-template <typename T>
+template <typename T, bool ADD>
 int bwd_t(const void* dy, const void* x, const void* w, const float* rstd, void* dx, void* dw,
           void* ws, int64_t M, int64_t N, int64_t ld_dy, int64_t ld_x, int64_t ld_dx,
-          cudaStream_t s) {
+          const Residual& rr, cudaStream_t s) {
   constexpr int E = Cvt<T>::N;
   const T* gp = static_cast<const T*>(dy);
   const T* xp = static_cast<const T*>(x);
   const T* wp = static_cast<const T*>(w);
+  const T* rp = static_cast<const T*>(rr.dres);
   T* dxp = static_cast<T*>(dx);
   T* dwp = static_cast<T*>(dw);
   float* wsp = static_cast<float*>(ws);
-  const bool vec_ok = (N % E == 0) && (ld_x % E == 0) && (ld_dy % E == 0) && (ld_dx % E == 0) &&
-                      aligned16(x) && aligned16(w) && aligned16(dy) && aligned16(dx);
+  bool vec_ok = (N % E == 0) && (ld_x % E == 0) && (ld_dy % E == 0) && (ld_dx % E == 0) &&
+                aligned16(x) && aligned16(w) && aligned16(dy) && aligned16(dx);
+  if (ADD) vec_ok = vec_ok && (rr.ld_dres % E == 0) && aligned16(rr.dres);
   const int64_t nv = vec_ok ? N / E : 0;
   RowCfg c{};
   if (vec_ok && nv > 128 && nv <= 4 * staged::kThreads) {
     const int vpt = nv <= staged::kThreads ? 1 : (nv <= 2 * staged::kThreads ? 2 : 4);
 #define BT_BWDS(V, R)                                                                            \
   if (vpt == V) {                                                                                \
-    static const cudaError_t attr = cudaFuncSetAttribute(                                        \
-        staged::rms_bwd_staged<T, V, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+    static const cudaError_t attr =                                                              \
+        cudaFuncSetAttribute(staged::rms_bwd_staged<T, V, R, ADD>,                               \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);           \
     (void)attr;                                                                                  \
-    const size_t smem = staged::smem_bytes(static_cast<int>(N), sizeof(T), R, true);             \
+    const size_t smem = staged::smem_bytes(static_cast<int>(N), sizeof(T), R, 2);                \
     const int grid = grid_for(ceil_div(M, R), 2);                                                \
-    staged::rms_bwd_staged<T, V, R><<<grid, staged::kThreads, smem, s>>>(                        \
-        gp, xp, wp, rstd, dxp, dwp, wsp, M, static_cast<int>(N), ld_dy, ld_x, ld_dx);            \
+    staged::rms_bwd_staged<T, V, R, ADD><<<grid, staged::kThreads, smem, s>>>(                   \
+        gp, xp, wp, rstd, dxp, dwp, wsp, M, static_cast<int>(N), ld_dy, ld_x, ld_dx, rp,         \
+        rr.ld_dres);                                                                             \
     BT_CHECK_LAUNCH("rms_bwd_staged");                                                           \
     return BT_OK;                                                                                \
   }
@@ -400,13 +477,13 @@ int bwd_t(const void* dy, const void* x, const void* w, const float* rstd, void*
     const int64_t rows_per_iter = static_cast<int64_t>(kThreads / c.lpr) * c.rpi;
     const int grid = grid_for(ceil_div(M, rows_per_iter), 4);
     const size_t smem = static_cast<size_t>(N) * sizeof(float);
-#define BT_BWD(L, V, R)                                                                        \
-  if (c.lpr == L && c.vpt == V) {                                                              \
-    rms_bwd_rows<T, V, L, R><<<grid, kThreads, smem, s>>>(gp, xp, wp, rstd, dxp, dwp, wsp, M,  \
-                                                          static_cast<int>(N), ld_dy, ld_x,    \
-                                                          ld_dx);                              \
-    BT_CHECK_LAUNCH("rms_bwd_rows");                                                           \
-    return BT_OK;                                                                              \
+#define BT_BWD(L, V, R)                                                                         \
+  if (c.lpr == L && c.vpt == V) {                                                               \
+    rms_bwd_rows<T, V, L, R, ADD><<<grid, kThreads, smem, s>>>(                                 \
+        gp, xp, wp, rstd, dxp, dwp, wsp, M, static_cast<int>(N), ld_dy, ld_x, ld_dx, rp,        \
+        rr.ld_dres);                                                                            \
+    BT_CHECK_LAUNCH("rms_bwd_rows");                                                            \
+    return BT_OK;                                                                               \
   }
     BT_BWD(8, 1, 4)
     BT_BWD(16, 1, 4)
@@ -416,13 +493,66 @@ int bwd_t(const void* dy, const void* x, const void* w, const float* rstd, void*
 #undef BT_BWD
   }
   rms_bwd_dx_generic<T><<<grid_for(M, 8), kThreads, 0, s>>>(gp, xp, wp, rstd, dxp, M, N, ld_dy,
-                                                            ld_x, ld_dx);
+                                                            ld_x, ld_dx, rp, rr.ld_dres);
   BT_CHECK_LAUNCH("rms_bwd_dx_generic");
   dim3 g(static_cast<unsigned>(ceil_div(N, 32)),
          static_cast<unsigned>(M < 8 * 64 ? 1 : (M / 8 < 64 ? M / 8 : 64)));
   rms_bwd_dw_generic<T><<<g, dim3(32, 8), 0, s>>>(gp, xp, rstd, dwp, wsp, M, static_cast<int>(N),
                                                   ld_dy, ld_x);
   BT_CHECK_LAUNCH("rms_bwd_dw_generic");
+  return BT_OK;
+}
+
+template <bool ADD>
+int fwd_any(int dtype, const void* x, const void* w, void* y, float* rstd, int64_t M, int64_t N,
+            int64_t ld_x, int64_t ld_y, float eps, const Residual& rr, cudaStream_t s) {
+  switch (dtype) {
+    case BT_BF16: return fwd_t<__nv_bfloat16, ADD>(x, w, y, rstd, M, N, ld_x, ld_y, eps, rr, s);
+    case BT_FP16: return fwd_t<__half, ADD>(x, w, y, rstd, M, N, ld_x, ld_y, eps, rr, s);
+    case BT_FP32: return fwd_t<float, ADD>(x, w, y, rstd, M, N, ld_x, ld_y, eps, rr, s);
+  }
+  set_error("rmsnorm_fwd: unknown dtype %d", dtype);
+  return BT_ERR_ARG;
+}
+
+template <bool ADD>
+int bwd_any(int dtype, const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+            void* dw, void* ws, int64_t M, int64_t N, int64_t ld_dy, int64_t ld_x, int64_t ld_dx,
+            const Residual& rr, cudaStream_t s) {
+  switch (dtype) {
+    case BT_BF16:
+      return bwd_t<__nv_bfloat16, ADD>(dy, x, w, rstd, dx, dw, ws, M, N, ld_dy, ld_x, ld_dx, rr, s);
+    case BT_FP16:
+      return bwd_t<__half, ADD>(dy, x, w, rstd, dx, dw, ws, M, N, ld_dy, ld_x, ld_dx, rr, s);
+    case BT_FP32:
+      return bwd_t<float, ADD>(dy, x, w, rstd, dx, dw, ws, M, N, ld_dy, ld_x, ld_dx, rr, s);
+  }
+  set_error("rmsnorm_bwd: unknown dtype %d", dtype);
+  return BT_ERR_ARG;
+}
+
+// dw of an empty batch: zero.  The scratch is all zeros by contract, so the finalize path
+// of the generic dw kernel with an empty row range writes exactly that.
+int bwd_empty(int dtype, void* dw, void* ws, int64_t N, cudaStream_t s) {
+  dim3 g(static_cast<unsigned>(ceil_div(N, 32)), 1);
+  float* wsp = static_cast<float*>(ws);
+  const int n = static_cast<int>(N);
+  switch (dtype) {
+    case BT_BF16:
+      rms_bwd_dw_generic<__nv_bfloat16><<<g, dim3(32, 8), 0, s>>>(
+          nullptr, nullptr, nullptr, static_cast<__nv_bfloat16*>(dw), wsp, 0, n, 0, 0);
+      break;
+    case BT_FP16:
+      rms_bwd_dw_generic<__half><<<g, dim3(32, 8), 0, s>>>(nullptr, nullptr, nullptr,
+                                                          static_cast<__half*>(dw), wsp, 0, n, 0, 0);
+      break;
+    case BT_FP32:
+      rms_bwd_dw_generic<float><<<g, dim3(32, 8), 0, s>>>(nullptr, nullptr, nullptr,
+                                                         static_cast<float*>(dw), wsp, 0, n, 0, 0);
+      break;
+    default: set_error("rmsnorm_bwd: unknown dtype %d", dtype); return BT_ERR_ARG;
+  }
+  BT_CHECK_LAUNCH("rms_bwd_dw_generic(empty)");
   return BT_OK;
 }
 
@@ -438,14 +568,29 @@ extern "C" int bt_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd
   BT_CHECK_ARG(ld_x >= N && ld_y >= N, "rmsnorm_fwd: row stride smaller than N");
   if (M == 0) return BT_OK;
   BT_CHECK_ARG(x && w && y && rstd, "rmsnorm_fwd: null pointer");
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  switch (dtype) {
-    case BT_BF16: return fwd_t<__nv_bfloat16>(x, w, y, rstd, M, N, ld_x, ld_y, eps, s);
-    case BT_FP16: return fwd_t<__half>(x, w, y, rstd, M, N, ld_x, ld_y, eps, s);
-    case BT_FP32: return fwd_t<float>(x, w, y, rstd, M, N, ld_x, ld_y, eps, s);
-  }
-  set_error("rmsnorm_fwd: unknown dtype %d", dtype);
-  return BT_ERR_ARG;
+  return fwd_any<false>(dtype, x, w, y, rstd, M, N, ld_x, ld_y, eps, Residual{},
+                        static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bt_add_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* sum,
+                                  void* y, float* rstd, int64_t M, int64_t N, int64_t ld_x,
+                                  int64_t ld_residual, int64_t ld_sum, int64_t ld_y, float eps,
+                                  int dtype, void* stream) {
+  using namespace bt;
+  BT_CHECK_ARG(M >= 0 && N > 0 && N < (1ll << 31), "add_rmsnorm_fwd: bad shape M=%lld N=%lld",
+               (long long)M, (long long)N);
+  BT_CHECK_ARG(ld_x >= N && ld_y >= N && ld_residual >= N && ld_sum >= N,
+               "add_rmsnorm_fwd: row stride smaller than N");
+  if (M == 0) return BT_OK;
+  BT_CHECK_ARG(x && residual && w && sum && y && rstd, "add_rmsnorm_fwd: null pointer");
+  BT_CHECK_ARG(sum != x && sum != residual && sum != y, "add_rmsnorm_fwd: sum must not alias");
+  Residual rr;
+  rr.res = residual;
+  rr.sum = sum;
+  rr.ld_res = ld_residual;
+  rr.ld_sum = ld_sum;
+  return fwd_any<true>(dtype, x, w, y, rstd, M, N, ld_x, ld_y, eps, rr,
+                       static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int64_t bt_rmsnorm_bwd_ws_bytes(int64_t N) {
@@ -471,42 +616,29 @@ extern "C" int bt_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
   BT_CHECK_ARG(ld_x >= N && ld_dy >= N && ld_dx >= N, "rmsnorm_bwd: row stride smaller than N");
   BT_CHECK_ARG(dw && ws, "rmsnorm_bwd: null dw / ws");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (M == 0) {
-    // No rows: dw = 0.  The scratch row is all zeros by contract, so reuse the
-    // finalize path of the generic dw kernel with an empty row range.
-    dim3 g(static_cast<unsigned>(ceil_div(N, 32)), 1);
-    switch (dtype) {
-      case BT_BF16:
-        rms_bwd_dw_generic<__nv_bfloat16><<<g, dim3(32, 8), 0, s>>>(
-            nullptr, nullptr, nullptr, static_cast<__nv_bfloat16*>(dw), static_cast<float*>(ws), 0,
-            static_cast<int>(N), 0, 0);
-        break;
-      case BT_FP16:
-        rms_bwd_dw_generic<__half><<<g, dim3(32, 8), 0, s>>>(nullptr, nullptr, nullptr,
-                                                            static_cast<__half*>(dw),
-                                                            static_cast<float*>(ws), 0,
-                                                            static_cast<int>(N), 0, 0);
-        break;
-      case BT_FP32:
-        rms_bwd_dw_generic<float><<<g, dim3(32, 8), 0, s>>>(nullptr, nullptr, nullptr,
-                                                           static_cast<float*>(dw),
-                                                           static_cast<float*>(ws), 0,
-                                                           static_cast<int>(N), 0, 0);
-        break;
-      default: set_error("rmsnorm_bwd: unknown dtype %d", dtype); return BT_ERR_ARG;
-    }
-    BT_CHECK_LAUNCH("rms_bwd_dw_generic(empty)");
-    return BT_OK;
-  }
+  if (M == 0) return bwd_empty(dtype, dw, ws, N, s);
   BT_CHECK_ARG(dy && x && w && rstd && dx, "rmsnorm_bwd: null pointer");
-  switch (dtype) {
-    case BT_BF16:
-      return bwd_t<__nv_bfloat16>(dy, x, w, rstd, dx, dw, ws, M, N, ld_dy, ld_x, ld_dx, s);
-    case BT_FP16: return bwd_t<__half>(dy, x, w, rstd, dx, dw, ws, M, N, ld_dy, ld_x, ld_dx, s);
-    case BT_FP32: return bwd_t<float>(dy, x, w, rstd, dx, dw, ws, M, N, ld_dy, ld_x, ld_dx, s);
-  }
-  set_error("rmsnorm_bwd: unknown dtype %d", dtype);
-  return BT_ERR_ARG;
+  return bwd_any<false>(dtype, dy, x, w, rstd, dx, dw, ws, M, N, ld_dy, ld_x, ld_dx, Residual{}, s);
+}
+
+extern "C" int bt_add_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
+                                  const void* dresidual, void* dx, void* dw, void* ws, int64_t M,
+                                  int64_t N, int64_t ld_dy, int64_t ld_x, int64_t ld_dresidual,
+                                  int64_t ld_dx, int dtype, void* stream) {
+  using namespace bt;
+  BT_CHECK_ARG(M >= 0 && N > 0 && N < (1ll << 31), "add_rmsnorm_bwd: bad shape M=%lld N=%lld",
+               (long long)M, (long long)N);
+  BT_CHECK_ARG(ld_x >= N && ld_dy >= N && ld_dx >= N && ld_dresidual >= N,
+               "add_rmsnorm_bwd: row stride smaller than N");
+  BT_CHECK_ARG(dw && ws, "add_rmsnorm_bwd: null dw / ws");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (M == 0) return bwd_empty(dtype, dw, ws, N, s);
+  BT_CHECK_ARG(dy && x && w && rstd && dx && dresidual, "add_rmsnorm_bwd: null pointer");
+  BT_CHECK_ARG(dx != dresidual && dx != dy && dx != x, "add_rmsnorm_bwd: dx must not alias an input");
+  Residual rr;
+  rr.dres = dresidual;
+  rr.ld_dres = ld_dresidual;
+  return bwd_any<true>(dtype, dy, x, w, rstd, dx, dw, ws, M, N, ld_dy, ld_x, ld_dx, rr, s);
 }
 
 // ---------------------------------------------------------------------------

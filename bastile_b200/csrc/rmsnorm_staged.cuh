@@ -20,59 +20,6 @@
 
 namespace bt {
 
-// Last step of every RMSNorm backward kernel.  Each CTA has added its column sums into one
-// of the dw_copies(N) private rows of the scratch; the CTA that draws the last ticket sums
-// the copies into dw and leaves the scratch zeroed for the next call.  The reads are all
-// issued before any of the zeroing stores so that they overlap instead of queueing up
-// behind stores to the same array.
-template <typename T>
-__device__ __forceinline__ void dw_finalize(float* __restrict__ ws, T* __restrict__ dw, int N,
-                                            unsigned int total_ctas, int tid, int nthreads) {
-  __shared__ bool s_last;
-  const int K = dw_copies(N);
-  unsigned int* counter = reinterpret_cast<unsigned int*>(ws + static_cast<int64_t>(K) * N);
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const unsigned int ticket = atomicAdd(counter, 1u);
-    s_last = (ticket == total_ctas - 1);
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  if ((N & 3) == 0) {
-    const float4* ws4 = reinterpret_cast<const float4*>(ws);
-    const int n4 = N >> 2;
-#pragma unroll 2
-    for (int c = tid; c < n4; c += nthreads) {
-      float4 v[8];
-#pragma unroll
-      for (int k = 0; k < 8; ++k)
-        v[k] = k < K ? __ldcg(ws4 + static_cast<int64_t>(k) * n4 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-      float o[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        o[0] += v[k].x;
-        o[1] += v[k].y;
-        o[2] += v[k].z;
-        o[3] += v[k].w;
-      }
-#pragma unroll
-      for (int e = 0; e < 4; ++e) dw[c * 4 + e] = Cvt<T>::from_f(o[e]);
-    }
-  } else {
-    for (int c = tid; c < N; c += nthreads) {
-      float v = 0.f;
-      for (int k = 0; k < K; ++k) v += __ldcg(ws + static_cast<int64_t>(k) * N + c);
-      dw[c] = Cvt<T>::from_f(v);
-    }
-  }
-  __syncthreads();
-  const int64_t total = static_cast<int64_t>(K) * N;
-  for (int64_t c = tid; c < total; c += nthreads) ws[c] = 0.f;
-  if (tid == 0) *counter = 0u;
-}
-
 namespace staged {
 
 constexpr int kThreads = 256;
@@ -116,14 +63,19 @@ struct Ring {
 };
 
 // ------------------------------------------------------------------ forward
-template <typename T, int VPT, int R>
+// ADD: a stage holds R rows of x and R rows of the residual; the rounded sum replaces x in
+// shared memory (a thread only ever touches its own column slices), is written to `sum`,
+// and is what gets normalised.
+template <typename T, int VPT, int R, bool ADD>
 __global__ void __launch_bounds__(kThreads, 2)
 rms_fwd_staged(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
-               float* __restrict__ rstd, int64_t M, int N, int64_t ld_x, int64_t ld_y, float eps) {
+               float* __restrict__ rstd, int64_t M, int N, int64_t ld_x, int64_t ld_y, float eps,
+               const T* __restrict__ res, T* __restrict__ sum, int64_t ld_res, int64_t ld_sum) {
   constexpr int E = Cvt<T>::N;
+  constexpr int kArrays = ADD ? 2 : 1;
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t row_bytes = static_cast<uint32_t>(N) * sizeof(T);
-  const uint32_t stage_bytes = R * row_bytes;
+  const uint32_t stage_bytes = kArrays * R * row_bytes;
   uint8_t* data = smem;
   float* red = reinterpret_cast<float*>(smem + kStages * stage_bytes);  // [2][R][kWarps]
   Ring* ring = reinterpret_cast<Ring*>(red + 2 * R * kWarps);
@@ -142,10 +94,13 @@ rms_fwd_staged(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__
   auto issue = [&](int64_t tile, int s) {
     const int64_t r0 = tile * R;
     const int rows = static_cast<int>(M - r0 < R ? M - r0 : R);
-    ptx::mbar_arrive_expect_tx(&ring->full[s], rows * row_bytes);
-    for (int r = 0; r < rows; ++r)
-      bulk_load(data + s * stage_bytes + r * row_bytes, x + (r0 + r) * ld_x, row_bytes,
-                &ring->full[s]);
+    ptx::mbar_arrive_expect_tx(&ring->full[s], kArrays * rows * row_bytes);
+    uint8_t* base = data + s * stage_bytes;
+    for (int r = 0; r < rows; ++r) {
+      bulk_load(base + r * row_bytes, x + (r0 + r) * ld_x, row_bytes, &ring->full[s]);
+      if constexpr (ADD)
+        bulk_load(base + (R + r) * row_bytes, res + (r0 + r) * ld_res, row_bytes, &ring->full[s]);
+    }
   };
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -167,7 +122,7 @@ rms_fwd_staged(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__
   int buf = 0;
   for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
     if (!ptx::mbar_wait(&ring->full[s], phase, &ring->abort_flag, &g_wait_error, 1)) break;
-    const uint8_t* st = data + s * stage_bytes;
+    uint8_t* st = data + s * stage_bytes;
     const int64_t r0 = tile * R;
     float ss[R];
 #pragma unroll
@@ -179,7 +134,19 @@ rms_fwd_staged(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__
           const int v = threadIdx.x + i * kThreads;
           if (v < nv) {
             float f[E];
-            Cvt<T>::unpack(lds_v4(st + r * row_bytes + v * 16), f);
+            if constexpr (ADD) {
+              float b[E];
+              Cvt<T>::unpack(lds_v4(st + r * row_bytes + v * 16), f);
+              Cvt<T>::unpack(lds_v4(st + (R + r) * row_bytes + v * 16), b);
+#pragma unroll
+              for (int e = 0; e < E; ++e) f[e] += b[e];
+              const uint4 packed = Cvt<T>::pack(f);
+              *reinterpret_cast<uint4*>(st + r * row_bytes + v * 16) = packed;
+              st_global_v4(sum + (r0 + r) * ld_sum + static_cast<int64_t>(v) * E, packed);
+              Cvt<T>::unpack(packed, f);
+            } else {
+              Cvt<T>::unpack(lds_v4(st + r * row_bytes + v * 16), f);
+            }
 #pragma unroll
             for (int e = 0; e < E; ++e) ss[r] = fmaf(f[e], f[e], ss[r]);
           }
@@ -206,6 +173,7 @@ rms_fwd_staged(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__
         }
       }
     }
+    if constexpr (ADD) ptx::fence_proxy_async_smem();  // our stores before the refill's writes
     __syncthreads();  // everyone is done with stage s
     if (threadIdx.x == 0) {
       const int64_t nt = tile + static_cast<int64_t>(kStages) * gridDim.x;
@@ -221,12 +189,14 @@ rms_fwd_staged(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__
 
 // ----------------------------------------------------------------- backward
 // ws: dw_copies(N) x N fp32 column sums + arrival counter, zero on entry, left zero on exit.
-template <typename T, int VPT, int R>
+// ADD: dx also takes in `dres`, the gradient arriving along the residual path; its slices
+// are fetched straight into registers at the top of a tile, ahead of the first pass.
+template <typename T, int VPT, int R, bool ADD>
 __global__ void __launch_bounds__(kThreads, 2)
 rms_bwd_staged(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
                const float* __restrict__ rstd, T* __restrict__ dx, T* __restrict__ dw,
                float* __restrict__ ws, int64_t M, int N, int64_t ld_dy, int64_t ld_x,
-               int64_t ld_dx) {
+               int64_t ld_dx, const T* __restrict__ dres, int64_t ld_dres) {
   constexpr int E = Cvt<T>::N;
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t row_bytes = static_cast<uint32_t>(N) * sizeof(T);
@@ -277,10 +247,22 @@ rms_bwd_staged(const T* __restrict__ dy, const T* __restrict__ x, const T* __res
   uint32_t phase = 0;
   int buf = 0;
   for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const int64_t r0 = tile * R;
+    uint4 rv[ADD ? R : 1][ADD ? VPT : 1];
+    if constexpr (ADD) {
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+          const int v = threadIdx.x + i * kThreads;
+          rv[r][i] = (r0 + r < M && v < nv)
+                         ? ld_stream_v4(dres + (r0 + r) * ld_dres + static_cast<int64_t>(v) * E)
+                         : make_uint4(0, 0, 0, 0);
+        }
+    }
     if (!ptx::mbar_wait(&ring->full[s], phase, &ring->abort_flag, &g_wait_error, 2)) break;
     const uint8_t* sx = data + s * stage_bytes;
     const uint8_t* sg = sx + R * row_bytes;
-    const int64_t r0 = tile * R;
     float dot[R], rs[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -319,6 +301,12 @@ rms_bwd_staged(const T* __restrict__ dy, const T* __restrict__ x, const T* __res
             Cvt<T>::unpack(lds_v4(sg + r * row_bytes + v * 16), gf);
 #pragma unroll
             for (int e = 0; e < E; ++e) o[e] = (gf[e] * wf[i][e] - xf[e] * rs[r] * c) * rs[r];
+            if constexpr (ADD) {
+              float a[E];
+              Cvt<T>::unpack(rv[r][i], a);
+#pragma unroll
+              for (int e = 0; e < E; ++e) o[e] += a[e];
+            }
             st_global_v4(dx + row * ld_dx + static_cast<int64_t>(v) * E, Cvt<T>::pack(o));
           }
         }
@@ -352,8 +340,9 @@ rms_bwd_staged(const T* __restrict__ dy, const T* __restrict__ x, const T* __res
   dw_finalize<T>(ws, dw, N, gridDim.x, threadIdx.x, kThreads);
 }
 
-inline size_t smem_bytes(int N, int elem, int R, bool bwd) {
-  return static_cast<size_t>(kStages) * (bwd ? 2 : 1) * R * N * elem + 2 * R * kWarps * sizeof(float) +
+// `arrays`: row sets per stage (forward: x [+ residual]; backward: x and dy).
+inline size_t smem_bytes(int N, int elem, int R, int arrays) {
+  return static_cast<size_t>(kStages) * arrays * R * N * elem + 2 * R * kWarps * sizeof(float) +
          sizeof(Ring) + 16;
 }
 

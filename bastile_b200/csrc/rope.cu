@@ -94,8 +94,10 @@ __global__ void __launch_bounds__(kThreads) rope_vec(const RopeArgs a) {
         Cvt<T>::unpack(v2[u], x2);
 #pragma unroll
         for (int e = 0; e < E; ++e) {
-          o1[e] = x1[e] * c[e] - x2[e] * s[e];
-          o2[e] = x2[e] * c[e] + x1[e] * s[e];
+          // written out as explicit fused multiply-adds: the fused q/k-norm + RoPE kernels
+          // use the same two operations and stay bit-identical to this one
+          o1[e] = fmaf(-x2[e], s[e], x1[e] * c[e]);
+          o2[e] = fmaf(x1[e], s[e], x2[e] * c[e]);
         }
         st_global_v4(outp[u], Cvt<T>::pack(o1));
         st_global_v4(outp[u] + half, Cvt<T>::pack(o2));

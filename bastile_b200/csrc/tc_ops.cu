@@ -40,7 +40,7 @@ int plain_gemm(const void* A, bool a_kmajor, int64_t lda, const void* B, bool b_
                const void* A1, int64_t lda1, const void* B1, int64_t ldb1, int64_t K1, void* D,
                int64_t ldd, int64_t M, int64_t N, int64_t K, int dtype, bool out_fp32,
                const float* addend, int64_t ld_add, const float* alpha, int32_t* status,
-               cudaStream_t s) {
+               cudaStream_t s, const void* addend_t = nullptr, int64_t ld_add_t = 0) {
   Launch L;
   L.dtype = dtype;
   out_fp32 = out_fp32 || dtype == BT_FP32;
@@ -60,7 +60,10 @@ int plain_gemm(const void* A, bool a_kmajor, int64_t lda, const void* B, bool b_
   L.p.addend = addend;
   L.p.ld_add = ld_add;
   L.p.alpha = alpha;
-  L.p.vec_ok = rows_aligned(D, ldd, out_fp32 ? 4 : 2) && rows_aligned(addend, ld_add, 4);
+  L.p.addend_t = addend_t;
+  L.p.ld_add_t = ld_add_t;
+  L.p.vec_ok = rows_aligned(D, ldd, out_fp32 ? 4 : 2) && rows_aligned(addend, ld_add, 4) &&
+               rows_aligned(addend_t, ld_add_t, esize(dtype));
   return gemm::launch<gemm::EPI_PLAIN>(L, s);
 }
 
@@ -91,13 +94,15 @@ extern "C" int bt_gemm(const void* A, const void* B, void* D, int64_t M, int64_t
 
 extern "C" int bt_mlp_fwd(const void* x, const void* wg, const void* wu, const void* wd, void* gate,
                           void* up, void* h, void* y, int64_t T, int64_t H, int64_t I, int64_t ld_x,
-                          int dtype, int32_t* status, void* stream) {
+                          const void* residual, int64_t ld_residual, int dtype, int32_t* status,
+                          void* stream) {
   using namespace bt;
   BT_CHECK_ARG(is_tc(dtype), "mlp_fwd: unknown dtype %d", dtype);
   BT_CHECK_ARG(T >= 0, "mlp_fwd: negative T");
   if (T == 0) return BT_OK;
   BT_CHECK_ARG(x && wg && wu && wd && gate && up && h && y, "mlp_fwd: null pointer");
   if (int rc = check_dims("mlp_fwd", T, I, H)) return rc;
+  BT_CHECK_ARG(residual == nullptr || ld_residual >= H, "mlp_fwd: residual row stride smaller than H");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int bf16 = dtype;  // operand storage, passed through to the launches
   const int es = esize(dtype);
@@ -119,9 +124,9 @@ extern "C" int bt_mlp_fwd(const void* x, const void* wg, const void* wu, const v
     L.p.vec_ok = rows_aligned(gate, I, es) && rows_aligned(up, I, es) && rows_aligned(h, I, es);
     if (int rc = gemm::launch<gemm::EPI_SWIGLU_FWD>(L, s)) return rc;
   }
-  // y = h Wd^T
+  // y = h Wd^T (+ residual)
   return plain_gemm(h, true, I, wd, true, I, nullptr, 0, nullptr, 0, 0, y, H, T, H, I, bf16, false,
-                    nullptr, 0, nullptr, status, s);
+                    nullptr, 0, nullptr, status, s, residual, ld_residual);
 }
 
 extern "C" int bt_mlp_bwd(const void* dy, const void* x, const void* wg, const void* wu,

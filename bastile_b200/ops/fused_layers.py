@@ -1,0 +1,317 @@
+"""Fusions across the op boundaries of a Qwen3 decoder layer (opt-in: ``apply(fused_layers=True)``).
+
+The reference patches four ops and leaves what sits between them to torch: the two
+``residual + hidden_states`` adds of ``Qwen3DecoderLayer.forward`` (transformers
+modeling_qwen3.py:316-336), the gradient accumulation autograd runs where a residual branch and
+a norm branch meet, and the q_norm / k_norm -> apply_rotary_pos_emb sequence of
+``Qwen3Attention.forward`` (modeling_qwen3.py:256-261), where every head row makes three round
+trips through HBM.  This module replaces those two ``forward`` methods so that
+
+* ``residual + attention_output`` is computed inside the post-attention RMSNorm kernel
+  (``bt_add_rmsnorm_fwd``), ``residual + mlp_output`` inside the down projection's epilogue
+  (``bt_mlp_fwd`` with a residual), and both gradient merges inside the RMSNorm backward
+  (``bt_add_rmsnorm_bwd``) - no stand-alone elementwise add is left in a layer;
+* q_norm + RoPE and k_norm + RoPE are one kernel each (``bt_headnorm_rope_fwd/_bwd``).
+
+Parameters, module names and results are those of the unfused patched model: the fused kernels
+round where the separate ones round (bit-identical for the norm + RoPE pair; the residual folded
+into the down projection is added before the single rounding instead of after it).
+"""
+
+from __future__ import annotations
+
+import inspect
+import logging
+
+import torch
+
+from .. import _lib
+from .rms_norm import B200RMSNorm, _as_rows
+from .rope import _dense
+from .swiglu import B200SwiGLUMLP
+
+log = logging.getLogger(__name__)
+
+
+def _ld(t2: torch.Tensor) -> int:
+    return t2.stride(0) if t2.shape[0] > 1 else t2.shape[1]
+
+
+class AddRMSNormFunction(torch.autograd.Function):
+    """``stream = x + residual``; returns ``(rms_norm(stream) * weight, stream)``.
+
+    With ``residual=None`` the stream is ``x`` itself (returned as a second output so that the
+    gradient of whatever consumes it later comes back through this node).  Either way the
+    backward adds the stream's gradient to the norm's input gradient inside the kernel."""
+
+    @staticmethod
+    def forward(ctx, x, residual, weight, eps):
+        dev = _lib.require_cuda(x, weight)
+        lib = _lib.get_lib()
+        code = _lib.dtype_code(x.dtype)
+        shape = x.shape
+        n = shape[-1]
+        if weight.numel() != n:
+            raise ValueError(f"add_rms_norm: weight has {weight.numel()} elements, rows have {n}")
+        x2 = _as_rows(x, n)
+        m = x2.shape[0]
+        w = weight.detach()
+        if w.dtype != x.dtype:
+            w = w.to(x.dtype)
+        w = w.contiguous()
+        y = torch.empty((m, n), dtype=x.dtype, device=dev)
+        rstd = torch.empty((m,), dtype=torch.float32, device=dev)
+        if residual is None:
+            with _lib.device_of(dev), _lib.timed("rmsnorm_fwd", 1, dev):
+                rc = lib.bt_rmsnorm_fwd(x2.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), m, n, _ld(x2), n,
+                                        float(eps), code, _lib.stream_ptr(dev))
+            _lib.check(rc, "bt_rmsnorm_fwd")
+            stream2, stream = x2, x.view_as(x)
+        else:
+            if residual.shape != shape or residual.dtype != x.dtype:
+                raise ValueError("add_rms_norm: residual must match x in shape and dtype")
+            r2 = _as_rows(residual, n)
+            stream2 = torch.empty((m, n), dtype=x.dtype, device=dev)
+            with _lib.device_of(dev), _lib.timed("rmsnorm_fwd", 1, dev):
+                rc = lib.bt_add_rmsnorm_fwd(x2.data_ptr(), r2.data_ptr(), w.data_ptr(), stream2.data_ptr(),
+                                            y.data_ptr(), rstd.data_ptr(), m, n, _ld(x2), _ld(r2), n, n, float(eps),
+                                            code, _lib.stream_ptr(dev))
+            _lib.check(rc, "bt_add_rmsnorm_fwd")
+            stream = stream2.view(shape)
+        ctx.save_for_backward(stream2, w, rstd)
+        ctx.set_materialize_grads(False)  # an unused output arrives as None, not as zeros
+        ctx.shape = shape
+        ctx.weight_dtype = weight.dtype
+        ctx.has_residual = residual is not None
+        return y.view(shape), stream
+
+    @staticmethod
+    def backward(ctx, dy, dstream):
+        s2, w, rstd = ctx.saved_tensors
+        dev = s2.device
+        lib = _lib.get_lib()
+        m, n = s2.shape
+        code = _lib.dtype_code(s2.dtype)
+        if dy is None:  # only the stream was used downstream
+            return dstream, (dstream if ctx.has_residual else None), None, None
+        if dy.dtype != s2.dtype:
+            dy = dy.to(s2.dtype)
+        dy2 = _as_rows(dy, n)
+        dx = torch.empty((m, n), dtype=s2.dtype, device=dev)
+        dw = torch.empty((n,), dtype=s2.dtype, device=dev)
+        ws = _lib.zero_workspace(dev, int(lib.bt_rmsnorm_bwd_ws_bytes(n)))
+        with _lib.device_of(dev), _lib.timed("rmsnorm_bwd", 1, dev):
+            if dstream is None:
+                rc = lib.bt_rmsnorm_bwd(dy2.data_ptr(), s2.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
+                                        dw.data_ptr(), ws.data_ptr(), m, n, _ld(dy2), _ld(s2), n, code,
+                                        _lib.stream_ptr(dev))
+            else:
+                if dstream.dtype != s2.dtype:
+                    dstream = dstream.to(s2.dtype)
+                ds2 = _as_rows(dstream, n)
+                rc = lib.bt_add_rmsnorm_bwd(dy2.data_ptr(), s2.data_ptr(), w.data_ptr(), rstd.data_ptr(),
+                                            ds2.data_ptr(), dx.data_ptr(), dw.data_ptr(), ws.data_ptr(), m, n,
+                                            _ld(dy2), _ld(s2), _ld(ds2), n, code, _lib.stream_ptr(dev))
+        _lib.check(rc, "bt_add_rmsnorm_bwd")
+        if dw.dtype != ctx.weight_dtype:
+            dw = dw.to(ctx.weight_dtype)
+        dx = dx.view(ctx.shape)
+        return dx, (dx if ctx.has_residual else None), dw, None
+
+
+def add_rms_norm(x, residual, weight, eps=1e-6):
+    """``(rms_norm(x + residual) * weight, x + residual)``; ``residual`` may be None."""
+    return AddRMSNormFunction.apply(x, residual, weight, eps)
+
+
+def _head_rows_supported(head_dim: int, dtype: torch.dtype) -> bool:
+    return dtype in (torch.bfloat16, torch.float16, torch.float32) and head_dim * dtype.itemsize in (128, 256, 512)
+
+
+def _cos_sin(cos, sin, dtype):
+    if cos.shape != sin.shape or cos.stride() != sin.stride():
+        sin = sin.expand_as(cos).contiguous()
+        cos = cos.contiguous()
+    if cos.dtype != dtype:
+        cos, sin = cos.to(dtype), sin.to(dtype)
+    if cos.stride(-1) != 1:
+        cos, sin = cos.contiguous(), sin.contiguous()
+    return cos, sin
+
+
+class HeadNormRoPEFunction(torch.autograd.Function):
+    """Per-head RMSNorm then RoPE of ``x`` [B, T, H, D] (one of the q / k projections viewed per
+    head); returns [B, T, H, D] (the caller transposes to [B, H, T, D] as HF attention does)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, cos, sin, eps):
+        dev = _lib.require_cuda(x, weight, cos, sin)
+        lib = _lib.get_lib()
+        if x.dim() != 4:
+            raise ValueError("head_norm_rope: x must be [batch, seq, heads, head_dim]")
+        b, t, h, d = x.shape
+        if weight.numel() != d:
+            raise ValueError(f"head_norm_rope: weight has {weight.numel()} elements, head_dim is {d}")
+        if cos.dim() != 3 or cos.shape[1] != t or cos.shape[-1] not in (d, d // 2) or cos.shape[0] not in (1, b):
+            raise ValueError(f"head_norm_rope: cos of shape {tuple(cos.shape)} does not fit x {tuple(x.shape)}")
+        if x.stride(-1) != 1:
+            x = x.contiguous()
+        w = weight.detach()
+        if w.dtype != x.dtype:
+            w = w.to(x.dtype)
+        w = w.contiguous()
+        cos, sin = _cos_sin(cos, sin, x.dtype)
+        out = torch.empty((b, t, h, d), dtype=x.dtype, device=dev)
+        rstd = torch.empty((b * t * h,), dtype=torch.float32, device=dev)
+        code = _lib.dtype_code(x.dtype)
+        with _lib.device_of(dev), _lib.timed("rope_fwd", 1, dev):
+            rc = lib.bt_headnorm_rope_fwd(x.data_ptr(), w.data_ptr(), cos.data_ptr(), sin.data_ptr(), out.data_ptr(),
+                                          rstd.data_ptr(), b, t, h, d, _lib.I64x3(*x.stride()[:3]),
+                                          _lib.I64x3(*out.stride()[:3]), _lib.I64x2(cos.stride(0), cos.stride(1)),
+                                          cos.shape[0], float(eps), code, _lib.stream_ptr(dev))
+        _lib.check(rc, "bt_headnorm_rope_fwd")
+        ctx.save_for_backward(x, w, rstd, cos, sin)
+        ctx.weight_dtype = weight.dtype
+        ctx.x_layout = (tuple(x.shape), tuple(x.stride()))
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, w, rstd, cos, sin = ctx.saved_tensors
+        dev = x.device
+        lib = _lib.get_lib()
+        b, t, h, d = x.shape
+        if dout.dtype != x.dtype:
+            dout = dout.to(x.dtype)
+        if dout.stride(-1) != 1:
+            dout = dout.contiguous()
+        # dx takes the memory layout of x so that the projection's backward can flatten it for free
+        if _dense(ctx.x_layout):
+            dx = torch.empty_strided(ctx.x_layout[0], ctx.x_layout[1], dtype=x.dtype, device=dev)
+        else:
+            dx = torch.empty((b, t, h, d), dtype=x.dtype, device=dev)
+        dw = torch.empty((d,), dtype=x.dtype, device=dev)
+        ws = _lib.zero_workspace(dev, int(lib.bt_rmsnorm_bwd_ws_bytes(d)))
+        with _lib.device_of(dev), _lib.timed("rope_bwd", 1, dev):
+            rc = lib.bt_headnorm_rope_bwd(dout.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), cos.data_ptr(),
+                                          sin.data_ptr(), dx.data_ptr(), dw.data_ptr(), ws.data_ptr(), b, t, h, d,
+                                          _lib.I64x3(*dout.stride()[:3]), _lib.I64x3(*x.stride()[:3]),
+                                          _lib.I64x3(*dx.stride()[:3]), _lib.I64x2(cos.stride(0), cos.stride(1)),
+                                          cos.shape[0], _lib.dtype_code(x.dtype), _lib.stream_ptr(dev))
+        _lib.check(rc, "bt_headnorm_rope_bwd")
+        if dw.dtype != ctx.weight_dtype:
+            dw = dw.to(ctx.weight_dtype)
+        return dx, dw, None, None, None
+
+
+def head_norm_rope(x, weight, cos, sin, eps=1e-6):
+    """RoPE(rms_norm(x) * weight) for x [B, T, H, D] with cos/sin [1 or B, T, D]."""
+    return HeadNormRoPEFunction.apply(x, weight, cos, sin, eps)
+
+
+# ------------------------------------------------------------------ the two patched forwards
+def decoder_layer_forward(self, hidden_states, attention_mask=None, position_ids=None, past_key_values=None,
+                          use_cache=False, position_embeddings=None, **kwargs):
+    """``Qwen3DecoderLayer.forward`` (modeling_qwen3.py:316-336) with the residual adds folded
+    into the neighbouring kernels.  Falls back to separate adds around modules that are not the
+    B200 ones (a model built before ``apply()``)."""
+    norm_in, norm_post, mlp = self.input_layernorm, self.post_attention_layernorm, self.mlp
+    fused_norms = isinstance(norm_in, B200RMSNorm) and isinstance(norm_post, B200RMSNorm)
+    if fused_norms:
+        normed, stream = add_rms_norm(hidden_states, None, norm_in.weight, norm_in.variance_epsilon)
+    else:
+        stream, normed = hidden_states, norm_in(hidden_states)
+    attn_out, _ = self.self_attn(hidden_states=normed, attention_mask=attention_mask, position_ids=position_ids,
+                                 past_key_values=past_key_values, use_cache=use_cache,
+                                 position_embeddings=position_embeddings, **kwargs)
+    if fused_norms:
+        normed, stream = add_rms_norm(attn_out, stream, norm_post.weight, norm_post.variance_epsilon)
+    else:
+        stream = stream + attn_out
+        normed = norm_post(stream)
+    if isinstance(mlp, B200SwiGLUMLP):
+        return mlp(normed, residual=stream)
+    return stream + mlp(normed)
+
+
+def attention_forward(self, hidden_states, position_embeddings, attention_mask, past_key_values=None, **kwargs):
+    """``Qwen3Attention.forward`` (modeling_qwen3.py:243-288) with q_norm + RoPE and
+    k_norm + RoPE as one kernel each; everything from the cache update on is unchanged."""
+    from transformers.models.qwen3 import modeling_qwen3 as hf
+
+    lead = hidden_states.shape[:-1]
+    cos, sin = position_embeddings
+    q_lin = self.q_proj(hidden_states).view(*lead, -1, self.head_dim)
+    k_lin = self.k_proj(hidden_states).view(*lead, -1, self.head_dim)
+    value = self.v_proj(hidden_states).view(*lead, -1, self.head_dim).transpose(1, 2)
+    fusable = (q_lin.dim() == 4 and q_lin.is_cuda and isinstance(self.q_norm, B200RMSNorm)
+               and isinstance(self.k_norm, B200RMSNorm) and _head_rows_supported(self.head_dim, q_lin.dtype)
+               and cos.dim() == 3)
+    if fusable:
+        query = head_norm_rope(q_lin, self.q_norm.weight, cos, sin, self.q_norm.variance_epsilon).transpose(1, 2)
+        key = head_norm_rope(k_lin, self.k_norm.weight, cos, sin, self.k_norm.variance_epsilon).transpose(1, 2)
+    else:
+        query, key = hf.apply_rotary_pos_emb(self.q_norm(q_lin).transpose(1, 2), self.k_norm(k_lin).transpose(1, 2),
+                                             cos, sin)
+    if past_key_values is not None:
+        key, value = past_key_values.update(key, value, self.layer_idx)
+    attend = hf.ALL_ATTENTION_FUNCTIONS.get_interface(self.config._attn_implementation, hf.eager_attention_forward)
+    out, weights = attend(self, query, key, value, attention_mask,
+                          dropout=0.0 if not self.training else self.attention_dropout, scaling=self.scaling,
+                          sliding_window=self.sliding_window, **kwargs)
+    return self.o_proj(out.reshape(*lead, -1).contiguous()), weights
+
+
+# Parameters the installed transformers must give the two methods for the replacements to be
+# drop-in; anything else and the fused forwards are not installed.
+_EXPECTED_PARAMS = {
+    "Qwen3DecoderLayer": ("self", "hidden_states", "attention_mask", "position_ids", "past_key_values", "use_cache",
+                          "position_embeddings", "kwargs"),
+    "Qwen3Attention": ("self", "hidden_states", "position_embeddings", "attention_mask", "past_key_values", "kwargs"),
+}
+_REPLACEMENTS = {"Qwen3DecoderLayer": decoder_layer_forward, "Qwen3Attention": attention_forward}
+PATCH_NAMES = {"Qwen3DecoderLayer": "decoder_layer_qwen3", "Qwen3Attention": "attention_qwen3"}
+_originals: dict[str, object] = {}
+
+
+def install(hf_module, decoder_layer: bool = True, attention: bool = True) -> list[str]:
+    """Replace the two ``forward`` methods on the classes of ``hf_module``; returns the names installed."""
+    done = []
+    for cls_name, wanted in (("Qwen3DecoderLayer", decoder_layer), ("Qwen3Attention", attention)):
+        if not wanted:
+            continue
+        cls = getattr(hf_module, cls_name, None)
+        if cls is None:
+            log.warning("fused layers: %s not found", cls_name)
+            continue
+        current = cls.forward
+        if current is _REPLACEMENTS[cls_name]:
+            done.append(PATCH_NAMES[cls_name])
+            continue
+        params = tuple(inspect.signature(inspect.unwrap(current)).parameters)
+        if params != _EXPECTED_PARAMS[cls_name]:
+            log.warning("fused layers: %s.forward has parameters %s, expected %s - left alone", cls_name, params,
+                        _EXPECTED_PARAMS[cls_name])
+            continue
+        _originals[cls_name] = current
+        cls.forward = _REPLACEMENTS[cls_name]
+        done.append(PATCH_NAMES[cls_name])
+    return done
+
+
+def uninstall(hf_module, names=None) -> list[str]:
+    """Put the original ``forward`` methods back (all, or those whose patch name is in ``names``)."""
+    done = []
+    for cls_name, original in list(_originals.items()):
+        if names is not None and PATCH_NAMES[cls_name] not in names:
+            continue
+        cls = getattr(hf_module, cls_name, None)
+        if cls is not None:
+            cls.forward = original
+            done.append(PATCH_NAMES[cls_name])
+        del _originals[cls_name]
+    return done
+
+
+def installed() -> list[str]:
+    return [PATCH_NAMES[c] for c in _originals]

@@ -80,10 +80,13 @@ _GEMM_DTYPES = (torch.bfloat16, torch.float16, torch.float32)
 
 
 class SwiGLUMLPFunction(torch.autograd.Function):
-    """down(silu(gate(x)) * up(x)) as fused tcgen05 kernels (bt_mlp_fwd / bt_mlp_bwd)."""
+    """down(silu(gate(x)) * up(x)) as fused tcgen05 kernels (bt_mlp_fwd / bt_mlp_bwd).
+
+    With ``residual`` the result is ``residual + down(...)``, added in the down projection's
+    epilogue; its gradient is the incoming gradient itself."""
 
     @staticmethod
-    def forward(ctx, x, wg, wu, wd):
+    def forward(ctx, x, wg, wu, wd, residual=None):
         dev = _lib.require_cuda(x, wg, wu, wd)
         lib = _lib.get_lib()
         if x.dtype not in _GEMM_DTYPES:
@@ -99,11 +102,18 @@ class SwiGLUMLPFunction(torch.autograd.Function):
         up = torch.empty((t, inter), dtype=x.dtype, device=dev)
         h = torch.empty((t, inter), dtype=x.dtype, device=dev)
         y = torch.empty((t, hidden), dtype=x.dtype, device=dev)
+        res2 = None
+        if residual is not None:
+            if residual.shape != x.shape or residual.dtype != x.dtype:
+                raise ValueError("bastile_b200 MLP: residual must match the input's shape and dtype")
+            res2 = _rows(residual)
         st = _lib.status_word(dev)
         with _lib.device_of(dev), _lib.timed("mlp_fwd", 2, dev):
             rc = lib.bt_mlp_fwd(x2.data_ptr(), wgc.data_ptr(), wuc.data_ptr(), wdc.data_ptr(), gate.data_ptr(),
-                                up.data_ptr(), h.data_ptr(), y.data_ptr(), t, hidden, inter, _ld(x2), code,
-                                st.data_ptr(), _lib.stream_ptr(dev))
+                                up.data_ptr(), h.data_ptr(), y.data_ptr(), t, hidden, inter, _ld(x2),
+                                res2.data_ptr() if res2 is not None else None,
+                                _ld(res2) if res2 is not None else 0, code, st.data_ptr(),
+                                _lib.stream_ptr(dev))
         _lib.check(rc, "bt_mlp_fwd")
         ctx.save_for_backward(x2, wgc, wuc, wdc, gate, up, h)
         ctx.x_shape = x.shape
@@ -120,7 +130,8 @@ class SwiGLUMLPFunction(torch.autograd.Function):
         if dy.dtype != x2.dtype:
             dy = dy.to(x2.dtype)
         dy2 = _rows(dy)
-        need_x, need_g, need_u, need_d = ctx.needs_input_grad
+        need_x, need_g, need_u, need_d = ctx.needs_input_grad[:4]
+        need_res = len(ctx.needs_input_grad) > 4 and ctx.needs_input_grad[4]
         # dgate | dup share one [T, 2I] buffer and dWg | dWu one [2I, H] buffer, so that the
         # library can compute both weight gradients as a single product
         dgu = torch.empty((t, 2 * inter), dtype=gate.dtype, device=dev)
@@ -154,6 +165,7 @@ class SwiGLUMLPFunction(torch.autograd.Function):
             dwg.to(dts[0]) if dwg is not None else None,
             dwu.to(dts[1]) if dwu is not None else None,
             dwd.to(dts[2]) if dwd is not None else None,
+            dy if need_res else None,
         )
 
 
@@ -173,10 +185,15 @@ class B200SwiGLUMLP(nn.Module):
         if hasattr(config, "hidden_act") and config.hidden_act not in ["silu", "swish"]:
             raise ValueError(f"Activation function {config.hidden_act} not supported.")
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``residual`` (not part of the reference's module): returns ``residual + mlp(x)``
+        with the add folded into the down projection."""
         if torch.is_autocast_enabled() and x.is_cuda:
             x = x.to(torch.get_autocast_dtype("cuda"))
-        return SwiGLUMLPFunction.apply(x, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight)
+            if residual is not None:
+                residual = residual.to(x.dtype)
+        return SwiGLUMLPFunction.apply(x, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight,
+                                       residual)
 
 
 CuTileSwiGLUMLP = B200SwiGLUMLP

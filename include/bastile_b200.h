@@ -72,6 +72,28 @@ int bt_rmsnorm_bwd(const void* dy, const void* x, const void* w,
                    int64_t ld_dx, int dtype, void* stream);
 int64_t bt_rmsnorm_bwd_ws_bytes(int64_t N);
 
+/* The residual add in front of a norm, fused into it (the reference keeps them
+ * apart: `hidden_states = residual + hidden_states` then the patched
+ * Qwen3RMSNorm, transformers modeling_qwen3.py:326-333 around
+ * src/bastile/ops/rms_norm.py:156-168):
+ *   sum = T(x + residual)   (written out: it is the next residual stream)
+ *   y   = sum * rstd * w,   rstd from the ROUNDED sum, as the unfused pair gives.
+ * All of x, residual, sum, y are [M,N] with their own row strides. */
+int bt_add_rmsnorm_fwd(const void* x, const void* residual, const void* w,
+                       void* sum, void* y, float* rstd, int64_t M, int64_t N,
+                       int64_t ld_x, int64_t ld_residual, int64_t ld_sum,
+                       int64_t ld_y, float eps, int dtype, void* stream);
+
+/* bt_rmsnorm_bwd whose dx also takes in the gradient that reaches the norm's
+ * input along the residual path: dx = T(norm_backward(dy) + dresidual).  Saves
+ * the separate gradient-accumulation pass autograd runs where the two branches
+ * of a residual block meet.  Scratch contract as bt_rmsnorm_bwd. */
+int bt_add_rmsnorm_bwd(const void* dy, const void* x, const void* w,
+                       const float* rstd, const void* dresidual, void* dx,
+                       void* dw, void* ws, int64_t M, int64_t N, int64_t ld_dy,
+                       int64_t ld_x, int64_t ld_dresidual, int64_t ld_dx,
+                       int dtype, void* stream);
+
 /* bt_rmsnorm_bwd for callers that cannot provide scratch memory.  It has no
  * counterpart in the reference (there, torch allocates the partial-sum tensor).
  * Meant for hosts that reach this library through an FFI and hold no device
@@ -161,16 +183,53 @@ int bt_gemm(const void* A, const void* B, void* D,
  * counterpart (cuBLAS picks its own kernels). */
 int bt_set_gemm_cta_pairs(int enable);
 
+/* ------------------------------------------- per-head RMSNorm + RoPE, fused */
+
+/* q_norm / k_norm followed by the rotary embedding, for ONE tensor of heads
+ * x [B,T,H,D] (the q or k projection output viewed per head; element strides of
+ * batch, position, head in x_strides; D contiguous):
+ *   y   = T(x * rstd * w)            per head row, rstd[b,t,h] = rsqrt(mean(x^2)+eps)
+ *   out = rotate-half RoPE of y with cos/sin[b or 0, t, 0..D/2)
+ * Replaces, for one of q and k, the patched Qwen3RMSNorm on a head_dim-wide row
+ * (src/bastile/ops/rms_norm.py:105-126) and _rope_kernel
+ * (src/bastile/ops/rope.py:13-90) that Qwen3Attention.forward runs back to
+ * back (transformers modeling_qwen3.py:256-261).  rstd is [B*T*H] in (b,t,h)
+ * order.  Head rows must be 128, 256 or 512 bytes (D = 64/128/256 for 16-bit
+ * types); anything else returns BT_ERR_ARG and the caller runs bt_rmsnorm_fwd
+ * and bt_rope instead.  Results are bit-identical to that pair. */
+int bt_headnorm_rope_fwd(const void* x, const void* w, const void* cos,
+                         const void* sin, void* out, float* rstd,
+                         int64_t B, int64_t T, int64_t H, int64_t D,
+                         const int64_t x_strides[3], const int64_t out_strides[3],
+                         const int64_t cos_strides[2], int64_t cos_bs,
+                         float eps, int dtype, void* stream);
+
+/* Backward of the pair: un-rotates dout (rope.py:132-136), then the RMSNorm
+ * backward (rms_norm.py:37-68, 128-153) gives dx [B,T,H,D] and dw [D].  `ws`:
+ * bt_rmsnorm_bwd_ws_bytes(D) zeroed bytes, left zero (as bt_rmsnorm_bwd). */
+int bt_headnorm_rope_bwd(const void* dout, const void* x, const void* w,
+                         const float* rstd, const void* cos, const void* sin,
+                         void* dx, void* dw, void* ws,
+                         int64_t B, int64_t T, int64_t H, int64_t D,
+                         const int64_t dout_strides[3], const int64_t x_strides[3],
+                         const int64_t dx_strides[3], const int64_t cos_strides[2],
+                         int64_t cos_bs, int dtype, void* stream);
+
 /* ------------------------------------------------------ SwiGLU MLP (fused)  */
 
 /* Forward of CuTileSwiGLUMLP (src/bastile/ops/swiglu.py:170-187):
  *   gate = x Wg^T, up = x Wu^T  (one tensor-core kernel, two accumulators),
  *   h = T(silu(gate)) * up fused in that kernel's epilogue,  y = h Wd^T.
  * x [T,H] (row stride ld_x), Wg/Wu [I,H], Wd [H,I] contiguous; gate, up, h
- * [T,I] and y [T,H] contiguous outputs (gate/up/h are what the backward needs). */
+ * [T,I] and y [T,H] contiguous outputs (gate/up/h are what the backward needs).
+ * `residual` [T,H] (row stride ld_residual, same dtype) may be NULL; otherwise
+ * y = T(h Wd^T + residual): the `residual + hidden_states` that follows the MLP
+ * in Qwen3DecoderLayer.forward (transformers modeling_qwen3.py:331-335) is added
+ * to the fp32 accumulator in the down projection's epilogue. */
 int bt_mlp_fwd(const void* x, const void* wg, const void* wu, const void* wd,
                void* gate, void* up, void* h, void* y,
                int64_t T, int64_t H, int64_t I, int64_t ld_x,
+               const void* residual, int64_t ld_residual,
                int dtype, int32_t* status, void* stream);
 
 /* Backward of the same block (autograd of src/bastile/ops/swiglu.py:186-187

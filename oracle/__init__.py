@@ -22,6 +22,10 @@ only pin for them.
 
 from .ops import (  # noqa: F401
     adamw_step,
+    add_rms_norm_bwd,
+    add_rms_norm_fwd,
+    head_norm_rope_bwd,
+    head_norm_rope_fwd,
     lce_fwd_bwd,
     lce_shard_stats,
     merge_shard_stats,

@@ -68,6 +68,53 @@ def rope(q, k, cos, sin, negate_sin=False):
     return rot(q), rot(k)
 
 
+# ------------------------------------------------- fusions across op boundaries
+def add_rms_norm_fwd(x, residual, w, eps=1e-6, round_to=None):
+    """stream = x + residual, y = rms_norm(stream) * w; returns (y, stream, rstd).
+
+    The residual add of Qwen3DecoderLayer.forward (transformers modeling_qwen3.py:326 / :335)
+    followed by the reference's norm (src/bastile/ops/rms_norm.py:15-34).  ``round_to`` is a
+    callable that rounds the stream to its storage type before it is normalised, as the
+    separate torch add does; None keeps it exact."""
+    stream = np.asarray(x, F64) + np.asarray(residual, F64)
+    if round_to is not None:
+        stream = np.asarray(round_to(stream.astype(F32)), F64)
+    y, rstd = rms_norm_fwd(stream, w, eps)
+    return y, stream.astype(F32), rstd
+
+
+def add_rms_norm_bwd(dy, dstream, stream, w, rstd=None, eps=1e-6):
+    """Gradient of add_rms_norm_fwd with respect to the stream (= to x = to residual), and dw:
+    the norm's input gradient (rms_norm.py:37-68) plus what arrives along the residual path."""
+    dx, dw = rms_norm_bwd(dy, stream, w, rstd, eps)
+    return (np.asarray(dx, F64) + np.asarray(dstream, F64)).astype(F32), dw
+
+
+def head_norm_rope_fwd(x, w, cos, sin, eps=1e-6, round_to=None):
+    """q_norm / k_norm then RoPE for x [B,T,H,D] (a projection output viewed per head), as
+    Qwen3Attention.forward chains them (modeling_qwen3.py:256-261): the reference's norm
+    (rms_norm.py:15-34) on head_dim-wide rows, then its rotation (rope.py:44-90).  Returns
+    (out [B,T,H,D], rstd [B,T,H]).  ``round_to`` rounds the normalised heads to the storage
+    type before the rotation, as two separate kernels do."""
+    y, rstd = rms_norm_fwd(x, w, eps)
+    if round_to is not None:
+        y = round_to(y)
+    yt = np.transpose(np.asarray(y, F64), (0, 2, 1, 3))
+    out, _ = rope(yt, yt[:, :1], cos, sin)
+    return np.transpose(out, (0, 2, 1, 3)), rstd
+
+
+def head_norm_rope_bwd(dout, x, w, cos, sin, eps=1e-6, round_to=None):
+    """Gradients of head_norm_rope_fwd: un-rotate with -sin (rope.py:132-136), then the norm's
+    backward (rms_norm.py:37-68, 150-153).  Returns (dx [B,T,H,D], dw [D])."""
+    gt = np.transpose(np.asarray(dout, F64), (0, 2, 1, 3))
+    dy, _ = rope(gt, gt[:, :1], cos, sin, negate_sin=True)
+    dy = np.transpose(dy, (0, 2, 1, 3))
+    if round_to is not None:
+        dy = round_to(dy)
+    return rms_norm_bwd(dy, x, w, None, eps)
+
+
 # ---------------------------------------------------------------------- SwiGLU
 def _sigmoid(g):
     return 1.0 / (1.0 + np.exp(-g))

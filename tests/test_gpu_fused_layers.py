@@ -1,0 +1,336 @@
+"""The fusions across op boundaries (`apply(fused_layers=True)`): add + RMSNorm, q/k-norm + RoPE,
+residual in the down projection - against the CPU oracle, against the separate kernels (bit for
+bit where the rounding points are the same), and on the tiny Qwen3 against the HF eager fixture."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import BF16_TOL, FP32_TOL, assert_close, load_golden
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+DTYPES = [(torch.float32, FP32_TOL), (torch.bfloat16, BF16_TOL), (torch.float16, BF16_TOL)]
+
+
+def _np(t):
+    return t.detach().float().cpu().numpy()
+
+
+def _round_like(dtype):
+    return lambda a: torch.as_tensor(np.asarray(a, np.float32)).to(dtype).float().numpy()
+
+
+def _cos_sin(t, d, theta=1e6, dtype=torch.float32, batch=1):
+    inv = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    emb = torch.outer(torch.arange(t, dtype=torch.float32), inv)
+    emb = torch.cat((emb, emb), -1)
+    return (emb.cos()[None].expand(batch, -1, -1).contiguous().to(DEV, dtype),
+            emb.sin()[None].expand(batch, -1, -1).contiguous().to(DEV, dtype))
+
+
+# ------------------------------------------------------------------ add + RMSNorm
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("m,n", [(1, 8), (37, 128), (300, 128), (33, 1024), (130, 2048), (67, 4096), (9, 8192),
+                                 (3, 5120), (4, 100), (7, 4099), (2, 16384), (0, 128)])
+def test_add_rmsnorm_vs_oracle_and_separate_kernels(m, n, dtype, tol):
+    from bastile_b200.ops.fused_layers import add_rms_norm
+    from bastile_b200.ops.rms_norm import rms_norm
+
+    torch.manual_seed(m * 1000 + n + 1)
+    x = torch.randn(m, n, device=DEV).to(dtype).requires_grad_(True)
+    r = torch.randn(m, n, device=DEV).to(dtype).requires_grad_(True)
+    w = (1 + 0.02 * torch.randn(n, device=DEV)).to(dtype).requires_grad_(True)
+    dy = torch.randn(m, n, device=DEV).to(dtype)
+    ds = torch.randn(m, n, device=DEV).to(dtype)
+    y, stream = add_rms_norm(x, r, w, 1e-6)
+    torch.autograd.backward([y, stream], [dy, ds])
+    assert y.dtype == dtype and stream.dtype == dtype
+
+    y_ref, s_ref, rstd = oracle.add_rms_norm_fwd(_np(x), _np(r), _np(w), 1e-6, round_to=_round_like(dtype))
+    dx_ref, dw_ref = oracle.add_rms_norm_bwd(_np(dy), _np(ds), s_ref, _np(w), rstd)
+    assert_close(stream, s_ref, what="stream", **tol)
+    assert_close(y, y_ref, what="y", **tol)
+    assert_close(x.grad, dx_ref, what="dx", **tol)
+    assert torch.equal(x.grad, r.grad)
+    dw_tol = dict(rtol=tol["rtol"], atol=max(tol["atol"], 2e-2 * np.sqrt(max(m, 1)) if dtype != torch.float32 else 1e-4))
+    assert_close(w.grad, dw_ref, what="dw", **dw_tol)
+
+    # the same thing from the separate kernels: torch add, then the plain norm
+    x2, r2, w2 = (t.detach().clone().requires_grad_(True) for t in (x, r, w))
+    s2 = x2 + r2
+    y2 = rms_norm(s2, w2, 1e-6)
+    torch.autograd.backward([y2, s2], [dy, ds])
+    assert torch.equal(stream, s2) and torch.equal(y, y2)
+    assert_close(w.grad, _np(w2.grad), what="dw vs separate", **dw_tol)  # atomics: order varies
+    # dx: the fused kernel adds the stream gradient before the single rounding, autograd after it
+    assert_close(x.grad, _np(x2.grad), what="dx vs separate", **tol)
+
+
+def test_add_rmsnorm_without_residual_merges_the_stream_gradient():
+    from bastile_b200.ops.fused_layers import add_rms_norm
+
+    torch.manual_seed(5)
+    x = torch.randn(3, 50, 256, device=DEV, dtype=torch.bfloat16).requires_grad_(True)
+    w = torch.ones(256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    h = x * 1.0
+    y, stream = add_rms_norm(h, None, w, 1e-6)
+    assert stream.data_ptr() == h.data_ptr()
+    dy, ds = torch.randn_like(y), torch.randn_like(y)
+    torch.autograd.backward([y, stream], [dy, ds])
+    rstd = oracle.rms_norm_fwd(_np(x), _np(w))[1]
+    dx_ref, _ = oracle.add_rms_norm_bwd(_np(dy), _np(ds), _np(x), _np(w), rstd)
+    assert_close(x.grad, dx_ref, what="dx", **BF16_TOL)
+    # only one of the two outputs used downstream
+    for use_y in (True, False):
+        x.grad = None
+        y, stream = add_rms_norm(x * 1.0, None, w, 1e-6)
+        (y if use_y else stream).backward(dy)
+        ref = oracle.rms_norm_bwd(_np(dy), _np(x), _np(w), rstd)[0] if use_y else _np(dy)
+        assert_close(x.grad, ref, what=f"dx use_y={use_y}", **BF16_TOL)
+
+
+def test_add_rmsnorm_full_size():
+    """8192 x 4096 bf16, the per-layer shape of Qwen3-8B at sequence length 8192."""
+    from bastile_b200.ops.fused_layers import add_rms_norm
+    from bastile_b200.ops.rms_norm import rms_norm
+
+    torch.manual_seed(1)
+    m, n = 8192, 4096
+    x = torch.randn(m, n, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(m, n, device=DEV, dtype=torch.bfloat16)
+    w = (1 + 0.02 * torch.randn(n, device=DEV)).to(torch.bfloat16).requires_grad_(True)
+    dy, ds = torch.randn_like(x), torch.randn_like(x)
+    y, stream = add_rms_norm(x, r, w, 1e-6)
+    torch.autograd.backward([y, stream], [dy, ds])
+    x2, w2 = x.detach().clone().requires_grad_(True), w.detach().clone().requires_grad_(True)
+    s2 = x2 + r
+    y2 = rms_norm(s2, w2, 1e-6)
+    torch.autograd.backward([y2, s2], [dy, ds])
+    assert torch.equal(stream, s2) and torch.equal(y, y2)
+    assert_close(w.grad, _np(w2.grad), what="dw", rtol=2e-2, atol=2e-2 * float(w2.grad.float().abs().max()))
+    idx = torch.tensor([0, 1, 4095, 8191], device=DEV)
+    assert_close(x.grad[idx], _np(x2.grad[idx]), what="dx rows", **BF16_TOL)
+
+
+# ------------------------------------------------------------------ q/k-norm + RoPE
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("b,t,h,d", [(1, 130, 32, 128), (2, 17, 8, 128), (3, 9, 5, 64), (1, 1, 1, 128), (2, 33, 3, 32)])
+def test_head_norm_rope_vs_oracle_and_separate_kernels(b, t, h, d, dtype, tol):
+    from bastile_b200.ops.fused_layers import _head_rows_supported, head_norm_rope
+    from bastile_b200.ops.rms_norm import rms_norm
+    from bastile_b200.ops.rope import apply_rotary_pos_emb
+
+    if not _head_rows_supported(d, dtype):
+        pytest.skip("head rows of this size go through the separate kernels")
+    torch.manual_seed(b + t + h + d)
+    # a projection output [B, T, H*D] viewed per head, as Qwen3Attention builds it
+    x = torch.randn(b, t, h * d, device=DEV).to(dtype).requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(d, device=DEV)).to(dtype).requires_grad_(True)
+    cos, sin = _cos_sin(t, d, dtype=dtype, batch=b if b == 2 else 1)
+    dout = torch.randn(b, h, t, d, device=DEV).to(dtype)  # attention hands back [B,H,T,D]
+    out = head_norm_rope(x.view(b, t, h, d), w, cos, sin, 1e-6).transpose(1, 2)
+    out.backward(dout)
+
+    rnd = _round_like(dtype)
+    o_ref, _ = oracle.head_norm_rope_fwd(_np(x).reshape(b, t, h, d), _np(w), _np(cos), _np(sin), 1e-6, round_to=rnd)
+    dx_ref, dw_ref = oracle.head_norm_rope_bwd(_np(dout).transpose(0, 2, 1, 3), _np(x).reshape(b, t, h, d), _np(w),
+                                               _np(cos), _np(sin), 1e-6, round_to=rnd)
+    assert_close(out.transpose(1, 2), o_ref, what="out", **tol)
+    assert_close(x.grad.view(b, t, h, d), dx_ref, what="dx", **tol)
+    m = b * t * h
+    dw_tol = dict(rtol=tol["rtol"], atol=max(tol["atol"], 2e-2 * np.sqrt(m) if dtype != torch.float32 else 1e-4))
+    assert_close(w.grad, dw_ref, what="dw", **dw_tol)
+
+    # the separate kernels round at the same two places: identical bits
+    x2, w2 = x.detach().clone().requires_grad_(True), w.detach().clone().requires_grad_(True)
+    q2 = rms_norm(x2.view(b, t, h, d), w2, 1e-6).transpose(1, 2)
+    k_dummy = torch.zeros(b, 1, t, d, device=DEV, dtype=dtype)
+    o2, _ = apply_rotary_pos_emb(q2, k_dummy, cos, sin)
+    o2.backward(dout)
+    assert torch.equal(out, o2)
+    assert torch.equal(x.grad, x2.grad)
+    assert_close(w.grad, _np(w2.grad), what="dw vs separate", **dw_tol)
+
+
+def test_head_norm_rope_full_size_matches_separate_kernels():
+    """q of Qwen3-8B at sequence length 8192: 32 heads x 128."""
+    from bastile_b200.ops.fused_layers import head_norm_rope
+    from bastile_b200.ops.rms_norm import rms_norm
+    from bastile_b200.ops.rope import apply_rotary_pos_emb
+
+    torch.manual_seed(2)
+    b, t, h, d = 1, 8192, 32, 128
+    x = torch.randn(b, t, h * d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(d, device=DEV)).to(torch.bfloat16).requires_grad_(True)
+    cos, sin = _cos_sin(t, d, dtype=torch.bfloat16)
+    dout = torch.randn(b, h, t, d, device=DEV, dtype=torch.bfloat16)
+    out = head_norm_rope(x.view(b, t, h, d), w, cos, sin, 1e-6).transpose(1, 2)
+    out.backward(dout)
+    x2, w2 = x.detach().clone().requires_grad_(True), w.detach().clone().requires_grad_(True)
+    q2 = rms_norm(x2.view(b, t, h, d), w2, 1e-6).transpose(1, 2)
+    o2, _ = apply_rotary_pos_emb(q2, torch.zeros(b, 1, t, d, device=DEV, dtype=torch.bfloat16), cos, sin)
+    o2.backward(dout)
+    assert torch.equal(out, o2) and torch.equal(x.grad, x2.grad)
+    assert_close(w.grad, _np(w2.grad), what="dw", rtol=2e-2, atol=2e-2 * float(w2.grad.float().abs().max()))
+
+
+def test_head_norm_rope_rejects_unsupported_head_rows():
+    from bastile_b200 import _lib
+
+    lib = _lib.get_lib()
+    x = torch.randn(1, 4, 2, 24, device=DEV, dtype=torch.bfloat16)
+    out, rstd = torch.empty_like(x), torch.empty(8, device=DEV)
+    w = torch.ones(24, device=DEV, dtype=torch.bfloat16)
+    cos, sin = _cos_sin(4, 24, dtype=torch.bfloat16)
+    rc = lib.bt_headnorm_rope_fwd(x.data_ptr(), w.data_ptr(), cos.data_ptr(), sin.data_ptr(), out.data_ptr(),
+                                  rstd.data_ptr(), 1, 4, 2, 24, _lib.I64x3(*x.stride()[:3]),
+                                  _lib.I64x3(*out.stride()[:3]), _lib.I64x2(cos.stride(0), cos.stride(1)), 1, 1e-6, 0,
+                                  _lib.stream_ptr(x.device))
+    assert rc == -1 and b"not supported" in lib.bt_last_error()
+
+
+# ------------------------------------------------------------------ residual in the down projection
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_mlp_with_residual_vs_oracle(dtype):
+    from bastile_b200.ops.swiglu import SwiGLUMLPFunction
+
+    torch.manual_seed(3)
+    t, hidden, inter = 200, 256, 640
+    x = torch.randn(t, hidden, device=DEV).to(dtype).requires_grad_(True)
+    r = torch.randn(t, hidden, device=DEV).to(dtype).requires_grad_(True)
+    wg, wu = (torch.randn(inter, hidden, device=DEV).mul(0.05).to(dtype).requires_grad_(True) for _ in range(2))
+    wd = torch.randn(hidden, inter, device=DEV).mul(0.05).to(dtype).requires_grad_(True)
+    dy = torch.randn(t, hidden, device=DEV).to(dtype)
+    y = SwiGLUMLPFunction.apply(x, wg, wu, wd, r)
+    y.backward(dy)
+    y_ref = oracle.mlp_fwd(_np(x), _np(wg), _np(wu), _np(wd))[0] + _np(r)
+    tol = dict(rtol=2e-2, atol=2e-2) if dtype != torch.float32 else dict(rtol=5e-3, atol=5e-3)
+    assert_close(y, y_ref, what="y", **tol)
+    assert torch.equal(r.grad, dy)
+    x2, wg2, wu2, wd2 = (a.detach().clone().requires_grad_(True) for a in (x, wg, wu, wd))
+    SwiGLUMLPFunction.apply(x2, wg2, wu2, wd2).backward(dy)
+    assert torch.equal(x.grad, x2.grad) and torch.equal(wd.grad, wd2.grad) and torch.equal(wg.grad, wg2.grad)
+
+
+# ------------------------------------------------------------------ whole model
+@pytest.fixture()
+def fused():
+    import bastile_b200
+
+    bastile_b200.reset()
+    applied = bastile_b200.apply(fused_layers=True)
+    yield applied
+    bastile_b200.reset()
+
+
+def _tiny_model(dtype):
+    from golden.make_golden import build_tiny_qwen3, tiny_qwen3_config
+    from transformers import Qwen3ForCausalLM
+
+    import bastile_b200
+
+    applied = bastile_b200.get_patched_ops()
+    bastile_b200.reset()
+    stock = build_tiny_qwen3()  # CPU fp32, seed 0: the weights of the fixture
+    bastile_b200.apply(fused_layers=True)
+    assert bastile_b200.get_patched_ops() == applied
+    model = Qwen3ForCausalLM(tiny_qwen3_config())
+    model.load_state_dict(stock.state_dict())
+    return model.to(DEV, dtype).train()
+
+
+def test_apply_fused_layers_installs_and_reset_restores(fused):
+    import transformers.models.qwen3.modeling_qwen3 as q3
+
+    import bastile_b200
+    from bastile_b200.ops import fused_layers
+
+    assert fused == ["rms_norm_qwen3", "rope_qwen3", "swiglu_qwen3", "decoder_layer_qwen3", "attention_qwen3",
+                     "fused_linear_cross_entropy"]
+    assert q3.Qwen3DecoderLayer.forward is fused_layers.decoder_layer_forward
+    assert q3.Qwen3Attention.forward is fused_layers.attention_forward
+    bastile_b200.reset()
+    assert q3.Qwen3DecoderLayer.forward is not fused_layers.decoder_layer_forward
+    assert q3.Qwen3Attention.forward is not fused_layers.attention_forward
+    assert fused_layers.installed() == []
+
+
+def test_tiny_qwen3_fused_layers_match_hf_eager_fixture(fused):
+    from golden.make_golden import tiny_qwen3_inputs
+
+    from bastile_b200 import _lib
+
+    g = load_golden("tiny_qwen3.npz")
+    model = _tiny_model(torch.bfloat16)
+    ids, labels = tiny_qwen3_inputs()
+    out = model(input_ids=ids.to(DEV), labels=labels.to(DEV))
+    out.loss.backward()
+    _lib.check_status(torch.device(DEV, torch.cuda.current_device()), "tiny model, fused layers")
+    loss_ref = float(g["loss"])
+    assert abs(out.loss.item() - loss_ref) <= 5e-3 * loss_ref
+    grads = dict(model.named_parameters())
+    for name, ref_norm in zip([str(n) for n in g["names"]], g["grad_norms"]):
+        gn = grads[name].grad.float().norm().item()
+        assert np.isfinite(gn)
+        assert abs(gn - ref_norm) <= 0.08 * ref_norm + 1e-4, f"{name}: grad norm {gn} vs {ref_norm}"
+    for key in g.files:
+        if not key.startswith("grad::"):
+            continue
+        pname = key[len("grad::"):]
+        if pname.endswith("[:64,:64]"):
+            got = grads[pname[:-len("[:64,:64]")]].grad[:64, :64]
+        else:
+            got = grads[pname].grad
+        ref = g[key]
+        assert_close(got, ref, what=pname, rtol=5e-2, atol=5e-2 * float(np.abs(ref).max()))
+
+
+def test_tiny_qwen3_fused_layers_fp32_match_hf_eager_fixture(fused):
+    from golden.make_golden import tiny_qwen3_inputs
+
+    g = load_golden("tiny_qwen3.npz")
+    model = _tiny_model(torch.float32)
+    ids, labels = tiny_qwen3_inputs()
+    out = model(input_ids=ids.to(DEV), labels=labels.to(DEV))
+    out.loss.backward()
+    assert abs(out.loss.item() - float(g["loss"])) <= 1e-3 * float(g["loss"])
+    grads = dict(model.named_parameters())
+    for name, ref_norm in zip([str(n) for n in g["names"]], g["grad_norms"]):
+        gn = grads[name].grad.float().norm().item()
+        assert abs(gn - ref_norm) <= 2e-2 * ref_norm + 1e-5, f"{name}: grad norm {gn} vs {ref_norm}"
+
+
+def test_fused_layers_eval_forward_and_kv_cache_match_unfused():
+    """Inference path (no labels, generation with a cache) through the fused forwards gives the
+    logits of the unfused patched model."""
+    from golden.make_golden import build_tiny_qwen3, tiny_qwen3_config, tiny_qwen3_inputs
+    from transformers import Qwen3ForCausalLM
+
+    import bastile_b200
+
+    bastile_b200.reset()
+    stock = build_tiny_qwen3()
+    ids, _ = tiny_qwen3_inputs()
+    logits = []
+    try:
+        for fused_on in (False, True):
+            bastile_b200.reset()
+            bastile_b200.apply(fused_layers=fused_on)
+            model = Qwen3ForCausalLM(tiny_qwen3_config())
+            model.load_state_dict(stock.state_dict())
+            model = model.to(DEV, torch.bfloat16).eval()
+            with torch.no_grad():
+                full = model(input_ids=ids.to(DEV)).logits
+                first = model(input_ids=ids[:, :100].to(DEV), use_cache=True)
+                rest = model(input_ids=ids[:, 100:].to(DEV), past_key_values=first.past_key_values, use_cache=True)
+            logits.append((full, torch.cat((first.logits, rest.logits), dim=1)))
+    finally:
+        bastile_b200.reset()
+    (full_u, cached_u), (full_f, cached_f) = logits
+    scale = float(full_u.float().abs().max())
+    assert_close(full_f, _np(full_u), what="logits", rtol=2e-2, atol=2e-2 * scale)
+    assert_close(cached_f, _np(full_f), what="cached vs full", rtol=3e-2, atol=3e-2 * scale)
+    assert_close(cached_f, _np(cached_u), what="cached", rtol=2e-2, atol=2e-2 * scale)

@@ -266,7 +266,7 @@ def test_mlp_bwd_c_abi_with_separate_buffers_and_skipped_outputs():
     st = _lib.status_word(dev)
     stream = _lib.stream_ptr(dev)
     _lib.check(lib.bt_mlp_fwd(x.data_ptr(), wg.data_ptr(), wu.data_ptr(), wd.data_ptr(), gate.data_ptr(), up.data_ptr(),
-                              h.data_ptr(), y.data_ptr(), t, hidden, inter, hidden, 0, st.data_ptr(), stream), "fwd")
+                              h.data_ptr(), y.data_ptr(), t, hidden, inter, hidden, None, 0, 0, st.data_ptr(), stream), "fwd")
     dgate, dup = (torch.empty(t, inter, device=dev, dtype=torch.bfloat16) for _ in range(2))
     dx = torch.empty_like(x)
     dwg, dwd = torch.empty_like(wg), torch.empty_like(wd)

@@ -21,6 +21,18 @@ _DTYPES = {torch.bfloat16: BT_BF16, torch.float16: BT_FP16, torch.float32: BT_FP
 _lock = threading.Lock()
 _lib = None
 
+class GemmDesc(ctypes.Structure):
+    """``bt_gemm_desc`` of include/bastile_b200.h."""
+
+    _fields_ = [("A", c_void_p), ("B", c_void_p), ("lda", c_int64), ("ldb", c_int64), ("K", c_int64),
+                ("A1", c_void_p), ("B1", c_void_p), ("lda1", c_int64), ("ldb1", c_int64), ("K1", c_int64),
+                ("D", c_void_p), ("ldd", c_int64), ("M", c_int64), ("N", c_int64),
+                ("a_kmajor", ctypes.c_int32), ("b_kmajor", ctypes.c_int32),
+                ("in_dtype", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
+                ("addend", c_void_p), ("ld_addend", c_int64), ("addend_t", c_void_p), ("ld_addend_t", c_int64),
+                ("alpha", c_void_p)]
+
+
 I64x3 = c_int64 * 3
 I64x2 = c_int64 * 2
 
@@ -52,6 +64,7 @@ SIGNATURES = {
                               c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "bt_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                         c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "bt_gemm_ex": (c_int, [POINTER(GemmDesc), c_void_p, c_void_p]),
     "bt_set_gemm_cta_pairs": (c_int, [c_int]),
     "bt_mlp_fwd": (c_int, [c_void_p] * 8 + [c_int64] * 4 + [c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "bt_mlp_bwd": (c_int, [c_void_p] * 14 + [c_int64] * 6 + [c_int, c_void_p, c_void_p]),

@@ -18,7 +18,9 @@ in the reference.
 One addition, off by default: ``apply(fused_layers=True)`` also replaces
 ``Qwen3DecoderLayer.forward`` and ``Qwen3Attention.forward`` with versions that
 fold the residual adds into the norm / down-projection kernels and run
-q/k-norm + RoPE as one kernel (``ops/fused_layers.py``); the names
+q/k-norm + RoPE as one kernel (``ops/fused_layers.py``; ``gemm_projections="dx"``
+or ``"all"`` additionally moves the q/k/v/o projections' input gradient, or all of
+their products, from ``nn.Linear`` to the library's GEMM); the names
 ``"decoder_layer_qwen3"`` and ``"attention_qwen3"`` are then appended to the
 returned list, and ``reset()`` restores both methods.
 """
@@ -114,7 +116,8 @@ def apply(rms_norm: bool = True, swiglu: bool = True, rope: bool = True,
             from .ops import fused_layers
 
             applied.extend(fused_layers.install(importlib.import_module(_QWEN3), decoder_layer=True,
-                                                attention=bool(rope)))
+                                                attention=bool(rope),
+                                                projections=kwargs.get("gemm_projections", "off")))
         except Exception as exc:  # patch failures are reported, not raised
             log.warning("Could not apply the fused decoder-layer forwards: %s", exc)
 

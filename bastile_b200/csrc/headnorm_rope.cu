@@ -3,13 +3,13 @@
 // backward.  Bandwidth-bound: each head row (D elements, 128 to 512 bytes) is read once and
 // written once; unfused, the same row makes three round trips (norm, then RoPE in place).
 //
-// Layout: a group of LPR lanes owns one head row, one 16-byte vector per lane, so
-// D = LPR * (elements per vector).  Lane l < LPR/2 holds a slice of the first half of the
-// row, lane l + LPR/2 the matching slice of the second half: the rotation partner is one
-// shuffle away, and both use the same slice of the cos/sin half row.  The row sum of
-// squares (and the backward's dot product) is a shuffle reduction inside the group.  A
-// 256-thread CTA works on (256 / LPR) * kRowsPerIter rows per iteration, all loads issued
-// before the first use.
+// Layout: a group of LPR lanes owns one head row; a lane holds one 16-byte slice of the first
+// half of the row and the matching slice of the second half (D = 2 * LPR * elements per
+// vector), so the rotation needs no exchange between lanes and both slices use the same
+// 16 bytes of the cos/sin half row.  The row sum of squares (and the backward's dot product)
+// is a shuffle reduction inside the group.  A 256-thread CTA works on 256 / LPR items per
+// iteration, an item being one token's block of 4 (backward: 2) consecutive heads, with all
+// of an item's loads issued before the first use.
 //
 // Rounding points are those of the unfused pair: the normalised row is rounded to the
 // storage type before it is rotated, and the backward rounds the un-rotated gradient before
@@ -20,7 +20,6 @@ namespace bt {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kRowsPerIter = 4;
 
 struct HeadArgs {
   const void* x;     // [B,T,H,D] projection output (strides xs)
@@ -46,65 +45,94 @@ __device__ __forceinline__ float round_to(float v) {
   return Cvt<T>::to_f(Cvt<T>::from_f(v));
 }
 
-template <typename T, int LPR>
-__global__ void __launch_bounds__(kThreads, 4) headnorm_rope_fwd(const HeadArgs a) {
+// Work item = (token, block of HPI consecutive heads): the heads of one token share the
+// token's cos/sin slice, and in [B,T,H,D] storage they are adjacent in memory.
+struct Item {
+  bool valid;
+  int64_t x_off, g_off, o_off, c_off, row0;  // element offsets of head h0; rstd index of head h0
+  int h0;
+};
+
+template <int HPI>
+__device__ __forceinline__ Item locate(const HeadArgs& a, uint32_t item, uint32_t items,
+                                       uint32_t hblocks) {
+  Item it;
+  it.valid = item < items;
+  const uint32_t bt = it.valid ? item / hblocks : 0u;
+  const uint32_t hb = it.valid ? item - bt * hblocks : 0u;
+  const uint32_t b = bt / static_cast<uint32_t>(a.T);
+  const uint32_t t = bt - b * static_cast<uint32_t>(a.T);
+  it.h0 = static_cast<int>(hb) * HPI;
+  it.x_off = b * a.xs[0] + t * a.xs[1] + it.h0 * a.xs[2];
+  it.g_off = b * a.gs[0] + t * a.gs[1] + it.h0 * a.gs[2];
+  it.o_off = b * a.os[0] + t * a.os[1] + it.h0 * a.os[2];
+  it.c_off = (a.cos_bs == 1 ? 0 : b * a.cs[0]) + t * a.cs[1];
+  it.row0 = static_cast<int64_t>(bt) * a.H + it.h0;
+  return it;
+}
+
+// Row sums are formed in the order the stand-alone RMSNorm kernels use for a row of this
+// width (a chain per 16-byte slice, first-half slice + matching second-half slice, then a
+// butterfly over the slices), which keeps rstd and the backward's dot product bit-identical.
+template <typename T, int LPR, int HPI, int MINB>
+__global__ void __launch_bounds__(kThreads, MINB) headnorm_rope_fwd(const HeadArgs a) {
   constexpr int E = Cvt<T>::N;
   constexpr int kGroups = kThreads / LPR;
-  constexpr int kHalf = LPR / 2;
   const int lane = threadIdx.x % LPR;
   const int group = threadIdx.x / LPR;
-  const int j = lane % kHalf;
-  const bool second = lane >= kHalf;
-  const int64_t M = a.B * a.T * a.H;
+  const int half = a.D / 2;
+  const int H = static_cast<int>(a.H);
+  const uint32_t hblocks = static_cast<uint32_t>((H + HPI - 1) / HPI);
+  const uint32_t items = static_cast<uint32_t>(a.B * a.T) * hblocks;
   const float inv_n = 1.0f / static_cast<float>(a.D);
-  const int64_t rows_per_iter = static_cast<int64_t>(kGroups) * kRowsPerIter;
 
-  float wf[E];
-  Cvt<T>::unpack(ld_global_v4(static_cast<const T*>(a.w) + lane * E), wf);
+  float w1[E], w2[E];
+  Cvt<T>::unpack(ld_global_v4(static_cast<const T*>(a.w) + lane * E), w1);
+  Cvt<T>::unpack(ld_global_v4(static_cast<const T*>(a.w) + half + lane * E), w2);
 
-  for (int64_t base = static_cast<int64_t>(blockIdx.x) * rows_per_iter; base < M;
-       base += static_cast<int64_t>(gridDim.x) * rows_per_iter) {
-    uint4 xv[kRowsPerIter], cv[kRowsPerIter], sv[kRowsPerIter];
-    T* outp[kRowsPerIter];
-#pragma unroll
-    for (int r = 0; r < kRowsPerIter; ++r) {
-      const int64_t row = base + r * kGroups + group;
-      outp[r] = nullptr;
-      xv[r] = cv[r] = sv[r] = make_uint4(0, 0, 0, 0);
-      if (row < M) {
-        const int64_t h = row % a.H;
-        const int64_t t = (row / a.H) % a.T;
-        const int64_t b = row / (a.H * a.T);
-        const int64_t cb = (a.cos_bs == 1) ? 0 : b;
-        xv[r] = ld_stream_v4(static_cast<const T*>(a.x) + b * a.xs[0] + t * a.xs[1] + h * a.xs[2] +
-                             lane * E);
-        cv[r] = ld_global_v4(static_cast<const T*>(a.cos) + cb * a.cs[0] + t * a.cs[1] + j * E);
-        sv[r] = ld_global_v4(static_cast<const T*>(a.sin) + cb * a.cs[0] + t * a.cs[1] + j * E);
-        outp[r] = static_cast<T*>(a.out) + b * a.os[0] + t * a.os[1] + h * a.os[2] + lane * E;
-      }
+  for (uint32_t base = blockIdx.x * kGroups; base < items; base += gridDim.x * kGroups) {
+    const Item it = locate<HPI>(a, base + group, items, hblocks);
+    uint4 x1[HPI], x2[HPI];
+    uint4 cv = make_uint4(0, 0, 0, 0), sv = make_uint4(0, 0, 0, 0);
+    if (it.valid) {
+      cv = ld_global_v4(static_cast<const T*>(a.cos) + it.c_off + lane * E);
+      sv = ld_global_v4(static_cast<const T*>(a.sin) + it.c_off + lane * E);
     }
 #pragma unroll
-    for (int r = 0; r < kRowsPerIter; ++r) {
-      const int64_t row = base + r * kGroups + group;
-      float f[E], c[E], s[E], o[E];
-      Cvt<T>::unpack(xv[r], f);
-      float ss = 0.f;
+    for (int u = 0; u < HPI; ++u) {
+      const bool ok = it.valid && it.h0 + u < H;
+      const T* xp = static_cast<const T*>(a.x) + it.x_off + u * a.xs[2] + lane * E;
+      x1[u] = ok ? ld_stream_v4(xp) : make_uint4(0, 0, 0, 0);
+      x2[u] = ok ? ld_stream_v4(xp + half) : make_uint4(0, 0, 0, 0);
+    }
+    float c[E], s[E];
+    Cvt<T>::unpack(cv, c);
+    Cvt<T>::unpack(sv, s);
 #pragma unroll
-      for (int e = 0; e < E; ++e) ss = fmaf(f[e], f[e], ss);
-      ss = group_sum<LPR>(ss);
-      const float rs = rsqrtf(ss * inv_n + a.eps);
-      Cvt<T>::unpack(cv[r], c);
-      Cvt<T>::unpack(sv[r], s);
+    for (int u = 0; u < HPI; ++u) {
+      float f1[E], f2[E], o1[E], o2[E];
+      Cvt<T>::unpack(x1[u], f1);
+      Cvt<T>::unpack(x2[u], f2);
+      float p1 = 0.f, p2 = 0.f;
 #pragma unroll
       for (int e = 0; e < E; ++e) {
-        const float y = round_to<T>(f[e] * rs * wf[e]);
-        const float partner = __shfl_xor_sync(0xffffffffu, y, kHalf);
-        // first half: y1*cos - y2*sin ; second half: y2*cos + y1*sin
-        o[e] = second ? fmaf(partner, s[e], y * c[e]) : fmaf(-partner, s[e], y * c[e]);
+        p1 = fmaf(f1[e], f1[e], p1);
+        p2 = fmaf(f2[e], f2[e], p2);
       }
-      if (outp[r] != nullptr) {
-        if (lane == 0) a.rstd_out[row] = rs;
-        st_global_v4(outp[r], Cvt<T>::pack(o));
+      const float ss = group_sum<LPR>(p1 + p2);
+      const float rs = rsqrtf(ss * inv_n + a.eps);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const float y1 = round_to<T>(f1[e] * rs * w1[e]);
+        const float y2 = round_to<T>(f2[e] * rs * w2[e]);
+        o1[e] = fmaf(-y2, s[e], y1 * c[e]);  // y1*cos - y2*sin
+        o2[e] = fmaf(y1, s[e], y2 * c[e]);   // y2*cos + y1*sin
+      }
+      if (it.valid && it.h0 + u < H) {
+        if (lane == 0) a.rstd_out[it.row0 + u] = rs;
+        T* op = static_cast<T*>(a.out) + it.o_off + u * a.os[2] + lane * E;
+        st_global_v4(op, Cvt<T>::pack(o1));
+        st_global_v4(op + half, Cvt<T>::pack(o2));
       }
     }
   }
@@ -112,77 +140,81 @@ __global__ void __launch_bounds__(kThreads, 4) headnorm_rope_fwd(const HeadArgs 
 
 // dx, dw of the fused pair.  ws: dw_copies(D) x D fp32 column sums + arrival counter, zero
 // on entry, left zero on exit (the contract of the RMSNorm backward).
-template <typename T, int LPR>
-__global__ void __launch_bounds__(kThreads, 3) headnorm_rope_bwd(const HeadArgs a) {
+template <typename T, int LPR, int HPI, int MINB>
+__global__ void __launch_bounds__(kThreads, MINB) headnorm_rope_bwd(const HeadArgs a) {
   constexpr int E = Cvt<T>::N;
   constexpr int kGroups = kThreads / LPR;
-  constexpr int kHalf = LPR / 2;
-  __shared__ float s_dw[LPR * E];
+  __shared__ float s_dw[2 * LPR * E];
   const int lane = threadIdx.x % LPR;
   const int group = threadIdx.x / LPR;
-  const int j = lane % kHalf;
-  const bool second = lane >= kHalf;
   const int N = a.D;
-  const int64_t M = a.B * a.T * a.H;
+  const int half = N / 2;
+  const int H = static_cast<int>(a.H);
+  const uint32_t hblocks = static_cast<uint32_t>((H + HPI - 1) / HPI);
+  const uint32_t items = static_cast<uint32_t>(a.B * a.T) * hblocks;
   const float inv_n = 1.0f / static_cast<float>(N);
-  const int64_t rows_per_iter = static_cast<int64_t>(kGroups) * kRowsPerIter;
 
   for (int c = threadIdx.x; c < N; c += kThreads) s_dw[c] = 0.f;
 
-  float wf[E], acc[E];
-  Cvt<T>::unpack(ld_global_v4(static_cast<const T*>(a.w) + lane * E), wf);
+  float w1[E], w2[E], acc1[E], acc2[E];
+  Cvt<T>::unpack(ld_global_v4(static_cast<const T*>(a.w) + lane * E), w1);
+  Cvt<T>::unpack(ld_global_v4(static_cast<const T*>(a.w) + half + lane * E), w2);
 #pragma unroll
-  for (int e = 0; e < E; ++e) acc[e] = 0.f;
+  for (int e = 0; e < E; ++e) acc1[e] = acc2[e] = 0.f;
 
-  for (int64_t base = static_cast<int64_t>(blockIdx.x) * rows_per_iter; base < M;
-       base += static_cast<int64_t>(gridDim.x) * rows_per_iter) {
-    uint4 xv[kRowsPerIter], gv[kRowsPerIter], cv[kRowsPerIter], sv[kRowsPerIter];
-    float rs[kRowsPerIter];
-    T* outp[kRowsPerIter];
-#pragma unroll
-    for (int r = 0; r < kRowsPerIter; ++r) {
-      const int64_t row = base + r * kGroups + group;
-      outp[r] = nullptr;
-      rs[r] = 0.f;
-      xv[r] = gv[r] = cv[r] = sv[r] = make_uint4(0, 0, 0, 0);
-      if (row < M) {
-        const int64_t h = row % a.H;
-        const int64_t t = (row / a.H) % a.T;
-        const int64_t b = row / (a.H * a.T);
-        const int64_t cb = (a.cos_bs == 1) ? 0 : b;
-        rs[r] = a.rstd_in[row];
-        xv[r] = ld_stream_v4(static_cast<const T*>(a.x) + b * a.xs[0] + t * a.xs[1] + h * a.xs[2] +
-                             lane * E);
-        gv[r] = ld_stream_v4(static_cast<const T*>(a.dout) + b * a.gs[0] + t * a.gs[1] +
-                             h * a.gs[2] + lane * E);
-        cv[r] = ld_global_v4(static_cast<const T*>(a.cos) + cb * a.cs[0] + t * a.cs[1] + j * E);
-        sv[r] = ld_global_v4(static_cast<const T*>(a.sin) + cb * a.cs[0] + t * a.cs[1] + j * E);
-        outp[r] = static_cast<T*>(a.out) + b * a.os[0] + t * a.os[1] + h * a.os[2] + lane * E;
-      }
+  for (uint32_t base = blockIdx.x * kGroups; base < items; base += gridDim.x * kGroups) {
+    const Item it = locate<HPI>(a, base + group, items, hblocks);
+    uint4 x1[HPI], x2[HPI], g1[HPI], g2[HPI];
+    float rs[HPI];
+    uint4 cv = make_uint4(0, 0, 0, 0), sv = make_uint4(0, 0, 0, 0);
+    if (it.valid) {
+      cv = ld_global_v4(static_cast<const T*>(a.cos) + it.c_off + lane * E);
+      sv = ld_global_v4(static_cast<const T*>(a.sin) + it.c_off + lane * E);
     }
 #pragma unroll
-    for (int r = 0; r < kRowsPerIter; ++r) {
-      float xf[E], gf[E], c[E], s[E], dy[E], o[E];
-      Cvt<T>::unpack(xv[r], xf);
-      Cvt<T>::unpack(gv[r], gf);
-      Cvt<T>::unpack(cv[r], c);
-      Cvt<T>::unpack(sv[r], s);
-      float dot = 0.f;
+    for (int u = 0; u < HPI; ++u) {
+      const bool ok = it.valid && it.h0 + u < H;
+      const T* xp = static_cast<const T*>(a.x) + it.x_off + u * a.xs[2] + lane * E;
+      const T* gp = static_cast<const T*>(a.dout) + it.g_off + u * a.gs[2] + lane * E;
+      rs[u] = ok ? a.rstd_in[it.row0 + u] : 0.f;
+      x1[u] = ok ? ld_stream_v4(xp) : make_uint4(0, 0, 0, 0);
+      x2[u] = ok ? ld_stream_v4(xp + half) : make_uint4(0, 0, 0, 0);
+      g1[u] = ok ? ld_stream_v4(gp) : make_uint4(0, 0, 0, 0);
+      g2[u] = ok ? ld_stream_v4(gp + half) : make_uint4(0, 0, 0, 0);
+    }
+    float c[E], s[E];
+    Cvt<T>::unpack(cv, c);
+    Cvt<T>::unpack(sv, s);
+#pragma unroll
+    for (int u = 0; u < HPI; ++u) {
+      float xa[E], xb[E], ga[E], gb[E], d1[E], d2[E];
+      Cvt<T>::unpack(x1[u], xa);
+      Cvt<T>::unpack(x2[u], xb);
+      Cvt<T>::unpack(g1[u], ga);
+      Cvt<T>::unpack(g2[u], gb);
+      float p1 = 0.f, p2 = 0.f;
 #pragma unroll
       for (int e = 0; e < E; ++e) {
-        const float partner = __shfl_xor_sync(0xffffffffu, gf[e], kHalf);
         // inverse rotation: d1*cos + d2*sin ; d2*cos - d1*sin
-        dy[e] = round_to<T>(second ? fmaf(-partner, s[e], gf[e] * c[e])
-                                   : fmaf(partner, s[e], gf[e] * c[e]));
-        const float xh = xf[e] * rs[r];
-        dot = fmaf(xh, dy[e] * wf[e], dot);
-        acc[e] = fmaf(dy[e], xh, acc[e]);
+        d1[e] = round_to<T>(fmaf(gb[e], s[e], ga[e] * c[e]));
+        d2[e] = round_to<T>(fmaf(-ga[e], s[e], gb[e] * c[e]));
+        const float h1 = xa[e] * rs[u], h2 = xb[e] * rs[u];
+        p1 = fmaf(h1, d1[e] * w1[e], p1);
+        p2 = fmaf(h2, d2[e] * w2[e], p2);
+        acc1[e] = fmaf(d1[e], h1, acc1[e]);
+        acc2[e] = fmaf(d2[e], h2, acc2[e]);
       }
-      dot = group_sum<LPR>(dot) * inv_n;
-      if (outp[r] != nullptr) {
+      const float dot = group_sum<LPR>(p1 + p2) * inv_n;
+      if (it.valid && it.h0 + u < H) {
+        float o1[E], o2[E];
 #pragma unroll
-        for (int e = 0; e < E; ++e) o[e] = fmaf(-(xf[e] * rs[r]), dot, dy[e] * wf[e]) * rs[r];
-        st_global_v4(outp[r], Cvt<T>::pack(o));
+        for (int e = 0; e < E; ++e) {
+          o1[e] = fmaf(-(xa[e] * rs[u]), dot, d1[e] * w1[e]) * rs[u];
+          o2[e] = fmaf(-(xb[e] * rs[u]), dot, d2[e] * w2[e]) * rs[u];
+        }
+        T* op = static_cast<T*>(a.out) + it.o_off + u * a.os[2] + lane * E;
+        st_global_v4(op, Cvt<T>::pack(o1));
+        st_global_v4(op + half, Cvt<T>::pack(o2));
       }
     }
   }
@@ -192,17 +224,27 @@ __global__ void __launch_bounds__(kThreads, 3) headnorm_rope_bwd(const HeadArgs 
 #pragma unroll
   for (int o = LPR; o < 32; o <<= 1) {
 #pragma unroll
-    for (int e = 0; e < E; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
+    for (int e = 0; e < E; ++e) {
+      acc1[e] += __shfl_xor_sync(0xffffffffu, acc1[e], o);
+      acc2[e] += __shfl_xor_sync(0xffffffffu, acc2[e], o);
+    }
   }
-  // element-major in shared memory (index e * LPR + lane): lanes of one instruction hit
-  // different banks
+  // element-major in shared memory (index (2e + which half) * LPR + lane): lanes of one
+  // instruction hit different banks
   if ((threadIdx.x & 31) < LPR) {
 #pragma unroll
-    for (int e = 0; e < E; ++e) atomicAdd(&s_dw[e * LPR + lane], acc[e]);
+    for (int e = 0; e < E; ++e) {
+      atomicAdd(&s_dw[(2 * e) * LPR + lane], acc1[e]);
+      atomicAdd(&s_dw[(2 * e + 1) * LPR + lane], acc2[e]);
+    }
   }
   __syncthreads();
   float* my_ws = a.ws + static_cast<int64_t>(blockIdx.x % dw_copies(N)) * N;
-  for (int c = threadIdx.x; c < N; c += kThreads) atomicAdd(my_ws + c, s_dw[(c % E) * LPR + c / E]);
+  for (int c = threadIdx.x; c < N; c += kThreads) {
+    const int hsel = c >= half ? 1 : 0;
+    const int cc = c - hsel * half;  // column inside its half: slice cc / E, element cc % E
+    atomicAdd(my_ws + c, s_dw[(2 * (cc % E) + hsel) * LPR + cc / E]);
+  }
   dw_finalize<T>(a.ws, static_cast<T*>(a.dw), N, gridDim.x, threadIdx.x, kThreads);
 }
 
@@ -215,8 +257,8 @@ bool mult_of(const int64_t* s, int n, int e) {
 template <typename T, bool BWD>
 int launch_t(const HeadArgs& a, cudaStream_t s) {
   constexpr int E = Cvt<T>::N;
-  const int lpr = a.D / E;
-  bool ok = a.D % E == 0 && (lpr == 8 || lpr == 16 || lpr == 32) && aligned16(a.x) &&
+  const int lpr = a.D / (2 * E);  // lanes per head row: each holds one slice of either half
+  bool ok = a.D % (2 * E) == 0 && (lpr == 4 || lpr == 8 || lpr == 16) && aligned16(a.x) &&
             aligned16(a.w) && aligned16(a.cos) && aligned16(a.sin) && aligned16(a.out) &&
             mult_of(a.xs, 3, E) && mult_of(a.os, 3, E) && mult_of(a.cs, 2, E);
   if (BWD) ok = ok && aligned16(a.dout) && mult_of(a.gs, 3, E);
@@ -227,21 +269,25 @@ int launch_t(const HeadArgs& a, cudaStream_t s) {
               a.D);
     return BT_ERR_ARG;
   }
-  const int64_t M = a.B * a.T * a.H;
-  const int64_t rows_per_iter = static_cast<int64_t>(kThreads / lpr) * kRowsPerIter;
-  const int64_t blocks = ceil_div(M, rows_per_iter);
-  const int64_t cap = static_cast<int64_t>(sm_count()) * (BWD ? 4 : 32);
+  constexpr int kHpi = BWD ? 2 : 4;  // heads per work item: 16-byte loads in flight per lane = 2 (4) * kHpi
+  const int64_t items = a.B * a.T * ceil_div(a.H, kHpi);
+  if (items >= (1ll << 31) || a.B * a.T * a.H >= (1ll << 31)) {
+    set_error("headnorm_rope: %lld head rows exceed the 32-bit work index", (long long)(a.B * a.T * a.H));
+    return BT_ERR_ARG;
+  }
+  const int64_t blocks = ceil_div(items, kThreads / lpr);
+  const int64_t cap = static_cast<int64_t>(sm_count()) * (BWD ? 2 : 8);
   const unsigned grid = static_cast<unsigned>(blocks < cap ? blocks : cap);
 #define BT_HEAD(L)                                                         \
   if (lpr == L) {                                                          \
     if (BWD)                                                               \
-      headnorm_rope_bwd<T, L><<<grid, kThreads, 0, s>>>(a);                \
+      headnorm_rope_bwd<T, L, kHpi, 2><<<grid, kThreads, 0, s>>>(a);       \
     else                                                                   \
-      headnorm_rope_fwd<T, L><<<grid, kThreads, 0, s>>>(a);                \
+      headnorm_rope_fwd<T, L, kHpi, 3><<<grid, kThreads, 0, s>>>(a);       \
   }
+  BT_HEAD(4)
   BT_HEAD(8)
   BT_HEAD(16)
-  BT_HEAD(32)
 #undef BT_HEAD
   BT_CHECK_LAUNCH(BWD ? "headnorm_rope_bwd" : "headnorm_rope_fwd");
   return BT_OK;

@@ -92,6 +92,30 @@ extern "C" int bt_gemm(const void* A, const void* B, void* D, int64_t M, int64_t
                     status, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int bt_gemm_ex(const bt_gemm_desc* d, int32_t* status, void* stream) {
+  using namespace bt;
+  BT_CHECK_ARG(d != nullptr, "gemm_ex: null descriptor");
+  BT_CHECK_ARG(is_tc(d->in_dtype), "gemm_ex: operands must be bf16, fp16 or fp32 (got dtype %d)",
+               d->in_dtype);
+  BT_CHECK_ARG(d->out_dtype == d->in_dtype || d->out_dtype == BT_FP32,
+               "gemm_ex: result must have the operand dtype or be fp32");
+  BT_CHECK_ARG(d->A && d->B && d->D, "gemm_ex: null pointer");
+  if (int rc = check_dims("gemm_ex", d->M, d->N, d->K)) return rc;
+  const bool second = d->A1 != nullptr;
+  if (second) {
+    BT_CHECK_ARG(d->B1 != nullptr, "gemm_ex: second product has A1 but no B1");
+    if (int rc = check_dims("gemm_ex (second product)", d->M, d->N, d->K1)) return rc;
+  }
+  BT_CHECK_ARG(d->ldd >= d->N && (d->addend == nullptr || d->ld_addend >= d->N) &&
+                   (d->addend_t == nullptr || d->ld_addend_t >= d->N),
+               "gemm_ex: result / addend stride too small");
+  return plain_gemm(d->A, d->a_kmajor != 0, d->lda, d->B, d->b_kmajor != 0, d->ldb,
+                    second ? d->A1 : nullptr, d->lda1, second ? d->B1 : nullptr, d->ldb1,
+                    second ? d->K1 : 0, d->D, d->ldd, d->M, d->N, d->K, d->in_dtype,
+                    d->out_dtype == BT_FP32, d->addend, d->ld_addend, d->alpha, status,
+                    static_cast<cudaStream_t>(stream), d->addend_t, d->ld_addend_t);
+}
+
 extern "C" int bt_mlp_fwd(const void* x, const void* wg, const void* wu, const void* wd, void* gate,
                           void* up, void* h, void* y, int64_t T, int64_t H, int64_t I, int64_t ld_x,
                           const void* residual, int64_t ld_residual, int dtype, int32_t* status,

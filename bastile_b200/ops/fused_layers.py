@@ -20,6 +20,7 @@ into the down projection is added before the single rounding instead of after it
 
 from __future__ import annotations
 
+import ctypes
 import inspect
 import logging
 
@@ -209,6 +210,139 @@ def head_norm_rope(x, weight, cos, sin, eps=1e-6):
     return HeadNormRoPEFunction.apply(x, weight, cos, sin, eps)
 
 
+# ------------------------------------------------------------------ projections on the tcgen05 GEMM
+_GEMM_DTYPES = (torch.bfloat16, torch.float16, torch.float32)
+# How the patched attention forward runs the q/k/v/o projections (install(projections=...)):
+#   "off": nn.Linear;  "dx": nn.Linear's GEMMs for the outputs and the weight gradients, but the
+#   shared input gradient dX = dQ Wq + dK Wk + dV Wv from two bt_gemm_ex launches (no accumulation
+#   passes);  "all": every product of q/k/v/o_proj on bt_gemm_ex.
+PROJECTION_MODES = ("off", "dx", "all")
+_projection_mode = "off"
+
+
+def _gemm(a, b, out, m, n, k, a_kmajor, b_kmajor, *, a1=None, b1=None, k1=0, addend_t=None, label, dev):
+    """out[m,n] = op(a) op(b) (+ op(a1) op(b1)) (+ addend_t) through bt_gemm_ex; 2-D row-major tensors."""
+    lib = _lib.get_lib()
+    d = _lib.GemmDesc()
+    d.A, d.B, d.lda, d.ldb, d.K = a.data_ptr(), b.data_ptr(), a.stride(0), b.stride(0), k
+    if a1 is not None:
+        d.A1, d.B1, d.lda1, d.ldb1, d.K1 = a1.data_ptr(), b1.data_ptr(), a1.stride(0), b1.stride(0), k1
+    d.D, d.ldd, d.M, d.N = out.data_ptr(), out.stride(0), m, n
+    d.a_kmajor, d.b_kmajor = int(a_kmajor), int(b_kmajor)
+    d.in_dtype = _lib.dtype_code(a.dtype)
+    d.out_dtype = _lib.dtype_code(out.dtype)
+    if addend_t is not None:
+        d.addend_t, d.ld_addend_t = addend_t.data_ptr(), addend_t.stride(0)
+    st = _lib.status_word(dev)
+    with _lib.device_of(dev), _lib.timed(label, 1, dev):
+        rc = lib.bt_gemm_ex(ctypes.byref(d), st.data_ptr(), _lib.stream_ptr(dev))
+    _lib.check(rc, "bt_gemm_ex")
+
+
+def _rows2d(t: torch.Tensor) -> torch.Tensor:
+    """[..., n] -> [rows, n], unit inner stride, row stride a multiple of 8 elements (16-byte rows)."""
+    n = t.shape[-1]
+    t2 = t.reshape(-1, n)
+    if t2.stride(-1) != 1 or (t2.shape[0] > 1 and (t2.stride(0) < n or t2.stride(0) % 8 != 0)):
+        t2 = t2.contiguous()
+    return t2
+
+
+def _weight(w: torch.Tensor, dtype) -> torch.Tensor:
+    w = w.detach()
+    if w.dtype != dtype:
+        w = w.to(dtype)
+    return w.contiguous()
+
+
+class SharedInputLinearFunction(torch.autograd.Function):
+    """``tuple(x @ w.T for w in weights)`` for bias-free linear layers that share their input
+    (the q / k / v projections; with one weight, a plain linear such as o_proj) on the tcgen05
+    GEMM.  The backward forms ``dx = sum_i dy_i @ w_i`` inside the GEMMs - two products per
+    launch accumulate in tensor memory, a third takes the running sum in as an addend - instead
+    of one GEMM per layer plus the accumulation passes autograd would add."""
+
+    @staticmethod
+    def forward(ctx, dx_only, x, *weights):
+        dev = _lib.require_cuda(x, *weights)
+        if x.dtype not in _GEMM_DTYPES:
+            raise TypeError(f"bastile_b200 linear: unsupported dtype {x.dtype}")
+        k = x.shape[-1]
+        x2 = _rows2d(x)
+        m = x2.shape[0]
+        ws = [_weight(w, x.dtype) for w in weights]
+        outs = []
+        for w in ws:
+            if w.dim() != 2 or w.shape[1] != k:
+                raise ValueError(f"bastile_b200 linear: weight {tuple(w.shape)} does not fit input [..., {k}]")
+            if dx_only:
+                y = torch.mm(x2, w.t())
+            else:
+                y = torch.empty((m, w.shape[0]), dtype=x.dtype, device=dev)
+                if m > 0:
+                    _gemm(x2, w, y, m, w.shape[0], k, True, True, label="proj_fwd", dev=dev)
+            outs.append(y.view(*x.shape[:-1], w.shape[0]))
+        ctx.dx_only = bool(dx_only)
+        ctx.save_for_backward(x2, *ws)
+        ctx.x_shape = x.shape
+        ctx.w_dtypes = [w.dtype for w in weights]
+        ctx.set_materialize_grads(False)
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *dys):
+        x2, *ws = ctx.saved_tensors
+        dev = x2.device
+        m, k = x2.shape
+        live = [(i, _rows2d(dy.to(x2.dtype))) for i, dy in enumerate(dys) if dy is not None]
+        dx = None
+        if ctx.needs_input_grad[1] and live and m > 0:
+            dx = torch.empty((m, k), dtype=x2.dtype, device=dev)
+            todo = list(live)
+            first = True
+            while todo:
+                # with an odd count, the first launch takes one product so that every later one
+                # carries two and the running sum
+                take = 1 if (first and len(todo) % 2 == 1) else 2
+                pairs, todo = todo[:take], todo[take:]
+                (i0, g0) = pairs[0]
+                kw = {}
+                if len(pairs) == 2:
+                    i1, g1 = pairs[1]
+                    kw = dict(a1=g1, b1=ws[i1], k1=ws[i1].shape[0])
+                # dy_i [m, n_i] is K-major; w_i [n_i, k] is stored [K, N]: N-major
+                _gemm(g0, ws[i0], dx, m, k, ws[i0].shape[0], True, False, addend_t=None if first else dx,
+                      label="proj_bwd", dev=dev, **kw)
+                first = False
+            dx = dx.view(ctx.x_shape)
+        elif ctx.needs_input_grad[1]:
+            dx = torch.zeros(ctx.x_shape, dtype=x2.dtype, device=dev)
+        dws = [None] * len(ws)
+        for i, g in live:
+            if ctx.needs_input_grad[2 + i]:
+                n = ws[i].shape[0]
+                if ctx.dx_only:
+                    dws[i] = torch.mm(g.t(), x2).to(ctx.w_dtypes[i])
+                    continue
+                dw = torch.empty((n, k), dtype=x2.dtype, device=dev)
+                if m > 0:
+                    # dw = dy^T x: both operands stored [K = rows, ...]: M-major and N-major
+                    _gemm(g, x2, dw, n, k, m, False, False, label="proj_bwd", dev=dev)
+                else:
+                    dw.zero_()
+                dws[i] = dw.to(ctx.w_dtypes[i])
+        return (None, dx, *dws)
+
+
+def shared_input_linear(x, *weights, dx_only: bool = False):
+    """``dx_only``: outputs and weight gradients from torch.mm, only the input gradient fused."""
+    return SharedInputLinearFunction.apply(dx_only, x, *weights)
+
+
+def _plain_linear(mod) -> bool:
+    return type(mod) is torch.nn.Linear and mod.bias is None
+
+
 # ------------------------------------------------------------------ the two patched forwards
 def decoder_layer_forward(self, hidden_states, attention_mask=None, position_ids=None, past_key_values=None,
                           use_cache=False, position_embeddings=None, **kwargs):
@@ -241,9 +375,17 @@ def attention_forward(self, hidden_states, position_embeddings, attention_mask, 
 
     lead = hidden_states.shape[:-1]
     cos, sin = position_embeddings
-    q_lin = self.q_proj(hidden_states).view(*lead, -1, self.head_dim)
-    k_lin = self.k_proj(hidden_states).view(*lead, -1, self.head_dim)
-    value = self.v_proj(hidden_states).view(*lead, -1, self.head_dim).transpose(1, 2)
+    on_gemm = (_projection_mode != "off" and hidden_states.is_cuda and hidden_states.dtype in _GEMM_DTYPES
+               and hidden_states.shape[-1] % 8 == 0 and self.head_dim % 8 == 0
+               and all(_plain_linear(m) for m in (self.q_proj, self.k_proj, self.v_proj, self.o_proj)))
+    if on_gemm:
+        q_lin, k_lin, v_lin = shared_input_linear(hidden_states, self.q_proj.weight, self.k_proj.weight,
+                                                  self.v_proj.weight, dx_only=_projection_mode == "dx")
+    else:
+        q_lin, k_lin, v_lin = self.q_proj(hidden_states), self.k_proj(hidden_states), self.v_proj(hidden_states)
+    q_lin = q_lin.view(*lead, -1, self.head_dim)
+    k_lin = k_lin.view(*lead, -1, self.head_dim)
+    value = v_lin.view(*lead, -1, self.head_dim).transpose(1, 2)
     fusable = (q_lin.dim() == 4 and q_lin.is_cuda and isinstance(self.q_norm, B200RMSNorm)
                and isinstance(self.k_norm, B200RMSNorm) and _head_rows_supported(self.head_dim, q_lin.dtype)
                and cos.dim() == 3)
@@ -259,7 +401,10 @@ def attention_forward(self, hidden_states, position_embeddings, attention_mask, 
     out, weights = attend(self, query, key, value, attention_mask,
                           dropout=0.0 if not self.training else self.attention_dropout, scaling=self.scaling,
                           sliding_window=self.sliding_window, **kwargs)
-    return self.o_proj(out.reshape(*lead, -1).contiguous()), weights
+    out = out.reshape(*lead, -1).contiguous()
+    if on_gemm and _projection_mode == "all":
+        return shared_input_linear(out, self.o_proj.weight)[0], weights
+    return self.o_proj(out), weights
 
 
 # Parameters the installed transformers must give the two methods for the replacements to be
@@ -274,8 +419,13 @@ PATCH_NAMES = {"Qwen3DecoderLayer": "decoder_layer_qwen3", "Qwen3Attention": "at
 _originals: dict[str, object] = {}
 
 
-def install(hf_module, decoder_layer: bool = True, attention: bool = True) -> list[str]:
-    """Replace the two ``forward`` methods on the classes of ``hf_module``; returns the names installed."""
+def install(hf_module, decoder_layer: bool = True, attention: bool = True, projections: str = "off") -> list[str]:
+    """Replace the two ``forward`` methods on the classes of ``hf_module``; returns the names installed.
+    ``projections`` is one of PROJECTION_MODES."""
+    global _projection_mode
+    if projections not in PROJECTION_MODES:
+        raise ValueError(f"projections must be one of {PROJECTION_MODES}, got {projections!r}")
+    _projection_mode = projections
     done = []
     for cls_name, wanted in (("Qwen3DecoderLayer", decoder_layer), ("Qwen3Attention", attention)):
         if not wanted:

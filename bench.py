@@ -384,6 +384,13 @@ def main():
     ap.add_argument("--optimizer", default="bastile", choices=["bastile", "torch"],
                     help="bastile: bastile_b200.optim.AdamW (one streaming kernel per tensor); torch: "
                          "torch.optim.AdamW(fused=True), what the reference's benchmark loop uses")
+    ap.add_argument("--no-fused-layers", action="store_true",
+                    help="leave Qwen3DecoderLayer.forward / Qwen3Attention.forward as HF has them (by default the "
+                         "bench applies bastile_b200.apply(fused_layers=True): residual adds folded into the norm "
+                         "and down-projection kernels, q/k-norm + RoPE as one kernel)")
+    ap.add_argument("--gemm-projections", default="off", choices=["off", "dx", "all"],
+                    help="with fused layers: off = q/k/v/o_proj stay on nn.Linear (cuBLAS); dx = their shared input "
+                         "gradient from two bt_gemm_ex launches; all = every product of theirs on bt_gemm_ex")
     ap.add_argument("--no-per-op", action="store_true")
     ap.add_argument("--only-op", default=None, choices=["rmsnorm", "rope", "mlp", "lce"],
                     help="run just this op's forward+backward micro-benchmark (small case for profilers)")
@@ -424,8 +431,11 @@ def main():
             dist.destroy_process_group()
         return
 
-    applied = bastile_b200.apply()
-    assert applied == ["rms_norm_qwen3", "rope_qwen3", "swiglu_qwen3", "fused_linear_cross_entropy"], applied
+    fused_layers = not args.no_fused_layers
+    applied = bastile_b200.apply(fused_layers=fused_layers, gemm_projections=args.gemm_projections)
+    expected = ["rms_norm_qwen3", "rope_qwen3", "swiglu_qwen3"]
+    expected += ["decoder_layer_qwen3", "attention_qwen3"] if fused_layers else []
+    assert applied == expected + ["fused_linear_cross_entropy"], applied
     peaks, peak_kind = load_peaks()
 
     cfg = Qwen3Config(**{**QWEN3_8B, "num_hidden_layers": args.layers, "intermediate_size": args.intermediate})
@@ -567,7 +577,7 @@ def main():
                                    "batch 1 fwd+bwd+AdamW, random init",
                        "global_batch_tokens": seq * world, "seq_len": seq,
                        "parallelism": parallelism,
-                       "attention": "torch SDPA", "activation_checkpointing": bool(args.grad_checkpoint), "optimizer": ("bastile_b200.optim.AdamW" if args.optimizer == "bastile" else "torch.optim.AdamW(fused=True)")
+                       "attention": "torch SDPA", "activation_checkpointing": bool(args.grad_checkpoint), "fused_layers": fused_layers, "gemm_projections": args.gemm_projections if fused_layers else "off", "optimizer": ("bastile_b200.optim.AdamW" if args.optimizer == "bastile" else "torch.optim.AdamW(fused=True)")
                                     + ", bf16 params and state",
                        "l2": "each step streams ~65 GB of weights, gradients and optimizer state: far larger than the 126 MB L2"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": seq * 8, "d2h_bytes_per_step": 4,

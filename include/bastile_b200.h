@@ -176,6 +176,29 @@ int bt_gemm(const void* A, const void* B, void* D,
             const float* addend, int64_t ld_addend, const float* alpha,
             int32_t* status, void* stream);
 
+/* bt_gemm with the rest of what the kernel can do, described by a struct (zero it, then
+ * fill in what is needed):
+ *   D = T_out(alpha[0] * (op(A)*op(B) + op(A1)*op(B1) + addend + addend_t))
+ * A1/B1 is an optional second product (contraction length K1, same M, N and operand
+ * layouts) accumulated in tensor memory before the epilogue; `addend_t` is an optional
+ * [M,N] addend stored in the operand dtype, which may alias D (each element is read
+ * before it is written).  With these, the input gradient of several linear layers that
+ * share their input - dX = dQ Wq + dK Wk + dV Wv for the q/k/v projections of
+ * Qwen3Attention (transformers modeling_qwen3.py:256-258), three cuBLAS GEMMs plus two
+ * accumulation passes under autograd - is two launches and no elementwise pass. */
+typedef struct bt_gemm_desc {
+  const void* A;  const void* B;  int64_t lda, ldb, K;
+  const void* A1; const void* B1; int64_t lda1, ldb1, K1;   /* A1 == NULL: no second product */
+  void* D; int64_t ldd;
+  int64_t M, N;
+  int32_t a_kmajor, b_kmajor;      /* both products */
+  int32_t in_dtype, out_dtype;
+  const float* addend;  int64_t ld_addend;     /* fp32, or NULL */
+  const void* addend_t; int64_t ld_addend_t;   /* operand dtype, or NULL */
+  const float* alpha;                          /* device scalar, or NULL */
+} bt_gemm_desc;
+int bt_gemm_ex(const bt_gemm_desc* desc, int32_t* status, void* stream);
+
 /* Selects how the tensor-core kernels tile their work: 0 = one CTA per 128x256
  * output tile (tcgen05 cta_group::1), 1 = pairs of CTAs in a 2-CTA cluster on
  * 256x256 tiles (cta_group::2).  A negative argument only queries.  Returns the

@@ -215,13 +215,61 @@ def test_mlp_with_residual_vs_oracle(dtype):
     assert torch.equal(x.grad, x2.grad) and torch.equal(wd.grad, wd2.grad) and torch.equal(wg.grad, wg2.grad)
 
 
+# ------------------------------------------------------------------ projections sharing their input
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("dx_only", [False, True])
+@pytest.mark.parametrize("widths", [(512, 128, 128), (256,), (384, 128), (128, 128, 128, 256)])
+def test_shared_input_linear_vs_float64(widths, dtype, dx_only):
+    """y_i = x W_i^T, dx = sum_i dy_i W_i (accumulated inside the GEMMs), dW_i = dy_i^T x."""
+    from bastile_b200 import _lib
+    from bastile_b200.ops.fused_layers import shared_input_linear
+
+    torch.manual_seed(len(widths) * 7 + widths[0])
+    rows, hidden = 333, 256
+    x = torch.randn(3, rows // 3, hidden, device=DEV).to(dtype).requires_grad_(True)
+    ws = [torch.randn(n, hidden, device=DEV).mul(0.05).to(dtype).requires_grad_(True) for n in widths]
+    dys = [torch.randn(3, rows // 3, n, device=DEV).to(dtype) for n in widths]
+    ys = shared_input_linear(x, *ws, dx_only=dx_only)
+    torch.autograd.backward(list(ys), dys)
+    _lib.check_status(x.device, "shared_input_linear")
+    x64 = x.detach().double().cpu().reshape(-1, hidden)
+    tol = dict(rtol=2e-2, atol=2e-2) if dtype != torch.float32 else dict(rtol=5e-3, atol=5e-3)
+    dx_ref = torch.zeros_like(x64)
+    for y, w, dy in zip(ys, ws, dys):
+        w64, dy64 = w.detach().double().cpu(), dy.double().cpu().reshape(-1, w.shape[0])
+        assert y.dtype == dtype and y.shape == (3, rows // 3, w.shape[0])
+        assert_close(y.reshape(-1, w.shape[0]), (x64 @ w64.T).numpy(), what="y", **tol)
+        dw_ref = (dy64.T @ x64).numpy()
+        assert_close(w.grad, dw_ref, what="dW", rtol=tol["rtol"], atol=tol["atol"] * float(np.abs(dw_ref).max()))
+        dx_ref += dy64 @ w64
+    assert_close(x.grad.reshape(-1, hidden), dx_ref.numpy(), what="dx", rtol=tol["rtol"],
+                 atol=tol["atol"] * float(dx_ref.abs().max()))
+
+
+def test_shared_input_linear_partial_gradients():
+    """An output that is not used downstream contributes nothing; weights can be frozen."""
+    from bastile_b200.ops.fused_layers import shared_input_linear
+
+    torch.manual_seed(11)
+    x = torch.randn(64, 128, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w0 = torch.randn(256, 128, device=DEV, dtype=torch.bfloat16).mul(0.05).requires_grad_(True)
+    w1 = torch.randn(128, 128, device=DEV, dtype=torch.bfloat16).mul(0.05)  # frozen
+    y0, y1 = shared_input_linear(x, w0, w1)
+    dy1 = torch.randn_like(y1)
+    y1.backward(dy1)
+    assert w0.grad is None
+    ref = dy1.double() @ w1.double()
+    assert_close(x.grad, ref.cpu().numpy(), what="dx", rtol=2e-2, atol=2e-2 * float(ref.abs().max()))
+
+
 # ------------------------------------------------------------------ whole model
-@pytest.fixture()
-def fused():
+@pytest.fixture(params=["off", "dx", "all"])
+def fused(request):
+    """apply(fused_layers=True) in each mode of the q/k/v/o projections."""
     import bastile_b200
 
     bastile_b200.reset()
-    applied = bastile_b200.apply(fused_layers=True)
+    applied = bastile_b200.apply(fused_layers=True, gemm_projections=request.param)
     yield applied
     bastile_b200.reset()
 
@@ -232,10 +280,12 @@ def _tiny_model(dtype):
 
     import bastile_b200
 
-    applied = bastile_b200.get_patched_ops()
+    from bastile_b200.ops import fused_layers
+
+    applied, mode = bastile_b200.get_patched_ops(), fused_layers._projection_mode
     bastile_b200.reset()
     stock = build_tiny_qwen3()  # CPU fp32, seed 0: the weights of the fixture
-    bastile_b200.apply(fused_layers=True)
+    bastile_b200.apply(fused_layers=True, gemm_projections=mode)
     assert bastile_b200.get_patched_ops() == applied
     model = Qwen3ForCausalLM(tiny_qwen3_config())
     model.load_state_dict(stock.state_dict())

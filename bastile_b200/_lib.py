@@ -49,10 +49,10 @@ SIGNATURES = {
     "bt_rmsnorm_bwd_ws_bytes": (c_int64, [c_int64]),
     "bt_add_rmsnorm_fwd": (c_int, [c_void_p] * 6 + [c_int64] * 6 + [c_float, c_int, c_void_p]),
     "bt_add_rmsnorm_bwd": (c_int, [c_void_p] * 8 + [c_int64] * 6 + [c_int, c_void_p]),
-    "bt_headnorm_rope_fwd": (c_int, [c_void_p] * 6 + [c_int64] * 4 + [POINTER(c_int64)] * 3 +
-                             [c_int64, c_float, c_int, c_void_p]),
-    "bt_headnorm_rope_bwd": (c_int, [c_void_p] * 9 + [c_int64] * 4 + [POINTER(c_int64)] * 4 +
-                             [c_int64, c_int, c_void_p]),
+    "bt_qk_norm_rope_fwd": (c_int, [c_void_p] * 10 + [c_int64] * 5 + [POINTER(c_int64)] * 5 +
+                            [c_int64, c_float, c_float, c_int, c_void_p]),
+    "bt_qk_norm_rope_bwd": (c_int, [c_void_p] * 16 + [c_int64] * 5 + [POINTER(c_int64)] * 7 +
+                            [c_int64, c_int, c_void_p]),
     "bt_rmsnorm_bwd_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                        c_int64, c_int64, c_int64, c_int, c_void_p]),
     "bt_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,

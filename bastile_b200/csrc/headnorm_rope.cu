@@ -1,6 +1,6 @@
-// Per-head RMSNorm followed by rotate-half RoPE as ONE pass over a [B,T,H,D] tensor of heads
-// (the q_norm / k_norm + apply_rotary_pos_emb sequence of Qwen3 attention), forward and
-// backward.  Bandwidth-bound: each head row (D elements, 128 to 512 bytes) is read once and
+// Per-head RMSNorm followed by rotate-half RoPE as ONE pass over the q and k tensors of heads,
+// each [B,T,H,D] (the q_norm / k_norm + apply_rotary_pos_emb sequence of Qwen3 attention),
+// forward and backward, one launch for both tensors.  Bandwidth-bound: each head row (D elements, 128 to 512 bytes) is read once and
 // written once; unfused, the same row makes three round trips (norm, then RoPE in place).
 //
 // Layout: a group of LPR lanes owns one head row; a lane holds one 16-byte slice of the first
@@ -40,6 +40,13 @@ struct HeadArgs {
   float eps;
 };
 
+// One launch serves two tensors of heads (q and k): CTAs [0, split) work on p[0], the rest
+// on p[1], each side with its own weight, rstd, dw and scratch.
+struct HeadPair {
+  HeadArgs p[2];
+  unsigned split;
+};
+
 template <typename T>
 __device__ __forceinline__ float round_to(float v) {
   return Cvt<T>::to_f(Cvt<T>::from_f(v));
@@ -75,9 +82,14 @@ __device__ __forceinline__ Item locate(const HeadArgs& a, uint32_t item, uint32_
 // width (a chain per 16-byte slice, first-half slice + matching second-half slice, then a
 // butterfly over the slices), which keeps rstd and the backward's dot product bit-identical.
 template <typename T, int LPR, int HPI, int MINB>
-__global__ void __launch_bounds__(kThreads, MINB) headnorm_rope_fwd(const HeadArgs a) {
+__global__ void __launch_bounds__(kThreads, MINB)
+headnorm_rope_fwd(const __grid_constant__ HeadPair pp) {
   constexpr int E = Cvt<T>::N;
   constexpr int kGroups = kThreads / LPR;
+  const bool side = blockIdx.x >= pp.split;
+  const HeadArgs& a = pp.p[side ? 1 : 0];
+  const unsigned bid = side ? blockIdx.x - pp.split : blockIdx.x;
+  const unsigned nblk = side ? gridDim.x - pp.split : pp.split;
   const int lane = threadIdx.x % LPR;
   const int group = threadIdx.x / LPR;
   const int half = a.D / 2;
@@ -90,7 +102,7 @@ __global__ void __launch_bounds__(kThreads, MINB) headnorm_rope_fwd(const HeadAr
   Cvt<T>::unpack(ld_global_v4(static_cast<const T*>(a.w) + lane * E), w1);
   Cvt<T>::unpack(ld_global_v4(static_cast<const T*>(a.w) + half + lane * E), w2);
 
-  for (uint32_t base = blockIdx.x * kGroups; base < items; base += gridDim.x * kGroups) {
+  for (uint32_t base = bid * kGroups; base < items; base += nblk * kGroups) {
     const Item it = locate<HPI>(a, base + group, items, hblocks);
     uint4 x1[HPI], x2[HPI];
     uint4 cv = make_uint4(0, 0, 0, 0), sv = make_uint4(0, 0, 0, 0);
@@ -141,9 +153,14 @@ __global__ void __launch_bounds__(kThreads, MINB) headnorm_rope_fwd(const HeadAr
 // dx, dw of the fused pair.  ws: dw_copies(D) x D fp32 column sums + arrival counter, zero
 // on entry, left zero on exit (the contract of the RMSNorm backward).
 template <typename T, int LPR, int HPI, int MINB>
-__global__ void __launch_bounds__(kThreads, MINB) headnorm_rope_bwd(const HeadArgs a) {
+__global__ void __launch_bounds__(kThreads, MINB)
+headnorm_rope_bwd(const __grid_constant__ HeadPair pp) {
   constexpr int E = Cvt<T>::N;
   constexpr int kGroups = kThreads / LPR;
+  const bool side = blockIdx.x >= pp.split;
+  const HeadArgs& a = pp.p[side ? 1 : 0];
+  const unsigned bid = side ? blockIdx.x - pp.split : blockIdx.x;
+  const unsigned nblk = side ? gridDim.x - pp.split : pp.split;
   __shared__ float s_dw[2 * LPR * E];
   const int lane = threadIdx.x % LPR;
   const int group = threadIdx.x / LPR;
@@ -162,7 +179,7 @@ __global__ void __launch_bounds__(kThreads, MINB) headnorm_rope_bwd(const HeadAr
 #pragma unroll
   for (int e = 0; e < E; ++e) acc1[e] = acc2[e] = 0.f;
 
-  for (uint32_t base = blockIdx.x * kGroups; base < items; base += gridDim.x * kGroups) {
+  for (uint32_t base = bid * kGroups; base < items; base += nblk * kGroups) {
     const Item it = locate<HPI>(a, base + group, items, hblocks);
     uint4 x1[HPI], x2[HPI], g1[HPI], g2[HPI];
     float rs[HPI];
@@ -239,13 +256,13 @@ __global__ void __launch_bounds__(kThreads, MINB) headnorm_rope_bwd(const HeadAr
     }
   }
   __syncthreads();
-  float* my_ws = a.ws + static_cast<int64_t>(blockIdx.x % dw_copies(N)) * N;
+  float* my_ws = a.ws + static_cast<int64_t>(bid % dw_copies(N)) * N;
   for (int c = threadIdx.x; c < N; c += kThreads) {
     const int hsel = c >= half ? 1 : 0;
     const int cc = c - hsel * half;  // column inside its half: slice cc / E, element cc % E
     atomicAdd(my_ws + c, s_dw[(2 * (cc % E) + hsel) * LPR + cc / E]);
   }
-  dw_finalize<T>(a.ws, static_cast<T*>(a.dw), N, gridDim.x, threadIdx.x, kThreads);
+  dw_finalize<T>(a.ws, static_cast<T*>(a.dw), N, nblk, threadIdx.x, kThreads);
 }
 
 bool mult_of(const int64_t* s, int n, int e) {
@@ -255,35 +272,59 @@ bool mult_of(const int64_t* s, int n, int e) {
 }
 
 template <typename T, bool BWD>
-int launch_t(const HeadArgs& a, cudaStream_t s) {
+bool side_ok(const HeadArgs& a) {
   constexpr int E = Cvt<T>::N;
-  const int lpr = a.D / (2 * E);  // lanes per head row: each holds one slice of either half
-  bool ok = a.D % (2 * E) == 0 && (lpr == 4 || lpr == 8 || lpr == 16) && aligned16(a.x) &&
-            aligned16(a.w) && aligned16(a.cos) && aligned16(a.sin) && aligned16(a.out) &&
-            mult_of(a.xs, 3, E) && mult_of(a.os, 3, E) && mult_of(a.cs, 2, E);
+  bool ok = aligned16(a.x) && aligned16(a.w) && aligned16(a.cos) && aligned16(a.sin) &&
+            aligned16(a.out) && mult_of(a.xs, 3, E) && mult_of(a.os, 3, E) && mult_of(a.cs, 2, E);
   if (BWD) ok = ok && aligned16(a.dout) && mult_of(a.gs, 3, E);
-  if (!ok) {
-    set_error("headnorm_rope: head_dim %d with this element size / alignment is not supported "
+  return ok;
+}
+
+template <typename T, bool BWD>
+int launch_t(const HeadPair& pp, cudaStream_t s) {
+  constexpr int E = Cvt<T>::N;
+  const int D = pp.p[0].D;
+  const int lpr = D / (2 * E);  // lanes per head row: each holds one slice of either half
+  if (D % (2 * E) != 0 || !(lpr == 4 || lpr == 8 || lpr == 16) || !side_ok<T, BWD>(pp.p[0]) ||
+      !side_ok<T, BWD>(pp.p[1])) {
+    set_error("qk_norm_rope: head_dim %d with this element size / alignment is not supported "
               "(head rows of 128, 256 or 512 bytes, 16-byte aligned strides); run the norm and "
               "the rotation as separate calls",
-              a.D);
+              D);
     return BT_ERR_ARG;
   }
   constexpr int kHpi = BWD ? 2 : 4;  // heads per work item: 16-byte loads in flight per lane = 2 (4) * kHpi
-  const int64_t items = a.B * a.T * ceil_div(a.H, kHpi);
-  if (items >= (1ll << 31) || a.B * a.T * a.H >= (1ll << 31)) {
-    set_error("headnorm_rope: %lld head rows exceed the 32-bit work index", (long long)(a.B * a.T * a.H));
-    return BT_ERR_ARG;
+  int64_t blocks[2];
+  for (int i = 0; i < 2; ++i) {
+    const HeadArgs& a = pp.p[i];
+    const int64_t items = a.B * a.T * ceil_div(a.H, kHpi);
+    if (items >= (1ll << 31) || a.B * a.T * a.H >= (1ll << 31)) {
+      set_error("qk_norm_rope: %lld head rows exceed the 32-bit work index",
+                (long long)(a.B * a.T * a.H));
+      return BT_ERR_ARG;
+    }
+    blocks[i] = ceil_div(items, kThreads / lpr);
   }
-  const int64_t blocks = ceil_div(items, kThreads / lpr);
+  // The CTA budget is shared out in proportion to the work of the two sides.
   const int64_t cap = static_cast<int64_t>(sm_count()) * (BWD ? 2 : 8);
-  const unsigned grid = static_cast<unsigned>(blocks < cap ? blocks : cap);
+  int64_t g0 = blocks[0], g1 = blocks[1];
+  if (g0 + g1 > cap) {
+    g0 = cap * blocks[0] / (blocks[0] + blocks[1]);
+    if (g0 < 1) g0 = 1;
+    if (g0 > cap - 1) g0 = cap - 1;
+    g1 = cap - g0;
+    if (g0 > blocks[0]) g0 = blocks[0];
+    if (g1 > blocks[1]) g1 = blocks[1];
+  }
+  HeadPair q = pp;
+  q.split = static_cast<unsigned>(g0);
+  const unsigned grid = static_cast<unsigned>(g0 + g1);
 #define BT_HEAD(L)                                                         \
   if (lpr == L) {                                                          \
-    if (BWD)                                                               \
-      headnorm_rope_bwd<T, L, kHpi, 2><<<grid, kThreads, 0, s>>>(a);       \
+    if constexpr (BWD)                                                     \
+      headnorm_rope_bwd<T, L, kHpi, 2><<<grid, kThreads, 0, s>>>(q);       \
     else                                                                   \
-      headnorm_rope_fwd<T, L, kHpi, 3><<<grid, kThreads, 0, s>>>(a);       \
+      headnorm_rope_fwd<T, L, kHpi, 3><<<grid, kThreads, 0, s>>>(q);       \
   }
   BT_HEAD(4)
   BT_HEAD(8)
@@ -294,85 +335,119 @@ int launch_t(const HeadArgs& a, cudaStream_t s) {
 }
 
 template <bool BWD>
-int launch_any(int dtype, const HeadArgs& a, cudaStream_t s) {
+int launch_any(int dtype, const HeadPair& pp, cudaStream_t s) {
   switch (dtype) {
-    case BT_BF16: return launch_t<__nv_bfloat16, BWD>(a, s);
-    case BT_FP16: return launch_t<__half, BWD>(a, s);
-    case BT_FP32: return launch_t<float, BWD>(a, s);
+    case BT_BF16: return launch_t<__nv_bfloat16, BWD>(pp, s);
+    case BT_FP16: return launch_t<__half, BWD>(pp, s);
+    case BT_FP32: return launch_t<float, BWD>(pp, s);
   }
-  set_error("headnorm_rope: unknown dtype %d", dtype);
+  set_error("qk_norm_rope: unknown dtype %d", dtype);
   return BT_ERR_ARG;
 }
 
-int fill_common(HeadArgs* a, const char* what, int64_t B, int64_t T, int64_t H, int64_t D,
-                const int64_t cos_strides[2], int64_t cos_bs) {
-  BT_CHECK_ARG(B >= 0 && T >= 0 && H >= 0, "%s: negative size", what);
+int check_common(const char* what, int64_t B, int64_t T, int64_t Hq, int64_t Hk, int64_t D,
+                 int64_t cos_bs) {
+  BT_CHECK_ARG(B >= 0 && T >= 0 && Hq >= 0 && Hk >= 0, "%s: negative size", what);
   BT_CHECK_ARG(D > 0 && D % 2 == 0 && D <= 4096, "%s: head_dim %lld must be even and <= 4096", what,
                (long long)D);
   BT_CHECK_ARG(cos_bs == 1 || cos_bs == B, "%s: cos batch %lld is neither 1 nor B=%lld", what,
                (long long)cos_bs, (long long)B);
+  return BT_OK;
+}
+
+void fill_side(HeadArgs* a, int64_t B, int64_t T, int64_t H, int64_t D, const void* cos,
+               const void* sin, const int64_t cos_strides[2], int64_t cos_bs) {
   a->B = B;
   a->T = T;
   a->H = H;
   a->D = static_cast<int>(D);
+  a->cos = cos;
+  a->sin = sin;
   a->cs[0] = cos_strides[0];
   a->cs[1] = cos_strides[1];
   a->cos_bs = static_cast<int>(cos_bs);
-  return BT_OK;
 }
 
 }  // namespace
 }  // namespace bt
 
-extern "C" int bt_headnorm_rope_fwd(const void* x, const void* w, const void* cos, const void* sin,
-                                    void* out, float* rstd, int64_t B, int64_t T, int64_t H,
-                                    int64_t D, const int64_t x_strides[3],
-                                    const int64_t out_strides[3], const int64_t cos_strides[2],
-                                    int64_t cos_bs, float eps, int dtype, void* stream) {
+extern "C" int bt_qk_norm_rope_fwd(const void* q, const void* k, const void* wq, const void* wk,
+                                   const void* cos, const void* sin, void* q_out, void* k_out,
+                                   float* rstd_q, float* rstd_k, int64_t B, int64_t T, int64_t Hq,
+                                   int64_t Hk, int64_t D, const int64_t q_strides[3],
+                                   const int64_t k_strides[3], const int64_t q_out_strides[3],
+                                   const int64_t k_out_strides[3], const int64_t cos_strides[2],
+                                   int64_t cos_bs, float eps_q, float eps_k, int dtype,
+                                   void* stream) {
   using namespace bt;
-  HeadArgs a{};
-  if (int rc = fill_common(&a, "headnorm_rope_fwd", B, T, H, D, cos_strides, cos_bs)) return rc;
-  if (B == 0 || T == 0 || H == 0) return BT_OK;
-  BT_CHECK_ARG(x && w && cos && sin && out && rstd, "headnorm_rope_fwd: null pointer");
-  a.x = x;
-  a.w = w;
-  a.cos = cos;
-  a.sin = sin;
-  a.out = out;
-  a.rstd_out = rstd;
-  a.eps = eps;
+  if (int rc = check_common("qk_norm_rope_fwd", B, T, Hq, Hk, D, cos_bs)) return rc;
+  if (B == 0 || T == 0) return BT_OK;
+  BT_CHECK_ARG(Hq > 0 && Hk > 0, "qk_norm_rope_fwd: both q and k need at least one head");
+  BT_CHECK_ARG(q && k && wq && wk && cos && sin && q_out && k_out && rstd_q && rstd_k,
+               "qk_norm_rope_fwd: null pointer");
+  HeadPair pp{};
+  fill_side(&pp.p[0], B, T, Hq, D, cos, sin, cos_strides, cos_bs);
+  fill_side(&pp.p[1], B, T, Hk, D, cos, sin, cos_strides, cos_bs);
+  pp.p[0].x = q;
+  pp.p[0].w = wq;
+  pp.p[0].out = q_out;
+  pp.p[0].rstd_out = rstd_q;
+  pp.p[0].eps = eps_q;
+  pp.p[1].x = k;
+  pp.p[1].w = wk;
+  pp.p[1].out = k_out;
+  pp.p[1].rstd_out = rstd_k;
+  pp.p[1].eps = eps_k;
   for (int i = 0; i < 3; ++i) {
-    a.xs[i] = x_strides[i];
-    a.os[i] = out_strides[i];
+    pp.p[0].xs[i] = q_strides[i];
+    pp.p[0].os[i] = q_out_strides[i];
+    pp.p[1].xs[i] = k_strides[i];
+    pp.p[1].os[i] = k_out_strides[i];
   }
-  return launch_any<false>(dtype, a, static_cast<cudaStream_t>(stream));
+  return launch_any<false>(dtype, pp, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int bt_headnorm_rope_bwd(const void* dout, const void* x, const void* w,
-                                    const float* rstd, const void* cos, const void* sin, void* dx,
-                                    void* dw, void* ws, int64_t B, int64_t T, int64_t H, int64_t D,
-                                    const int64_t dout_strides[3], const int64_t x_strides[3],
-                                    const int64_t dx_strides[3], const int64_t cos_strides[2],
-                                    int64_t cos_bs, int dtype, void* stream) {
+extern "C" int bt_qk_norm_rope_bwd(const void* dq_out, const void* dk_out, const void* q,
+                                   const void* k, const void* wq, const void* wk,
+                                   const float* rstd_q, const float* rstd_k, const void* cos,
+                                   const void* sin, void* dq, void* dk, void* dwq, void* dwk,
+                                   void* ws_q, void* ws_k, int64_t B, int64_t T, int64_t Hq,
+                                   int64_t Hk, int64_t D, const int64_t dq_out_strides[3],
+                                   const int64_t dk_out_strides[3], const int64_t q_strides[3],
+                                   const int64_t k_strides[3], const int64_t dq_strides[3],
+                                   const int64_t dk_strides[3], const int64_t cos_strides[2],
+                                   int64_t cos_bs, int dtype, void* stream) {
   using namespace bt;
-  HeadArgs a{};
-  if (int rc = fill_common(&a, "headnorm_rope_bwd", B, T, H, D, cos_strides, cos_bs)) return rc;
-  BT_CHECK_ARG(B > 0 && T > 0 && H > 0, "headnorm_rope_bwd: empty input");
-  BT_CHECK_ARG(dout && x && w && rstd && cos && sin && dx && dw && ws,
-               "headnorm_rope_bwd: null pointer");
-  a.dout = dout;
-  a.x = x;
-  a.w = w;
-  a.rstd_in = rstd;
-  a.cos = cos;
-  a.sin = sin;
-  a.out = dx;
-  a.dw = dw;
-  a.ws = static_cast<float*>(ws);
+  if (int rc = check_common("qk_norm_rope_bwd", B, T, Hq, Hk, D, cos_bs)) return rc;
+  BT_CHECK_ARG(B > 0 && T > 0 && Hq > 0 && Hk > 0, "qk_norm_rope_bwd: empty input");
+  BT_CHECK_ARG(dq_out && dk_out && q && k && wq && wk && rstd_q && rstd_k && cos && sin && dq &&
+                   dk && dwq && dwk && ws_q && ws_k,
+               "qk_norm_rope_bwd: null pointer");
+  BT_CHECK_ARG(ws_q != ws_k, "qk_norm_rope_bwd: q and k need separate scratch buffers");
+  HeadPair pp{};
+  fill_side(&pp.p[0], B, T, Hq, D, cos, sin, cos_strides, cos_bs);
+  fill_side(&pp.p[1], B, T, Hk, D, cos, sin, cos_strides, cos_bs);
+  pp.p[0].dout = dq_out;
+  pp.p[0].x = q;
+  pp.p[0].w = wq;
+  pp.p[0].rstd_in = rstd_q;
+  pp.p[0].out = dq;
+  pp.p[0].dw = dwq;
+  pp.p[0].ws = static_cast<float*>(ws_q);
+  pp.p[1].dout = dk_out;
+  pp.p[1].x = k;
+  pp.p[1].w = wk;
+  pp.p[1].rstd_in = rstd_k;
+  pp.p[1].out = dk;
+  pp.p[1].dw = dwk;
+  pp.p[1].ws = static_cast<float*>(ws_k);
   for (int i = 0; i < 3; ++i) {
-    a.gs[i] = dout_strides[i];
-    a.xs[i] = x_strides[i];
-    a.os[i] = dx_strides[i];
+    pp.p[0].gs[i] = dq_out_strides[i];
+    pp.p[0].xs[i] = q_strides[i];
+    pp.p[0].os[i] = dq_strides[i];
+    pp.p[1].gs[i] = dk_out_strides[i];
+    pp.p[1].xs[i] = k_strides[i];
+    pp.p[1].os[i] = dk_strides[i];
   }
-  return launch_any<true>(dtype, a, static_cast<cudaStream_t>(stream));
+  return launch_any<true>(dtype, pp, static_cast<cudaStream_t>(stream));
 }

@@ -11,7 +11,7 @@ trips through HBM.  This module replaces those two ``forward`` methods so that
   (``bt_add_rmsnorm_fwd``), ``residual + mlp_output`` inside the down projection's epilogue
   (``bt_mlp_fwd`` with a residual), and both gradient merges inside the RMSNorm backward
   (``bt_add_rmsnorm_bwd``) - no stand-alone elementwise add is left in a layer;
-* q_norm + RoPE and k_norm + RoPE are one kernel each (``bt_headnorm_rope_fwd/_bwd``).
+* q_norm + RoPE and k_norm + RoPE are one kernel for both tensors (``bt_qk_norm_rope_fwd/_bwd``).
 
 Parameters, module names and results are those of the unfused patched model: the fused kernels
 round where the separate ones round (bit-identical for the norm + RoPE pair; the residual folded
@@ -140,74 +140,99 @@ def _cos_sin(cos, sin, dtype):
     return cos, sin
 
 
-class HeadNormRoPEFunction(torch.autograd.Function):
-    """Per-head RMSNorm then RoPE of ``x`` [B, T, H, D] (one of the q / k projections viewed per
-    head); returns [B, T, H, D] (the caller transposes to [B, H, T, D] as HF attention does)."""
+class QKNormRoPEFunction(torch.autograd.Function):
+    """Per-head RMSNorm then RoPE of ``q`` [B, T, Hq, D] and ``k`` [B, T, Hk, D] (the q / k
+    projections viewed per head), one kernel launch for both; returns tensors of the same
+    shapes (the caller transposes to [B, H, T, D] as HF attention does)."""
 
     @staticmethod
-    def forward(ctx, x, weight, cos, sin, eps):
-        dev = _lib.require_cuda(x, weight, cos, sin)
+    def forward(ctx, q, k, wq, wk, cos, sin, eps_q, eps_k):
+        dev = _lib.require_cuda(q, k, wq, wk, cos, sin)
         lib = _lib.get_lib()
-        if x.dim() != 4:
-            raise ValueError("head_norm_rope: x must be [batch, seq, heads, head_dim]")
-        b, t, h, d = x.shape
-        if weight.numel() != d:
-            raise ValueError(f"head_norm_rope: weight has {weight.numel()} elements, head_dim is {d}")
+        if q.dim() != 4 or k.dim() != 4:
+            raise ValueError("qk_norm_rope: q and k must be [batch, seq, heads, head_dim]")
+        b, t, hq, d = q.shape
+        hk = k.shape[2]
+        if k.shape[0] != b or k.shape[1] != t or k.shape[3] != d or k.dtype != q.dtype:
+            raise ValueError(f"qk_norm_rope: q {tuple(q.shape)} and k {tuple(k.shape)} disagree")
+        if wq.numel() != d or wk.numel() != d:
+            raise ValueError(f"qk_norm_rope: norm weights must have head_dim = {d} elements")
         if cos.dim() != 3 or cos.shape[1] != t or cos.shape[-1] not in (d, d // 2) or cos.shape[0] not in (1, b):
-            raise ValueError(f"head_norm_rope: cos of shape {tuple(cos.shape)} does not fit x {tuple(x.shape)}")
-        if x.stride(-1) != 1:
-            x = x.contiguous()
-        w = weight.detach()
-        if w.dtype != x.dtype:
-            w = w.to(x.dtype)
-        w = w.contiguous()
-        cos, sin = _cos_sin(cos, sin, x.dtype)
-        out = torch.empty((b, t, h, d), dtype=x.dtype, device=dev)
-        rstd = torch.empty((b * t * h,), dtype=torch.float32, device=dev)
-        code = _lib.dtype_code(x.dtype)
-        with _lib.device_of(dev), _lib.timed("rope_fwd", 1, dev):
-            rc = lib.bt_headnorm_rope_fwd(x.data_ptr(), w.data_ptr(), cos.data_ptr(), sin.data_ptr(), out.data_ptr(),
-                                          rstd.data_ptr(), b, t, h, d, _lib.I64x3(*x.stride()[:3]),
-                                          _lib.I64x3(*out.stride()[:3]), _lib.I64x2(cos.stride(0), cos.stride(1)),
-                                          cos.shape[0], float(eps), code, _lib.stream_ptr(dev))
-        _lib.check(rc, "bt_headnorm_rope_fwd")
-        ctx.save_for_backward(x, w, rstd, cos, sin)
-        ctx.weight_dtype = weight.dtype
-        ctx.x_layout = (tuple(x.shape), tuple(x.stride()))
-        return out
+            raise ValueError(f"qk_norm_rope: cos of shape {tuple(cos.shape)} does not fit q {tuple(q.shape)}")
+        if q.stride(-1) != 1:
+            q = q.contiguous()
+        if k.stride(-1) != 1:
+            k = k.contiguous()
+        ws = [_weight(w, q.dtype) for w in (wq, wk)]
+        cos, sin = _cos_sin(cos, sin, q.dtype)
+        q_out = torch.empty((b, t, hq, d), dtype=q.dtype, device=dev)
+        k_out = torch.empty((b, t, hk, d), dtype=q.dtype, device=dev)
+        rstd_q = torch.empty((b * t * hq,), dtype=torch.float32, device=dev)
+        rstd_k = torch.empty((b * t * hk,), dtype=torch.float32, device=dev)
+        if q.numel() > 0 and k.numel() > 0:
+            with _lib.device_of(dev), _lib.timed("rope_fwd", 1, dev):
+                rc = lib.bt_qk_norm_rope_fwd(q.data_ptr(), k.data_ptr(), ws[0].data_ptr(), ws[1].data_ptr(),
+                                             cos.data_ptr(), sin.data_ptr(), q_out.data_ptr(), k_out.data_ptr(),
+                                             rstd_q.data_ptr(), rstd_k.data_ptr(), b, t, hq, hk, d,
+                                             _lib.I64x3(*q.stride()[:3]), _lib.I64x3(*k.stride()[:3]),
+                                             _lib.I64x3(*q_out.stride()[:3]), _lib.I64x3(*k_out.stride()[:3]),
+                                             _lib.I64x2(cos.stride(0), cos.stride(1)), cos.shape[0], float(eps_q),
+                                             float(eps_k), _lib.dtype_code(q.dtype), _lib.stream_ptr(dev))
+            _lib.check(rc, "bt_qk_norm_rope_fwd")
+        ctx.save_for_backward(q, k, ws[0], ws[1], rstd_q, rstd_k, cos, sin)
+        ctx.w_dtypes = (wq.dtype, wk.dtype)
+        ctx.layouts = ((tuple(q.shape), tuple(q.stride())), (tuple(k.shape), tuple(k.stride())))
+        return q_out, k_out
 
     @staticmethod
-    def backward(ctx, dout):
-        x, w, rstd, cos, sin = ctx.saved_tensors
-        dev = x.device
+    def backward(ctx, dq_out, dk_out):
+        q, k, wq, wk, rstd_q, rstd_k, cos, sin = ctx.saved_tensors
+        dev = q.device
         lib = _lib.get_lib()
-        b, t, h, d = x.shape
-        if dout.dtype != x.dtype:
-            dout = dout.to(x.dtype)
-        if dout.stride(-1) != 1:
-            dout = dout.contiguous()
-        # dx takes the memory layout of x so that the projection's backward can flatten it for free
-        if _dense(ctx.x_layout):
-            dx = torch.empty_strided(ctx.x_layout[0], ctx.x_layout[1], dtype=x.dtype, device=dev)
+        b, t, hq, d = q.shape
+        hk = k.shape[2]
+
+        def grad_in(g, like):
+            if g is None:
+                return torch.zeros_like(like, memory_format=torch.contiguous_format)
+            if g.dtype != like.dtype:
+                g = g.to(like.dtype)
+            return g if g.stride(-1) == 1 else g.contiguous()
+
+        def grad_out(layout, like):
+            # in the memory layout of the input, so that the projection's backward can flatten it for free
+            if _dense(layout):
+                return torch.empty_strided(layout[0], layout[1], dtype=like.dtype, device=dev)
+            return torch.empty(like.shape, dtype=like.dtype, device=dev)
+
+        dq_out, dk_out = grad_in(dq_out, q), grad_in(dk_out, k)
+        dq, dk = grad_out(ctx.layouts[0], q), grad_out(ctx.layouts[1], k)
+        dwq = torch.empty((d,), dtype=q.dtype, device=dev)
+        dwk = torch.empty((d,), dtype=q.dtype, device=dev)
+        nbytes = (int(lib.bt_rmsnorm_bwd_ws_bytes(d)) + 255) // 256 * 256
+        ws = _lib.zero_workspace(dev, 2 * nbytes)
+        if q.numel() > 0 and k.numel() > 0:
+            with _lib.device_of(dev), _lib.timed("rope_bwd", 1, dev):
+                rc = lib.bt_qk_norm_rope_bwd(dq_out.data_ptr(), dk_out.data_ptr(), q.data_ptr(), k.data_ptr(),
+                                             wq.data_ptr(), wk.data_ptr(), rstd_q.data_ptr(), rstd_k.data_ptr(),
+                                             cos.data_ptr(), sin.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                                             dwq.data_ptr(), dwk.data_ptr(), ws.data_ptr(), ws.data_ptr() + nbytes,
+                                             b, t, hq, hk, d, _lib.I64x3(*dq_out.stride()[:3]),
+                                             _lib.I64x3(*dk_out.stride()[:3]), _lib.I64x3(*q.stride()[:3]),
+                                             _lib.I64x3(*k.stride()[:3]), _lib.I64x3(*dq.stride()[:3]),
+                                             _lib.I64x3(*dk.stride()[:3]), _lib.I64x2(cos.stride(0), cos.stride(1)),
+                                             cos.shape[0], _lib.dtype_code(q.dtype), _lib.stream_ptr(dev))
+            _lib.check(rc, "bt_qk_norm_rope_bwd")
         else:
-            dx = torch.empty((b, t, h, d), dtype=x.dtype, device=dev)
-        dw = torch.empty((d,), dtype=x.dtype, device=dev)
-        ws = _lib.zero_workspace(dev, int(lib.bt_rmsnorm_bwd_ws_bytes(d)))
-        with _lib.device_of(dev), _lib.timed("rope_bwd", 1, dev):
-            rc = lib.bt_headnorm_rope_bwd(dout.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), cos.data_ptr(),
-                                          sin.data_ptr(), dx.data_ptr(), dw.data_ptr(), ws.data_ptr(), b, t, h, d,
-                                          _lib.I64x3(*dout.stride()[:3]), _lib.I64x3(*x.stride()[:3]),
-                                          _lib.I64x3(*dx.stride()[:3]), _lib.I64x2(cos.stride(0), cos.stride(1)),
-                                          cos.shape[0], _lib.dtype_code(x.dtype), _lib.stream_ptr(dev))
-        _lib.check(rc, "bt_headnorm_rope_bwd")
-        if dw.dtype != ctx.weight_dtype:
-            dw = dw.to(ctx.weight_dtype)
-        return dx, dw, None, None, None
+            dwq.zero_()
+            dwk.zero_()
+        return dq, dk, dwq.to(ctx.w_dtypes[0]), dwk.to(ctx.w_dtypes[1]), None, None, None, None
 
 
-def head_norm_rope(x, weight, cos, sin, eps=1e-6):
-    """RoPE(rms_norm(x) * weight) for x [B, T, H, D] with cos/sin [1 or B, T, D]."""
-    return HeadNormRoPEFunction.apply(x, weight, cos, sin, eps)
+def qk_norm_rope(q, k, wq, wk, cos, sin, eps_q=1e-6, eps_k=1e-6):
+    """(RoPE(rms_norm(q) * wq), RoPE(rms_norm(k) * wk)) for q [B, T, Hq, D], k [B, T, Hk, D] and
+    cos/sin [1 or B, T, D]."""
+    return QKNormRoPEFunction.apply(q, k, wq, wk, cos, sin, eps_q, eps_k)
 
 
 # ------------------------------------------------------------------ projections on the tcgen05 GEMM
@@ -370,7 +395,7 @@ def decoder_layer_forward(self, hidden_states, attention_mask=None, position_ids
 
 def attention_forward(self, hidden_states, position_embeddings, attention_mask, past_key_values=None, **kwargs):
     """``Qwen3Attention.forward`` (modeling_qwen3.py:243-288) with q_norm + RoPE and
-    k_norm + RoPE as one kernel each; everything from the cache update on is unchanged."""
+    k_norm + RoPE as one kernel; everything from the cache update on is unchanged."""
     from transformers.models.qwen3 import modeling_qwen3 as hf
 
     lead = hidden_states.shape[:-1]
@@ -390,8 +415,9 @@ def attention_forward(self, hidden_states, position_embeddings, attention_mask, 
                and isinstance(self.k_norm, B200RMSNorm) and _head_rows_supported(self.head_dim, q_lin.dtype)
                and cos.dim() == 3)
     if fusable:
-        query = head_norm_rope(q_lin, self.q_norm.weight, cos, sin, self.q_norm.variance_epsilon).transpose(1, 2)
-        key = head_norm_rope(k_lin, self.k_norm.weight, cos, sin, self.k_norm.variance_epsilon).transpose(1, 2)
+        query, key = qk_norm_rope(q_lin, k_lin, self.q_norm.weight, self.k_norm.weight, cos, sin,
+                                  self.q_norm.variance_epsilon, self.k_norm.variance_epsilon)
+        query, key = query.transpose(1, 2), key.transpose(1, 2)
     else:
         query, key = hf.apply_rotary_pos_emb(self.q_norm(q_lin).transpose(1, 2), self.k_norm(k_lin).transpose(1, 2),
                                              cos, sin)

@@ -222,7 +222,10 @@ def run_reference_arm(args):
 # ------------------------------------------------------------------ per-op microbench
 def _kernel_ms(fn, flush, iters, warm):
     """Median over `iters` calls of the device time spent inside the library calls that `fn`
-    makes (CUDA events recorded around each call on its stream), L2 flushed before every call."""
+    makes (CUDA events recorded around each call on its stream), L2 flushed before every call.
+    The flush READS a 256 MiB buffer: it evicts what the previous call left without filling the
+    L2 with dirty lines, whose write-back (up to 126 MB, about 20 us) a write-flush would charge
+    to the first timed kernel."""
     import torch
 
     from bastile_b200 import _lib
@@ -231,7 +234,7 @@ def _kernel_ms(fn, flush, iters, warm):
         fn()
     per_iter = []
     for _ in range(iters):
-        flush.zero_()  # 256 MiB > 126 MB L2
+        flush.sum()  # streams 256 MiB (> 126 MB L2) through the cache, leaving clean lines
         torch.cuda._sleep(600_000)  # keep the GPU busy while the host queues the op, so that the
         # events bracket kernels that are already waiting in the stream (no host gaps inside)
         _lib.instr.reset(enabled=True)
@@ -265,7 +268,7 @@ def per_op_bench(peaks, only=None, iters=None):
 
     dev = "cuda"
     torch.manual_seed(1)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flush = torch.zeros(64 << 20, dtype=torch.int32, device=dev)  # 256 MiB
     out = {}
     bf = torch.bfloat16
     want = lambda name: only is None or only == name  # noqa: E731
@@ -283,6 +286,48 @@ def per_op_bench(peaks, only=None, iters=None):
             byts = 5 * m * n * 2 + 8 * m + 6 * n
             out[f"rmsnorm_{m}x{n}_fwd_bwd"] = _hbm(_kernel_ms(rms, flush, iters or 20, 5), byts, peaks)
             del x, w, dy
+
+    if want("rmsnorm"):
+        from bastile_b200.ops.fused_layers import add_rms_norm
+
+        m, n = 8192, 4096
+        x = torch.randn(m, n, device=dev, dtype=bf).requires_grad_(True)
+        r = torch.randn(m, n, device=dev, dtype=bf)
+        w = (1 + 0.02 * torch.randn(n, device=dev)).to(bf).requires_grad_(True)
+        dy, ds = torch.randn(m, n, device=dev, dtype=bf), torch.randn(m, n, device=dev, dtype=bf)
+
+        def add_rms():
+            x.grad = w.grad = None
+            y, stream = add_rms_norm(x, r, w, 1e-6)
+            torch.autograd.backward([y, stream], [dy, ds])
+
+        # fwd: x, residual in; sum, y out.  bwd: dy, sum, d(stream) in; dx out.
+        byts = 8 * m * n * 2 + 8 * m + 6 * n
+        out[f"add_rmsnorm_{m}x{n}_fwd_bwd"] = _hbm(_kernel_ms(add_rms, flush, iters or 20, 5), byts, peaks)
+        del x, r, w, dy, ds
+
+    if want("rope"):
+        from bastile_b200.ops.fused_layers import qk_norm_rope as fused_qk
+
+        inv = 1.0 / (1e6 ** (torch.arange(0, 128, 2, dtype=torch.float32) / 128))
+        emb = torch.outer(torch.arange(8192, dtype=torch.float32), inv)
+        emb = torch.cat((emb, emb), -1)
+        cos, sin = emb.cos()[None].to(dev, bf), emb.sin()[None].to(dev, bf)
+        xq = torch.randn(1, 8192, 32, 128, device=dev, dtype=bf).requires_grad_(True)
+        xk = torch.randn(1, 8192, 8, 128, device=dev, dtype=bf).requires_grad_(True)
+        wq = torch.ones(128, device=dev, dtype=bf, requires_grad=True)
+        wk = torch.ones(128, device=dev, dtype=bf, requires_grad=True)
+        dq, dk = torch.randn_like(xq), torch.randn_like(xk)
+
+        def qk_norm_rope():
+            xq.grad = xk.grad = wq.grad = wk.grad = None
+            qo, ko = fused_qk(xq, xk, wq, wk, cos, sin)
+            torch.autograd.backward([qo, ko], [dq, dk])
+
+        # fwd: heads in, heads out; bwd: d(out), heads in, d(heads) out; plus the cos/sin half rows
+        byts = 5 * (xq.numel() + xk.numel()) * 2 + 2 * 2 * 8192 * 64 * 2
+        out["qk_norm_rope_q32_k8_8192x128_fwd_bwd"] = _hbm(_kernel_ms(qk_norm_rope, flush, iters or 20, 5), byts, peaks)
+        del xq, xk, dq, dk
 
     if want("rope"):
         q = torch.randn(1, 32, 8192, 128, device=dev, dtype=bf).requires_grad_(True)
@@ -339,7 +384,7 @@ def per_op_bench(peaks, only=None, iters=None):
                 lce()
             ts = []
             for _ in range(iters or 5):
-                flush.zero_()
+                flush.sum()
                 dist.barrier()
                 torch.cuda.synchronize()
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

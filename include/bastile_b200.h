@@ -208,35 +208,41 @@ int bt_set_gemm_cta_pairs(int enable);
 
 /* ------------------------------------------- per-head RMSNorm + RoPE, fused */
 
-/* q_norm / k_norm followed by the rotary embedding, for ONE tensor of heads
- * x [B,T,H,D] (the q or k projection output viewed per head; element strides of
- * batch, position, head in x_strides; D contiguous):
+/* q_norm / k_norm followed by the rotary embedding, for the two tensors of
+ * heads q [B,T,Hq,D] and k [B,T,Hk,D] (the projection outputs viewed per head;
+ * element strides of batch, position, head; D contiguous), in one launch:
  *   y   = T(x * rstd * w)            per head row, rstd[b,t,h] = rsqrt(mean(x^2)+eps)
  *   out = rotate-half RoPE of y with cos/sin[b or 0, t, 0..D/2)
- * Replaces, for one of q and k, the patched Qwen3RMSNorm on a head_dim-wide row
+ * Replaces the patched Qwen3RMSNorm on head_dim-wide rows
  * (src/bastile/ops/rms_norm.py:105-126) and _rope_kernel
  * (src/bastile/ops/rope.py:13-90) that Qwen3Attention.forward runs back to
- * back (transformers modeling_qwen3.py:256-261).  rstd is [B*T*H] in (b,t,h)
- * order.  Head rows must be 128, 256 or 512 bytes (D = 64/128/256 for 16-bit
- * types); anything else returns BT_ERR_ARG and the caller runs bt_rmsnorm_fwd
- * and bt_rope instead.  Results are bit-identical to that pair. */
-int bt_headnorm_rope_fwd(const void* x, const void* w, const void* cos,
-                         const void* sin, void* out, float* rstd,
-                         int64_t B, int64_t T, int64_t H, int64_t D,
-                         const int64_t x_strides[3], const int64_t out_strides[3],
-                         const int64_t cos_strides[2], int64_t cos_bs,
-                         float eps, int dtype, void* stream);
+ * back (transformers modeling_qwen3.py:256-261).  rstd_q / rstd_k are
+ * [B*T*H] in (b,t,h) order.  Head rows must be 128, 256 or 512 bytes
+ * (D = 64/128/256 for 16-bit types); anything else returns BT_ERR_ARG and the
+ * caller runs bt_rmsnorm_fwd and bt_rope instead.  Results are bit-identical
+ * to that pair of calls. */
+int bt_qk_norm_rope_fwd(const void* q, const void* k, const void* wq, const void* wk,
+                        const void* cos, const void* sin, void* q_out, void* k_out,
+                        float* rstd_q, float* rstd_k,
+                        int64_t B, int64_t T, int64_t Hq, int64_t Hk, int64_t D,
+                        const int64_t q_strides[3], const int64_t k_strides[3],
+                        const int64_t q_out_strides[3], const int64_t k_out_strides[3],
+                        const int64_t cos_strides[2], int64_t cos_bs,
+                        float eps_q, float eps_k, int dtype, void* stream);
 
-/* Backward of the pair: un-rotates dout (rope.py:132-136), then the RMSNorm
- * backward (rms_norm.py:37-68, 128-153) gives dx [B,T,H,D] and dw [D].  `ws`:
- * bt_rmsnorm_bwd_ws_bytes(D) zeroed bytes, left zero (as bt_rmsnorm_bwd). */
-int bt_headnorm_rope_bwd(const void* dout, const void* x, const void* w,
-                         const float* rstd, const void* cos, const void* sin,
-                         void* dx, void* dw, void* ws,
-                         int64_t B, int64_t T, int64_t H, int64_t D,
-                         const int64_t dout_strides[3], const int64_t x_strides[3],
-                         const int64_t dx_strides[3], const int64_t cos_strides[2],
-                         int64_t cos_bs, int dtype, void* stream);
+/* Backward of the pair: un-rotates dq_out / dk_out (rope.py:132-136), then the
+ * RMSNorm backward (rms_norm.py:37-68, 128-153) gives dq, dk and the two weight
+ * gradients dwq, dwk [D].  ws_q and ws_k: two separate scratch buffers of
+ * bt_rmsnorm_bwd_ws_bytes(D) zeroed bytes each, left zero (as bt_rmsnorm_bwd). */
+int bt_qk_norm_rope_bwd(const void* dq_out, const void* dk_out, const void* q, const void* k,
+                        const void* wq, const void* wk, const float* rstd_q, const float* rstd_k,
+                        const void* cos, const void* sin, void* dq, void* dk,
+                        void* dwq, void* dwk, void* ws_q, void* ws_k,
+                        int64_t B, int64_t T, int64_t Hq, int64_t Hk, int64_t D,
+                        const int64_t dq_out_strides[3], const int64_t dk_out_strides[3],
+                        const int64_t q_strides[3], const int64_t k_strides[3],
+                        const int64_t dq_strides[3], const int64_t dk_strides[3],
+                        const int64_t cos_strides[2], int64_t cos_bs, int dtype, void* stream);
 
 /* ------------------------------------------------------ SwiGLU MLP (fused)  */
 

@@ -117,67 +117,81 @@ def test_add_rmsnorm_full_size():
 
 # ------------------------------------------------------------------ q/k-norm + RoPE
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-@pytest.mark.parametrize("b,t,h,d", [(1, 130, 32, 128), (2, 17, 8, 128), (3, 9, 5, 64), (1, 1, 1, 128), (2, 33, 3, 32)])
-def test_head_norm_rope_vs_oracle_and_separate_kernels(b, t, h, d, dtype, tol):
-    from bastile_b200.ops.fused_layers import _head_rows_supported, head_norm_rope
+@pytest.mark.parametrize("b,t,hq,hk,d", [(1, 130, 32, 8, 128), (2, 17, 8, 8, 128), (3, 9, 5, 3, 64), (1, 1, 1, 1, 128),
+                                         (2, 33, 3, 1, 32), (1, 700, 6, 2, 256)])
+def test_qk_norm_rope_vs_oracle_and_separate_kernels(b, t, hq, hk, d, dtype, tol):
+    from bastile_b200.ops.fused_layers import _head_rows_supported, qk_norm_rope
     from bastile_b200.ops.rms_norm import rms_norm
     from bastile_b200.ops.rope import apply_rotary_pos_emb
 
     if not _head_rows_supported(d, dtype):
         pytest.skip("head rows of this size go through the separate kernels")
-    torch.manual_seed(b + t + h + d)
-    # a projection output [B, T, H*D] viewed per head, as Qwen3Attention builds it
-    x = torch.randn(b, t, h * d, device=DEV).to(dtype).requires_grad_(True)
-    w = (1 + 0.1 * torch.randn(d, device=DEV)).to(dtype).requires_grad_(True)
+    torch.manual_seed(b + t + hq + d)
+    # projection outputs [B, T, H*D] viewed per head, as Qwen3Attention builds them
+    xq = torch.randn(b, t, hq * d, device=DEV).to(dtype).requires_grad_(True)
+    xk = torch.randn(b, t, hk * d, device=DEV).to(dtype).requires_grad_(True)
+    wq = (1 + 0.1 * torch.randn(d, device=DEV)).to(dtype).requires_grad_(True)
+    wk = (1 + 0.1 * torch.randn(d, device=DEV)).to(dtype).requires_grad_(True)
     cos, sin = _cos_sin(t, d, dtype=dtype, batch=b if b == 2 else 1)
-    dout = torch.randn(b, h, t, d, device=DEV).to(dtype)  # attention hands back [B,H,T,D]
-    out = head_norm_rope(x.view(b, t, h, d), w, cos, sin, 1e-6).transpose(1, 2)
-    out.backward(dout)
+    dqo = torch.randn(b, hq, t, d, device=DEV).to(dtype)  # attention hands back [B,H,T,D]
+    dko = torch.randn(b, hk, t, d, device=DEV).to(dtype)
+    qo, ko = qk_norm_rope(xq.view(b, t, hq, d), xk.view(b, t, hk, d), wq, wk, cos, sin, 1e-6, 1e-5)
+    qo, ko = qo.transpose(1, 2), ko.transpose(1, 2)
+    torch.autograd.backward([qo, ko], [dqo, dko])
 
     rnd = _round_like(dtype)
-    o_ref, _ = oracle.head_norm_rope_fwd(_np(x).reshape(b, t, h, d), _np(w), _np(cos), _np(sin), 1e-6, round_to=rnd)
-    dx_ref, dw_ref = oracle.head_norm_rope_bwd(_np(dout).transpose(0, 2, 1, 3), _np(x).reshape(b, t, h, d), _np(w),
-                                               _np(cos), _np(sin), 1e-6, round_to=rnd)
-    assert_close(out.transpose(1, 2), o_ref, what="out", **tol)
-    assert_close(x.grad.view(b, t, h, d), dx_ref, what="dx", **tol)
-    m = b * t * h
-    dw_tol = dict(rtol=tol["rtol"], atol=max(tol["atol"], 2e-2 * np.sqrt(m) if dtype != torch.float32 else 1e-4))
-    assert_close(w.grad, dw_ref, what="dw", **dw_tol)
+    for x, w, out, dout, h, eps in ((xq, wq, qo, dqo, hq, 1e-6), (xk, wk, ko, dko, hk, 1e-5)):
+        x4 = _np(x).reshape(b, t, h, d)
+        o_ref, _ = oracle.head_norm_rope_fwd(x4, _np(w), _np(cos), _np(sin), eps, round_to=rnd)
+        dx_ref, dw_ref = oracle.head_norm_rope_bwd(_np(dout).transpose(0, 2, 1, 3), x4, _np(w), _np(cos), _np(sin),
+                                                   eps, round_to=rnd)
+        assert_close(out.transpose(1, 2), o_ref, what="out", **tol)
+        assert_close(x.grad.view(b, t, h, d), dx_ref, what="dx", **tol)
+        dw_tol = dict(rtol=tol["rtol"],
+                      atol=max(tol["atol"], 2e-2 * np.sqrt(b * t * h) if dtype != torch.float32 else 1e-4))
+        assert_close(w.grad, dw_ref, what="dw", **dw_tol)
 
     # the separate kernels round at the same two places: identical bits
-    x2, w2 = x.detach().clone().requires_grad_(True), w.detach().clone().requires_grad_(True)
-    q2 = rms_norm(x2.view(b, t, h, d), w2, 1e-6).transpose(1, 2)
-    k_dummy = torch.zeros(b, 1, t, d, device=DEV, dtype=dtype)
-    o2, _ = apply_rotary_pos_emb(q2, k_dummy, cos, sin)
-    o2.backward(dout)
-    assert torch.equal(out, o2)
-    assert torch.equal(x.grad, x2.grad)
-    assert_close(w.grad, _np(w2.grad), what="dw vs separate", **dw_tol)
+    xq2, xk2, wq2, wk2 = (a.detach().clone().requires_grad_(True) for a in (xq, xk, wq, wk))
+    q2 = rms_norm(xq2.view(b, t, hq, d), wq2, 1e-6).transpose(1, 2)
+    k2 = rms_norm(xk2.view(b, t, hk, d), wk2, 1e-5).transpose(1, 2)
+    qo2, ko2 = apply_rotary_pos_emb(q2, k2, cos, sin)
+    torch.autograd.backward([qo2, ko2], [dqo, dko])
+    assert torch.equal(qo, qo2) and torch.equal(ko, ko2)
+    assert torch.equal(xq.grad, xq2.grad) and torch.equal(xk.grad, xk2.grad)
 
 
-def test_head_norm_rope_full_size_matches_separate_kernels():
-    """q of Qwen3-8B at sequence length 8192: 32 heads x 128."""
-    from bastile_b200.ops.fused_layers import head_norm_rope
+def test_qk_norm_rope_full_size_matches_separate_kernels():
+    """q and k of Qwen3-8B at sequence length 8192: 32 and 8 heads of 128."""
+    from bastile_b200.ops.fused_layers import qk_norm_rope
     from bastile_b200.ops.rms_norm import rms_norm
     from bastile_b200.ops.rope import apply_rotary_pos_emb
 
     torch.manual_seed(2)
-    b, t, h, d = 1, 8192, 32, 128
-    x = torch.randn(b, t, h * d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
-    w = (1 + 0.1 * torch.randn(d, device=DEV)).to(torch.bfloat16).requires_grad_(True)
-    cos, sin = _cos_sin(t, d, dtype=torch.bfloat16)
-    dout = torch.randn(b, h, t, d, device=DEV, dtype=torch.bfloat16)
-    out = head_norm_rope(x.view(b, t, h, d), w, cos, sin, 1e-6).transpose(1, 2)
-    out.backward(dout)
-    x2, w2 = x.detach().clone().requires_grad_(True), w.detach().clone().requires_grad_(True)
-    q2 = rms_norm(x2.view(b, t, h, d), w2, 1e-6).transpose(1, 2)
-    o2, _ = apply_rotary_pos_emb(q2, torch.zeros(b, 1, t, d, device=DEV, dtype=torch.bfloat16), cos, sin)
-    o2.backward(dout)
-    assert torch.equal(out, o2) and torch.equal(x.grad, x2.grad)
-    assert_close(w.grad, _np(w2.grad), what="dw", rtol=2e-2, atol=2e-2 * float(w2.grad.float().abs().max()))
+    b, t, hq, hk, d = 1, 8192, 32, 8, 128
+    bf = torch.bfloat16
+    xq = torch.randn(b, t, hq * d, device=DEV, dtype=bf, requires_grad=True)
+    xk = torch.randn(b, t, hk * d, device=DEV, dtype=bf, requires_grad=True)
+    wq = (1 + 0.1 * torch.randn(d, device=DEV)).to(bf).requires_grad_(True)
+    wk = (1 + 0.1 * torch.randn(d, device=DEV)).to(bf).requires_grad_(True)
+    cos, sin = _cos_sin(t, d, dtype=bf)
+    dqo = torch.randn(b, hq, t, d, device=DEV, dtype=bf)
+    dko = torch.randn(b, hk, t, d, device=DEV, dtype=bf)
+    qo, ko = qk_norm_rope(xq.view(b, t, hq, d), xk.view(b, t, hk, d), wq, wk, cos, sin)
+    qo, ko = qo.transpose(1, 2), ko.transpose(1, 2)
+    torch.autograd.backward([qo, ko], [dqo, dko])
+    xq2, xk2, wq2, wk2 = (a.detach().clone().requires_grad_(True) for a in (xq, xk, wq, wk))
+    q2 = rms_norm(xq2.view(b, t, hq, d), wq2, 1e-6).transpose(1, 2)
+    k2 = rms_norm(xk2.view(b, t, hk, d), wk2, 1e-6).transpose(1, 2)
+    qo2, ko2 = apply_rotary_pos_emb(q2, k2, cos, sin)
+    torch.autograd.backward([qo2, ko2], [dqo, dko])
+    assert torch.equal(qo, qo2) and torch.equal(ko, ko2)
+    assert torch.equal(xq.grad, xq2.grad) and torch.equal(xk.grad, xk2.grad)
+    for w, w2 in ((wq, wq2), (wk, wk2)):
+        assert_close(w.grad, _np(w2.grad), what="dw", rtol=2e-2, atol=2e-2 * float(w2.grad.float().abs().max()))
 
 
-def test_head_norm_rope_rejects_unsupported_head_rows():
+def test_qk_norm_rope_rejects_unsupported_head_rows():
     from bastile_b200 import _lib
 
     lib = _lib.get_lib()
@@ -185,10 +199,11 @@ def test_head_norm_rope_rejects_unsupported_head_rows():
     out, rstd = torch.empty_like(x), torch.empty(8, device=DEV)
     w = torch.ones(24, device=DEV, dtype=torch.bfloat16)
     cos, sin = _cos_sin(4, 24, dtype=torch.bfloat16)
-    rc = lib.bt_headnorm_rope_fwd(x.data_ptr(), w.data_ptr(), cos.data_ptr(), sin.data_ptr(), out.data_ptr(),
-                                  rstd.data_ptr(), 1, 4, 2, 24, _lib.I64x3(*x.stride()[:3]),
-                                  _lib.I64x3(*out.stride()[:3]), _lib.I64x2(cos.stride(0), cos.stride(1)), 1, 1e-6, 0,
-                                  _lib.stream_ptr(x.device))
+    s3 = _lib.I64x3(*x.stride()[:3])
+    rc = lib.bt_qk_norm_rope_fwd(x.data_ptr(), x.data_ptr(), w.data_ptr(), w.data_ptr(), cos.data_ptr(),
+                                 sin.data_ptr(), out.data_ptr(), out.data_ptr(), rstd.data_ptr(), rstd.data_ptr(), 1, 4,
+                                 2, 2, 24, s3, s3, s3, s3, _lib.I64x2(cos.stride(0), cos.stride(1)), 1, 1e-6, 1e-6, 0,
+                                 _lib.stream_ptr(x.device))
     assert rc == -1 and b"not supported" in lib.bt_last_error()
 
 

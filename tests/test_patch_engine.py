@@ -135,3 +135,57 @@ def test_register_patch_and_registry_roundtrip():
     assert reg.get_applied() == ["a_x"] and reg.get("a_x").original is abs
     reg.mark_reset("a_x")
     assert reg.get_applied() == [] and reg.get("missing") is None
+
+
+def test_fused_layers_are_opt_in_and_reset_restores_the_hf_forwards(qwen3):
+    """apply() alone leaves Qwen3DecoderLayer.forward / Qwen3Attention.forward untouched (the
+    reference patches neither); fused_layers=True replaces both and every form of reset() that
+    names them, or names nothing, puts the originals back."""
+    from bastile_b200.ops import fused_layers
+
+    hf_layer, hf_attn = qwen3.Qwen3DecoderLayer.forward, qwen3.Qwen3Attention.forward
+    bastile.apply()
+    assert qwen3.Qwen3DecoderLayer.forward is hf_layer and qwen3.Qwen3Attention.forward is hf_attn
+    bastile.reset()
+
+    applied = bastile.apply(fused_layers=True)
+    assert applied == ["rms_norm_qwen3", "rope_qwen3", "swiglu_qwen3", "decoder_layer_qwen3", "attention_qwen3",
+                       "fused_linear_cross_entropy"]
+    assert qwen3.Qwen3DecoderLayer.forward is fused_layers.decoder_layer_forward
+    assert qwen3.Qwen3Attention.forward is fused_layers.attention_forward
+    assert bastile.apply(fused_layers=True) == applied  # idempotent
+    assert bastile.get_patched_ops() == ["rms_norm_qwen3", "rope_qwen3", "swiglu_qwen3"]  # registry patches only
+    bastile.reset(["attention_qwen3"])
+    assert qwen3.Qwen3Attention.forward is hf_attn
+    assert qwen3.Qwen3DecoderLayer.forward is fused_layers.decoder_layer_forward
+    bastile.reset()
+    assert qwen3.Qwen3DecoderLayer.forward is hf_layer and fused_layers.installed() == []
+
+    # without the norm patch there is nothing to fuse into; without RoPE only the layer forward goes in
+    assert "decoder_layer_qwen3" not in bastile.apply(fused_layers=True, rms_norm=False)
+    bastile.reset()
+    applied = bastile.apply(fused_layers=True, rope=False)
+    assert "decoder_layer_qwen3" in applied and "attention_qwen3" not in applied
+    bastile.reset()
+    with pytest.raises(ValueError):
+        fused_layers.install(qwen3, projections="sometimes")
+
+
+def test_fused_forwards_fall_back_to_plain_modules_on_cpu(qwen3):
+    """A model built BEFORE apply() keeps HF's own norm / MLP modules; the fused layer forward
+    must then behave exactly like HF's (here on CPU, where none of the kernels can run; the RoPE
+    patch is a module-level function that has no CPU form, so it stays off)."""
+    from golden.make_golden import build_tiny_qwen3, tiny_qwen3_inputs
+
+    model = build_tiny_qwen3().eval()  # HF modules inside
+    ids, _ = tiny_qwen3_inputs()
+    with torch.no_grad():
+        want = model(input_ids=ids).logits
+    applied = bastile.apply(fused_layers=True, rope=False, fused_linear_cross_entropy=False)
+    assert "decoder_layer_qwen3" in applied
+    try:
+        with torch.no_grad():
+            got = model(input_ids=ids).logits
+    finally:
+        bastile.reset()
+    assert torch.equal(got, want)

@@ -75,7 +75,7 @@ SIGNATURES = {
     "bt_lce_count_valid": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
     "bt_lce_reduce_loss": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "bt_adamw_step": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_float,
-                              c_float, c_float, c_int64, c_int, c_void_p]),
+                              c_float, c_float, c_int64, c_int, c_int, c_void_p]),
     "bt_scale_cast": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]),
 }
 

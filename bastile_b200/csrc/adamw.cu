@@ -110,12 +110,13 @@ __global__ void __launch_bounds__(kThreads) adamw_many(const Table t, Hyper h) {
 }
 
 template <typename T>
-int one_t(void* p, const void* g, void* m, void* v, int64_t n, const Hyper& h, cudaStream_t s) {
+int one_t(void* p, const void* g, void* m, void* v, int64_t n, const Hyper& h, int ctas_per_sm,
+          cudaStream_t s) {
   constexpr int E = Cvt<T>::N;
   const int vec_ok = aligned16(p) && aligned16(g) && aligned16(m) && aligned16(v);
   const int64_t work = vec_ok ? ceil_div(n, E) : n;
   const int64_t blocks = ceil_div(work, kThreads);
-  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * ctas_per_sm;
   adamw_one<T><<<static_cast<unsigned>(blocks < 1 ? 1 : (blocks < cap ? blocks : cap)), kThreads, 0,
                  s>>>(static_cast<T*>(p), static_cast<const T*>(g), static_cast<T*>(m),
                       static_cast<T*>(v), n, vec_ok, h);
@@ -139,9 +140,11 @@ int many_t(const Table& t, int64_t max_n, const Hyper& h, cudaStream_t s) {
 extern "C" int bt_adamw_step(void* const* params, const void* const* grads, void* const* exp_avg,
                              void* const* exp_avg_sq, const int64_t* numel, int n_tensors, float lr,
                              float beta1, float beta2, float eps, float weight_decay, int64_t step,
-                             int dtype, void* stream) {
+                             int ctas_per_sm, int dtype, void* stream) {
   using namespace bt;
   BT_CHECK_ARG(n_tensors >= 0 && step >= 1, "adamw_step: bad tensor count or step");
+  BT_CHECK_ARG(ctas_per_sm >= 0 && ctas_per_sm <= 32, "adamw_step: ctas_per_sm must be 0..32");
+  if (ctas_per_sm == 0) ctas_per_sm = 16;
   BT_CHECK_ARG(n_tensors == 0 || (params && grads && exp_avg && exp_avg_sq && numel),
                "adamw_step: null table");
   BT_CHECK_ARG(dtype == BT_BF16 || dtype == BT_FP16 || dtype == BT_FP32, "adamw_step: unknown dtype %d",
@@ -190,9 +193,9 @@ extern "C" int bt_adamw_step(void* const* params, const void* const* grads, void
     }
     int rc;
     switch (dtype) {
-      case BT_BF16: rc = one_t<__nv_bfloat16>(params[i], grads[i], exp_avg[i], exp_avg_sq[i], n, h, s); break;
-      case BT_FP16: rc = one_t<__half>(params[i], grads[i], exp_avg[i], exp_avg_sq[i], n, h, s); break;
-      default: rc = one_t<float>(params[i], grads[i], exp_avg[i], exp_avg_sq[i], n, h, s); break;
+      case BT_BF16: rc = one_t<__nv_bfloat16>(params[i], grads[i], exp_avg[i], exp_avg_sq[i], n, h, ctas_per_sm, s); break;
+      case BT_FP16: rc = one_t<__half>(params[i], grads[i], exp_avg[i], exp_avg_sq[i], n, h, ctas_per_sm, s); break;
+      default: rc = one_t<float>(params[i], grads[i], exp_avg[i], exp_avg_sq[i], n, h, ctas_per_sm, s); break;
     }
     if (rc) return rc;
   }

@@ -436,6 +436,9 @@ def main():
     ap.add_argument("--gemm-projections", default="off", choices=["off", "dx", "all"],
                     help="with fused layers: off = q/k/v/o_proj stay on nn.Linear (cuBLAS); dx = their shared input "
                          "gradient from two bt_gemm_ex launches; all = every product of theirs on bt_gemm_ex")
+    ap.add_argument("--no-overlap-optimizer", action="store_true",
+                    help="single GPU: run the whole AdamW step after the backward pass instead of updating each "
+                         "large parameter underneath it as soon as its gradient is complete")
     ap.add_argument("--no-per-op", action="store_true")
     ap.add_argument("--only-op", default=None, choices=["rmsnorm", "rope", "mlp", "lce"],
                     help="run just this op's forward+backward micro-benchmark (small case for profilers)")
@@ -527,10 +530,14 @@ def main():
 
         net = DDP(model, device_ids=[local], gradient_as_bucket_view=True, bucket_cap_mb=256)
         parallelism = f"dp{world} (DistributedDataParallel, NCCL)"
+    overlap_opt = args.optimizer == "bastile" and world == 1 and not args.no_overlap_optimizer
     if args.optimizer == "bastile":
         from bastile_b200.optim import AdamW
 
-        opt = AdamW(net.parameters(), lr=1e-4)
+        # one process: every large parameter is updated as soon as its gradient is complete, on a side
+        # stream underneath the rest of the backward pass (under DDP / FSDP gradients are only final after
+        # the reduction, so the update stays in step())
+        opt = AdamW(net.parameters(), lr=1e-4, overlap_backward=overlap_opt)
     else:
         opt = torch.optim.AdamW(net.parameters(), lr=1e-4, fused=True)
 
@@ -622,7 +629,7 @@ def main():
                                    "batch 1 fwd+bwd+AdamW, random init",
                        "global_batch_tokens": seq * world, "seq_len": seq,
                        "parallelism": parallelism,
-                       "attention": "torch SDPA", "activation_checkpointing": bool(args.grad_checkpoint), "fused_layers": fused_layers, "gemm_projections": args.gemm_projections if fused_layers else "off", "optimizer": ("bastile_b200.optim.AdamW" if args.optimizer == "bastile" else "torch.optim.AdamW(fused=True)")
+                       "attention": "torch SDPA", "activation_checkpointing": bool(args.grad_checkpoint), "fused_layers": fused_layers, "gemm_projections": args.gemm_projections if fused_layers else "off", "optimizer": (("bastile_b200.optim.AdamW" + (", updates overlapped with the backward pass" if overlap_opt else "")) if args.optimizer == "bastile" else "torch.optim.AdamW(fused=True)")
                                     + ", bf16 params and state",
                        "l2": "each step streams ~65 GB of weights, gradients and optimizer state: far larger than the 126 MB L2"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": seq * 8, "d2h_bytes_per_step": 4,

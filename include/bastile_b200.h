@@ -338,12 +338,16 @@ int bt_scale_cast(const void* in, void* out, int64_t n, const float* scale,
  * count used for the bias corrections.  The reference has no optimizer of its
  * own: its benchmark loop runs torch.optim.AdamW inside the timed region
  * (tests/benchmarks/e2e/qwen_8b_seqlen.py:122-125, 154-158); this is that step
- * as one streaming pass per tensor. */
+ * as one streaming pass per tensor.  `ctas_per_sm` caps the resident CTAs per SM
+ * of the large-tensor kernel (0 = default 16, which saturates HBM when the
+ * kernel runs alone); a caller that runs the update on a side stream underneath
+ * tensor-core work passes 1 or 2 so that the other stream's kernels still find
+ * room on every SM. */
 int bt_adamw_step(void* const* params, const void* const* grads,
                   void* const* exp_avg, void* const* exp_avg_sq,
                   const int64_t* numel, int n_tensors,
-                  float lr, float beta1, float beta2, float eps,
-                  float weight_decay, int64_t step, int dtype, void* stream);
+                  float lr, float beta1, float beta2, float eps, float weight_decay,
+                  int64_t step, int ctas_per_sm, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -51,3 +51,50 @@ def test_cuda_adamw_matches_oracle_and_torch(dtype):
             assert_close(p, r, what=f"param {i} vs torch", rtol=2e-2, atol=2e-2)
             assert_close(ours.state[p]["exp_avg"], ref.state[r]["exp_avg"], what=f"m {i}", rtol=2e-2, atol=2e-3)
     assert set(ours.state[params[0]]) == {"step", "exp_avg", "exp_avg_sq"}
+
+
+@pytest.mark.gpu
+def test_overlap_backward_gives_the_same_bits_as_the_plain_step():
+    """Updates queued from post-accumulate-grad hooks on a side stream (large tensors) plus the
+    rest in step(): every parameter and moment ends up bit-identical to the plain optimizer."""
+    from bastile_b200.optim import _OVERLAP_MIN_NUMEL, AdamW
+
+    def build():
+        torch.manual_seed(3)
+        return torch.nn.Sequential(torch.nn.Linear(1024, 2048, bias=True), torch.nn.GELU(),
+                                   torch.nn.Linear(2048, 1024, bias=False), torch.nn.LayerNorm(1024),
+                                   torch.nn.Linear(1024, 1024, bias=False)).cuda().to(torch.bfloat16)
+
+    nets = [build(), build()]
+    assert any(p.numel() >= _OVERLAP_MIN_NUMEL for p in nets[0].parameters())
+    assert any(p.numel() < _OVERLAP_MIN_NUMEL for p in nets[0].parameters())
+    hp = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    opts = [AdamW(nets[0].parameters(), **hp), AdamW(nets[1].parameters(), overlap_backward=True, **hp)]
+    torch.manual_seed(4)
+    xs = [torch.randn(512, 1024, device="cuda", dtype=torch.bfloat16) for _ in range(4)]
+    for x in xs:
+        for net, opt in zip(nets, opts):
+            opt.zero_grad(set_to_none=True)
+            net(x).float().pow(2).mean().backward()
+            opt.step()
+    assert len(opts[1]._early) == 0 and len(opts[1]._side_streams) == 1
+    torch.cuda.synchronize()
+    for (name, a), b in zip(nets[0].named_parameters(), nets[1].parameters()):
+        assert torch.equal(a, b), name
+        assert torch.equal(opts[0].state[a]["exp_avg"], opts[1].state[b]["exp_avg"]), name
+        assert torch.equal(opts[0].state[a]["exp_avg_sq"], opts[1].state[b]["exp_avg_sq"]), name
+        assert opts[0].state[a]["step"] == opts[1].state[b]["step"] == len(xs)
+    with pytest.raises(RuntimeError):
+        opts[1].step(closure=lambda: None)
+
+
+def test_overlap_backward_is_inert_without_cuda_gradients():
+    """On CPU tensors the hooks do nothing (and the optimizer refuses the step as before)."""
+    from bastile_b200.optim import AdamW
+
+    w = torch.nn.Parameter(torch.randn(2048, 1024))
+    opt = AdamW([w], overlap_backward=True)
+    (w * w).sum().backward()
+    assert not opt._early and not opt._side_streams
+    with pytest.raises(RuntimeError):
+        opt.step()

@@ -18,6 +18,19 @@
 //                 i.e. accumulator columns [0,128) = A*B0^T, [128,256) = A*B1^T;
 //     two pairs : the K loop runs over (A0,B0) and then (A1,B1) into one accumulator.
 //
+//   Two kernels share the epilogues.  gemm_kernel is the layout above.  gemm_kernel_pair
+//   (the default) runs 2-CTA clusters on 256 x 256 tiles with tcgen05.mma.cta_group::2:
+//   each CTA stages its own 128 rows of A and 128 columns of B (6-stage ring of 32 KB),
+//   the leader CTA's warp 1 issues the MMAs for both, tcgen05.commit arrives on both
+//   CTAs' barriers, and an eleventh warp (352 threads) issues the B loads next to warp
+//   0's A loads.  Tile loads are plain per-CTA TMA loads; nothing is multicast.
+//
+//   fp32 operands are multiplied as tf32 (K depth 32 per 128-byte row); Geo<T> carries
+//   the per-type tile geometry at compile time.
+//
+//   The plain epilogue can add an fp32 matrix and/or a matrix in the operand type (a
+//   residual stream) to the accumulator before the single rounding.
+//
 //   Every mbarrier wait is bounded (sm100_ptx.cuh); a wait that runs out sets the
 //   caller's status word, makes all roles leave their loops, and the CTA still
 //   frees its tensor memory before exiting.

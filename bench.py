@@ -211,7 +211,11 @@ def run_reference_arm(args):
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": len(vals), "warmup": min(args.warmup, 1), "ms_per_step": SEQ_LEN / value * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"qwen3-8b seq{SEQ_LEN} batch1 fwd+bwd+AdamW (CPU sample at seq {seq})"},
+            "config": {"workload": f"qwen3-8b ({QWEN3_8B['num_hidden_layers']} layers, hidden 4096, intermediate "
+                                   f"{QWEN3_8B['intermediate_size']}, vocab 151936) seq {SEQ_LEN} batch 1 fwd+bwd+AdamW, "
+                                   "random init",
+                       "sample": f"bounded CPU sample at {seq} tokens, composed to a 36-layer step (see cpu_baseline)",
+                       "global_batch_tokens": SEQ_LEN, "seq_len": SEQ_LEN, "parallelism": "host CPU threads"},
             "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "reference",
                              "sample": sample},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

@@ -47,9 +47,14 @@ struct HeadPair {
   unsigned split;
 };
 
+// Rounds a 16-byte vector's worth of fp32 values to the storage type and back (paired
+// conversions: half the instructions of rounding element by element).
 template <typename T>
-__device__ __forceinline__ float round_to(float v) {
-  return Cvt<T>::to_f(Cvt<T>::from_f(v));
+__device__ __forceinline__ void round_vec(float (&v)[Cvt<T>::N]) {
+  if constexpr (sizeof(T) < 4) {
+    const uint4 packed = Cvt<T>::pack(v);
+    Cvt<T>::unpack(packed, v);
+  }
 }
 
 // Work item = (token, block of HPI consecutive heads): the heads of one token share the
@@ -133,12 +138,18 @@ headnorm_rope_fwd(const __grid_constant__ HeadPair pp) {
       }
       const float ss = group_sum<LPR>(p1 + p2);
       const float rs = rsqrtf(ss * inv_n + a.eps);
+      float y1[E], y2[E];
 #pragma unroll
       for (int e = 0; e < E; ++e) {
-        const float y1 = round_to<T>(f1[e] * rs * w1[e]);
-        const float y2 = round_to<T>(f2[e] * rs * w2[e]);
-        o1[e] = fmaf(-y2, s[e], y1 * c[e]);  // y1*cos - y2*sin
-        o2[e] = fmaf(y1, s[e], y2 * c[e]);   // y2*cos + y1*sin
+        y1[e] = f1[e] * rs * w1[e];
+        y2[e] = f2[e] * rs * w2[e];
+      }
+      round_vec<T>(y1);  // the normalised row as the stand-alone norm kernel would have stored it
+      round_vec<T>(y2);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        o1[e] = fmaf(-y2[e], s[e], y1[e] * c[e]);  // y1*cos - y2*sin
+        o2[e] = fmaf(y1[e], s[e], y2[e] * c[e]);   // y2*cos + y1*sin
       }
       if (it.valid && it.h0 + u < H) {
         if (lane == 0) a.rstd_out[it.row0 + u] = rs;
@@ -213,8 +224,13 @@ headnorm_rope_bwd(const __grid_constant__ HeadPair pp) {
 #pragma unroll
       for (int e = 0; e < E; ++e) {
         // inverse rotation: d1*cos + d2*sin ; d2*cos - d1*sin
-        d1[e] = round_to<T>(fmaf(gb[e], s[e], ga[e] * c[e]));
-        d2[e] = round_to<T>(fmaf(-ga[e], s[e], gb[e] * c[e]));
+        d1[e] = fmaf(gb[e], s[e], ga[e] * c[e]);
+        d2[e] = fmaf(-ga[e], s[e], gb[e] * c[e]);
+      }
+      round_vec<T>(d1);  // the un-rotated gradient as the stand-alone RoPE backward would have stored it
+      round_vec<T>(d2);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
         const float h1 = xa[e] * rs[u], h2 = xb[e] * rs[u];
         p1 = fmaf(h1, d1[e] * w1[e], p1);
         p2 = fmaf(h2, d2[e] * w2[e], p2);

@@ -249,15 +249,15 @@ def _gemm(a, b, out, m, n, k, a_kmajor, b_kmajor, *, a1=None, b1=None, k1=0, add
     """out[m,n] = op(a) op(b) (+ op(a1) op(b1)) (+ addend_t) through bt_gemm_ex; 2-D row-major tensors."""
     lib = _lib.get_lib()
     d = _lib.GemmDesc()
-    d.A, d.B, d.lda, d.ldb, d.K = a.data_ptr(), b.data_ptr(), a.stride(0), b.stride(0), k
+    d.A, d.B, d.lda, d.ldb, d.K = a.data_ptr(), b.data_ptr(), _ld(a), _ld(b), k
     if a1 is not None:
-        d.A1, d.B1, d.lda1, d.ldb1, d.K1 = a1.data_ptr(), b1.data_ptr(), a1.stride(0), b1.stride(0), k1
-    d.D, d.ldd, d.M, d.N = out.data_ptr(), out.stride(0), m, n
+        d.A1, d.B1, d.lda1, d.ldb1, d.K1 = a1.data_ptr(), b1.data_ptr(), _ld(a1), _ld(b1), k1
+    d.D, d.ldd, d.M, d.N = out.data_ptr(), _ld(out), m, n
     d.a_kmajor, d.b_kmajor = int(a_kmajor), int(b_kmajor)
     d.in_dtype = _lib.dtype_code(a.dtype)
     d.out_dtype = _lib.dtype_code(out.dtype)
     if addend_t is not None:
-        d.addend_t, d.ld_addend_t = addend_t.data_ptr(), addend_t.stride(0)
+        d.addend_t, d.ld_addend_t = addend_t.data_ptr(), _ld(addend_t)
     st = _lib.status_word(dev)
     with _lib.device_of(dev), _lib.timed(label, 1, dev):
         rc = lib.bt_gemm_ex(ctypes.byref(d), st.data_ptr(), _lib.stream_ptr(dev))

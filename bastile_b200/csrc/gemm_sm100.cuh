@@ -36,6 +36,7 @@
 //   frees its tensor memory before exiting.
 #pragma once
 
+#include <atomic>
 #include <mutex>
 
 #include "bt_common.cuh"
@@ -81,6 +82,9 @@ struct Params {
   uint64_t a_desc_hi, b_desc_hi;
   uint32_t a_kstep, b_kstep;  // descriptor address step per MMA K slice, 16-byte units
   int32_t* status;
+  // Dynamic tile hand-out (pair kernel, optional): word 0 is the next-tile counter, then
+  // kSchedRing published tile ids per CTA pair.  nullptr: tiles are dealt round-robin.
+  unsigned long long* sched;
   // --- plain epilogue: out = T(alpha * (acc + addend))
   void* out;
   int64_t ldo;
@@ -543,6 +547,58 @@ constexpr int kThreadsPair = kThreads + 32;
 constexpr int kStageBytes2 = kABytes + kBBytes / 2;
 constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + 1024 + 256;
 
+// ---- dynamic tile hand-out -------------------------------------------------------------
+// With a fixed round-robin deal a CTA pair that gets its SMs late (a collective's kernel is
+// sitting on them when the GEMM starts) still has its whole share of tiles in front of it and
+// the launch takes up to twice as long.  In dynamic mode the leader CTA's A-producer draws
+// tile numbers from a global counter, one tile ahead of the one it is loading, and publishes
+// them in a small ring in global memory; every other role of the pair - the second
+// producer, the peer CTA's producers, the MMA issuer, the epilogue warps - reads its i-th
+// tile from ring slot i % kSchedRing (tag i + 1 in the upper half says the slot is fresh).
+// How far the drawing thread can be ahead of the slowest reader: one tile published in
+// advance, up to kStages2 tiles of loads in flight when a tile is a single k-block, and two
+// accumulators between the MMA issuer and the epilogue - nine tiles, so sixteen slots never
+// wrap onto an unread entry.  The host clears counter and ring before the launch.
+constexpr int kSchedRing = 16;
+constexpr int kSchedMaxPairs = 256;
+constexpr int kSchedWords = 1 + kSchedMaxPairs * kSchedRing;
+constexpr int kSchedSlots = 32;
+__device__ unsigned long long g_tile_sched[kSchedSlots][kSchedWords];
+
+__device__ __forceinline__ int sched_draw(const Params& p) {
+  const unsigned int t = atomicAdd(reinterpret_cast<unsigned int*>(p.sched), 1u);
+  return t < static_cast<unsigned int>(p.num_tiles) ? static_cast<int>(t) : -1;
+}
+__device__ __forceinline__ void sched_publish(const Params& p, int pair, int i, int tile) {
+  unsigned long long* slot = p.sched + 1 + pair * kSchedRing + (i % kSchedRing);
+  const unsigned long long v = (static_cast<unsigned long long>(i + 1) << 32) |
+                               static_cast<unsigned int>(tile + 1);
+  asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(slot), "l"(v) : "memory");
+}
+// The i-th tile of this pair (-1: no more tiles, or the wait was given up).
+__device__ __forceinline__ int sched_wait(const Params& p, int pair, int npairs, int i,
+                                          volatile int* cta_abort, int status_bit) {
+  if (p.sched == nullptr) {
+    const int t = pair + i * npairs;
+    return t < p.num_tiles ? t : -1;
+  }
+  const unsigned long long* slot = p.sched + 1 + pair * kSchedRing + (i % kSchedRing);
+  const uint64_t t0 = ptx::globaltimer_ns();
+  for (;;) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(slot) : "memory");
+    if (static_cast<unsigned int>(v >> 32) == static_cast<unsigned int>(i + 1))
+      return static_cast<int>(static_cast<unsigned int>(v)) - 1;
+    if (*cta_abort != 0) return -1;
+    if (ptx::globaltimer_ns() - t0 > 1000000000ull) {
+      *cta_abort = 1;
+      if (p.status != nullptr) atomicOr(p.status, status_bit);
+      return -1;
+    }
+    __nanosleep(200);
+  }
+}
+
 template <int EPI, typename T>
 __global__ void __launch_bounds__(kThreadsPair, 1)
 gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
@@ -603,10 +659,27 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
     // barrier traffic) was within a factor ~1.4 of the 512 cycles the MMAs of a k-block take.
     if (lane == 0) {
       const bool do_a = warp == 0;
+      const bool draws = p.sched != nullptr && do_a && leader;  // this thread hands out the tiles
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = pair; ok && tile < p.num_tiles; tile += npairs) {
+      int next = -1;
+      if (draws) {
+        next = sched_draw(p);
+        sched_publish(p, pair, 0, next);
+      }
+      for (int it = 0; ok; ++it) {
+        int tile;
+        if (draws) {
+          tile = next;
+          if (tile >= 0) {  // claim the following tile now: the others find it published early
+            next = sched_draw(p);
+            sched_publish(p, pair, it + 1, next);
+          }
+        } else {
+          tile = sched_wait(p, pair, npairs, it, cta_abort, ST_PRODUCER);
+        }
+        if (tile < 0) break;
         int m_idx, n_idx;
         tile_coords(p, tile, &m_idx, &n_idx);
         const int m0 = m_idx * (2 * BM) + static_cast<int>(rank) * BM;
@@ -657,7 +730,8 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = pair; ok && tile < p.num_tiles; tile += npairs) {
+      for (int it = 0; ok; ++it) {
+        if (sched_wait(p, pair, npairs, it, cta_abort, ST_MMA_ACC) < 0) break;
         if (!ptx::mbar_wait(&tempty[acc], acc_phase ^ 1u, cta_abort, p.status, ST_MMA_ACC)) break;
         ptx::tcgen05_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
@@ -699,7 +773,11 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
     const int half = (warp - 2) >> 2;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = pair; tile < p.num_tiles; tile += npairs) {
+    for (int it = 0;; ++it) {
+      int tile = 0;
+      if (lane == 0) tile = sched_wait(p, pair, npairs, it, cta_abort, ST_EPILOGUE);
+      tile = __shfl_sync(0xffffffffu, tile, 0);
+      if (tile < 0) break;
       int m_idx, n_idx;
       tile_coords(p, tile, &m_idx, &n_idx);
       if (!ptx::mbar_wait(&tfull[acc], acc_phase, cta_abort, p.status, ST_EPILOGUE)) break;
@@ -828,6 +906,27 @@ int launch_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1
   return BT_OK;
 }
 
+// 0 (default): tiles are dealt round-robin; 1: CTA pairs draw them from a global counter.
+inline int& dynamic_tiles() {
+  static int mode = 0;
+  return mode;
+}
+
+// Device address of the scheduler pool on the current device (looked up once per device).
+inline unsigned long long* sched_pool() {
+  static std::mutex mu;
+  static unsigned long long* pools[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (pools[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_tile_sched) != cudaSuccess) return nullptr;
+    pools[dev] = static_cast<unsigned long long*>(ptr);
+  }
+  return pools[dev];
+}
+
 template <int EPI, typename T>
 int launch_pair_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1,
                   const CUtensorMap& b1, const Params& p, cudaStream_t s) {
@@ -844,6 +943,24 @@ int launch_pair_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMa
   }
   const int max_pairs = sm_count() / 2;
   const int pairs = p.num_tiles < max_pairs ? p.num_tiles : max_pairs;
+  Params q = p;
+  q.sched = nullptr;
+  if (dynamic_tiles() != 0 && pairs <= kSchedMaxPairs && p.num_tiles > pairs) {
+    // a slot of the scheduler pool, cleared on the stream ahead of the kernel
+    static std::atomic<unsigned> next_slot{0};
+    unsigned long long* pool = sched_pool();
+    if (pool == nullptr) {
+      set_error("gemm: cannot locate the tile-scheduler pool");
+      return BT_ERR_DRIVER;
+    }
+    q.sched = pool + static_cast<size_t>(next_slot.fetch_add(1) % kSchedSlots) * kSchedWords;
+    const cudaError_t me =
+        cudaMemsetAsync(q.sched, 0, sizeof(unsigned long long) * (1 + pairs * kSchedRing), s);
+    if (me != cudaSuccess) {
+      set_error("gemm: clearing the tile scheduler failed: %s", cudaGetErrorString(me));
+      return BT_ERR_LAUNCH;
+    }
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
   cfg.blockDim = dim3(kThreadsPair, 1, 1);
@@ -856,7 +973,7 @@ int launch_pair_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMa
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a0, b0, a1, b1, p);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a0, b0, a1, b1, q);
   if (e != cudaSuccess) {
     set_error("gemm_kernel_pair: %s", cudaGetErrorString(e));
     return BT_ERR_LAUNCH;

@@ -76,6 +76,12 @@ extern "C" int bt_set_gemm_cta_pairs(int enable) {
   return prev;
 }
 
+extern "C" int bt_set_gemm_dynamic_tiles(int enable) {
+  const int prev = bt::gemm::dynamic_tiles();
+  if (enable >= 0) bt::gemm::dynamic_tiles() = enable ? 1 : 0;
+  return prev;
+}
+
 extern "C" int bt_gemm(const void* A, const void* B, void* D, int64_t M, int64_t N, int64_t K,
                        int64_t lda, int64_t ldb, int64_t ldd, int a_kmajor, int b_kmajor,
                        int in_dtype, int out_dtype, const float* addend, int64_t ld_addend,

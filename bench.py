@@ -443,6 +443,10 @@ def main():
     ap.add_argument("--no-overlap-optimizer", action="store_true",
                     help="single GPU: run the whole AdamW step after the backward pass instead of updating each "
                          "large parameter underneath it as soon as its gradient is complete")
+    ap.add_argument("--tiles", default="auto", choices=["auto", "fixed", "dynamic"],
+                    help="how the GEMM's CTA pairs get their tiles: dealt round-robin at launch (fixed) or drawn from "
+                         "a global counter at run time (dynamic: bt_set_gemm_dynamic_tiles(1)); auto = dynamic when "
+                         "NCCL collectives share the GPU with the backward pass (more than one rank), else fixed")
     ap.add_argument("--no-per-op", action="store_true")
     ap.add_argument("--only-op", default=None, choices=["rmsnorm", "rope", "mlp", "lce"],
                     help="run just this op's forward+backward micro-benchmark (small case for profilers)")
@@ -484,6 +488,8 @@ def main():
         return
 
     fused_layers = not args.no_fused_layers
+    dynamic_tiles = args.tiles == "dynamic" or (args.tiles == "auto" and world > 1)
+    _lib.get_lib().bt_set_gemm_dynamic_tiles(1 if dynamic_tiles else 0)
     applied = bastile_b200.apply(fused_layers=fused_layers, gemm_projections=args.gemm_projections)
     expected = ["rms_norm_qwen3", "rope_qwen3", "swiglu_qwen3"]
     expected += ["decoder_layer_qwen3", "attention_qwen3"] if fused_layers else []
@@ -633,7 +639,7 @@ def main():
                                    "batch 1 fwd+bwd+AdamW, random init",
                        "global_batch_tokens": seq * world, "seq_len": seq,
                        "parallelism": parallelism,
-                       "attention": "torch SDPA", "activation_checkpointing": bool(args.grad_checkpoint), "fused_layers": fused_layers, "gemm_projections": args.gemm_projections if fused_layers else "off", "optimizer": (("bastile_b200.optim.AdamW" + (", updates overlapped with the backward pass" if overlap_opt else "")) if args.optimizer == "bastile" else "torch.optim.AdamW(fused=True)")
+                       "attention": "torch SDPA", "activation_checkpointing": bool(args.grad_checkpoint), "gemm_tiles": "dynamic" if dynamic_tiles else "fixed", "fused_layers": fused_layers, "gemm_projections": args.gemm_projections if fused_layers else "off", "optimizer": (("bastile_b200.optim.AdamW" + (", updates overlapped with the backward pass" if overlap_opt else "")) if args.optimizer == "bastile" else "torch.optim.AdamW(fused=True)")
                                     + ", bf16 params and state",
                        "l2": "each step streams ~65 GB of weights, gradients and optimizer state: far larger than the 126 MB L2"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": seq * 8, "d2h_bytes_per_step": 4,

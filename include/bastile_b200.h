@@ -244,6 +244,17 @@ int bt_qk_norm_rope_bwd(const void* dq_out, const void* dk_out, const void* q, c
                         const int64_t dq_strides[3], const int64_t dk_strides[3],
                         const int64_t cos_strides[2], int64_t cos_bs, int dtype, void* stream);
 
+/* How the CTA pairs of the tensor-core kernels get their output tiles: 0
+ * (default) = dealt round-robin at launch, 1 = drawn from a global counter while
+ * the kernel runs.  Dynamic hand-out is for a GPU whose SMs the GEMM has to
+ * share with another stream's long-running kernels (NCCL collectives under
+ * data-parallel training): a pair that gets its SMs late then finds few tiles
+ * left instead of its whole fixed share.  It costs one small memset per launch
+ * (the scheduler's words live in a fixed pool inside the library; nothing is
+ * allocated).  A negative argument only queries.  Returns the previous
+ * setting.  Process-wide.  No reference counterpart. */
+int bt_set_gemm_dynamic_tiles(int enable);
+
 /* ------------------------------------------------------ SwiGLU MLP (fused)  */
 
 /* Forward of CuTileSwiGLUMLP (src/bastile/ops/swiglu.py:170-187):

@@ -11,16 +11,40 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.fixture(params=[1, 0], ids=["cta_pairs", "single_cta"])
+@pytest.fixture(params=[(1, 0), (1, 1), (0, 0)], ids=["cta_pairs", "cta_pairs_dynamic_tiles", "single_cta"])
 def gemm_mode(request):
     """Run a test under both tilings of the tensor-core kernels (cta_group::2 pairs, the default,
-    and one CTA per tile)."""
+    and one CTA per tile), the pairs also with tiles drawn from a global counter."""
     from bastile_b200 import _lib
 
     lib = _lib.get_lib()
-    prev = lib.bt_set_gemm_cta_pairs(request.param)
+    pairs, dynamic = request.param
+    prev = lib.bt_set_gemm_cta_pairs(pairs), lib.bt_set_gemm_dynamic_tiles(dynamic)
     yield request.param
-    lib.bt_set_gemm_cta_pairs(prev)
+    lib.bt_set_gemm_cta_pairs(prev[0])
+    lib.bt_set_gemm_dynamic_tiles(prev[1])
+
+
+@pytest.mark.parametrize("M,N,K", [(2500, 5000, 64), (2500, 5000, 200), (4096, 6144, 1024), (20000, 300, 520)])
+def test_dynamic_tile_handout_gives_the_same_bits(M, N, K):
+    """More tiles than CTA pairs (so tiles really are drawn at run time), down to one k-block
+    per tile: every output element comes from the same arithmetic as with the fixed deal."""
+    from bastile_b200 import _lib
+
+    lib = _lib.get_lib()
+    torch.manual_seed(M + K)
+    A = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    B = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    prev = lib.bt_set_gemm_dynamic_tiles(0)
+    try:
+        fixed = _gemm(A, B, M, N, K, 1, 1)
+        lib.bt_set_gemm_dynamic_tiles(1)
+        for _ in range(3):
+            assert torch.equal(_gemm(A, B, M, N, K, 1, 1), fixed)
+    finally:
+        lib.bt_set_gemm_dynamic_tiles(prev)
+    ref = A[:64].double() @ B[:512].double().T
+    assert_close(fixed[:64, :512], ref.cpu().numpy(), what="D", rtol=2e-2, atol=2e-2 * max(1.0, np.sqrt(K) / 4))
 
 
 def _gemm(A, B, M, N, K, ak, bk, out_dtype=None, addend=None, alpha=None):

@@ -13,14 +13,16 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.fixture(params=[1, 0], ids=["cta_pairs", "single_cta"])
+@pytest.fixture(params=[(1, 0), (1, 1), (0, 0)], ids=["cta_pairs", "cta_pairs_dynamic_tiles", "single_cta"])
 def gemm_mode(request):
     from bastile_b200 import _lib
 
     lib = _lib.get_lib()
-    prev = lib.bt_set_gemm_cta_pairs(request.param)
+    pairs, dynamic = request.param
+    prev = lib.bt_set_gemm_cta_pairs(pairs), lib.bt_set_gemm_dynamic_tiles(dynamic)
     yield request.param
-    lib.bt_set_gemm_cta_pairs(prev)
+    lib.bt_set_gemm_cta_pairs(prev[0])
+    lib.bt_set_gemm_dynamic_tiles(prev[1])
 
 
 def _run(x, w, t, **kw):

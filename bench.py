@@ -10,9 +10,14 @@ with RMSNorm, RoPE, the SwiGLU MLP and the fused lm_head + cross-entropy running
 the bastile_b200 kernels and the optimizer step on bastile_b200.optim.AdamW (--optimizer torch
 selects torch.optim.AdamW as in the reference's own benchmark,
 tests/benchmarks/e2e/qwen_8b_seqlen.py:80-203); attention and the q/k/v/o projections are
-stock PyTorch.  With N > 1 (launched by torchrun,
+stock PyTorch.  By default the patch set is `apply(fused_layers=True)` (residual adds folded into
+the norm / down-projection kernels, q/k-norm + RoPE as one kernel; --no-fused-layers for exactly
+the reference's four patches) and, on one GPU, the optimizer updates each large parameter
+underneath the backward pass as soon as its gradient is complete (--no-overlap-optimizer).
+With N > 1 (launched by torchrun,
 one rank per GPU) every rank steps its own sequence and gradients are averaged by
-DistributedDataParallel over NCCL: weak scaling by tokens.
+DistributedDataParallel over NCCL: weak scaling by tokens; the GEMM then draws its tiles at
+run time (--tiles) because NCCL kernels share the SMs with the backward pass.
 
 Rank 0 prints ONE JSON line.  `value` is tokens/s with the step's inputs already on
 the device; `e2e` is the same loop fed from pinned host buffers with the loss read

@@ -121,3 +121,52 @@ def test_tiny_qwen3_fixture_is_reproducible():
     np.testing.assert_allclose(norms, g["param_norms"], rtol=1e-6)
     out = model(input_ids=ids, labels=labels)
     assert abs(out.loss.item() - float(g["loss"])) < 1e-5
+
+
+def test_fused_oracle_forms_match_hf_eager_autograd():
+    """The restatements of the fused forms (residual add + norm; q/k-norm + RoPE) against the HF
+    eager modules they stand for, forward and autograd backward, in fp32 on the CPU - the same
+    pin as for the four patched ops themselves."""
+    import transformers.models.qwen3.modeling_qwen3 as q3
+
+    torch.manual_seed(7)
+    # residual + x -> Qwen3RMSNorm, gradient arriving on both the norm output and the stream
+    m, n = 37, 256
+    x = torch.randn(m, n, requires_grad=True)
+    r = torch.randn(m, n, requires_grad=True)
+    norm = q3.Qwen3RMSNorm(n, eps=1e-6)
+    with torch.no_grad():
+        norm.weight.copy_(1 + 0.1 * torch.randn(n))
+    stream = r + x
+    y = norm(stream)
+    dy, ds = torch.randn(m, n), torch.randn(m, n)
+    torch.autograd.backward([y, stream], [dy, ds])
+    w = norm.weight.detach().numpy()
+    y_o, s_o, rstd = oracle.add_rms_norm_fwd(x.detach().numpy(), r.detach().numpy(), w, 1e-6)
+    dx_o, dw_o = oracle.add_rms_norm_bwd(dy.numpy(), ds.numpy(), s_o, w, rstd)
+    assert_close(torch.as_tensor(y_o), y.detach().numpy(), what="y", rtol=1e-5, atol=1e-5)
+    assert_close(torch.as_tensor(s_o), stream.detach().numpy(), what="stream", rtol=1e-6, atol=1e-6)
+    assert_close(torch.as_tensor(dx_o), x.grad.numpy(), what="dx", rtol=1e-4, atol=1e-5)
+    assert_close(torch.as_tensor(dx_o), r.grad.numpy(), what="dresidual", rtol=1e-4, atol=1e-5)
+    assert_close(torch.as_tensor(dw_o), norm.weight.grad.numpy(), what="dw", rtol=1e-4, atol=1e-4)
+
+    # q_norm / k_norm then apply_rotary_pos_emb, as Qwen3Attention.forward chains them
+    b, t, h, d = 2, 19, 3, 64
+    xq = torch.randn(b, t, h, d, requires_grad=True)
+    qn = q3.Qwen3RMSNorm(d, eps=1e-6)
+    with torch.no_grad():
+        qn.weight.copy_(1 + 0.1 * torch.randn(d))
+    inv = 1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    emb = torch.outer(torch.arange(t, dtype=torch.float32), inv)
+    emb = torch.cat((emb, emb), -1)
+    cos, sin = emb.cos()[None].expand(b, -1, -1), emb.sin()[None].expand(b, -1, -1)
+    q_rot, _ = q3.apply_rotary_pos_emb(qn(xq).transpose(1, 2), torch.zeros(b, 1, t, d), cos, sin)
+    dq = torch.randn(b, h, t, d)
+    q_rot.backward(dq)
+    wq = qn.weight.detach().numpy()
+    o_o, _ = oracle.head_norm_rope_fwd(xq.detach().numpy(), wq, cos.numpy(), sin.numpy(), 1e-6)
+    dx_o, dw_o = oracle.head_norm_rope_bwd(dq.transpose(1, 2).numpy(), xq.detach().numpy(), wq, cos.numpy(),
+                                           sin.numpy(), 1e-6)
+    assert_close(torch.as_tensor(o_o), q_rot.detach().transpose(1, 2).numpy(), what="q rotated", rtol=1e-5, atol=1e-5)
+    assert_close(torch.as_tensor(dx_o), xq.grad.numpy(), what="dq", rtol=1e-4, atol=1e-5)
+    assert_close(torch.as_tensor(dw_o), qn.weight.grad.numpy(), what="dw", rtol=1e-4, atol=1e-4)

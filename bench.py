@@ -24,7 +24,7 @@ the device; `e2e` is the same loop fed from pinned host buffers with the loss re
 back every step.  `roofline` describes the dominant kernel (the tcgen05 GEMM that
 runs the MLP block) from CUDA events recorded around its launches inside the timed
 steps.  `per_op` holds the forward+backward micro-benchmarks of the four ops at the
-BASELINE shapes.  `cpu_baseline` (N = 1 only) times HF eager on the host cores on a
+per-op benchmark shapes.  `cpu_baseline` (N = 1 only) times HF eager on the host cores on a
 bounded sample.  `--impl reference` prints that CPU measurement as its own line.
 """
 
@@ -266,7 +266,7 @@ def _tensor(ms, flops, peaks):
 
 
 def per_op_bench(peaks, only=None, iters=None):
-    """Forward+backward of each op at the BASELINE per-op shapes (bf16, seed 1), called through
+    """Forward+backward of each op at the per-op benchmark shapes (bf16, seed 1), called through
     the public ops; the time is that of the kernels (events around the library calls)."""
     import torch
 

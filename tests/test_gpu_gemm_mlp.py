@@ -244,7 +244,7 @@ def test_mlp_module_matches_hf_eager_module():
 
 
 def test_mlp_full_size_linearity_and_sampled_rows():
-    """BASELINE shape x[8192,4096], intermediate 12288: sampled rows vs the oracle, and the
+    """Benchmark shape x[8192,4096], intermediate 12288: sampled rows vs the oracle, and the
     backward's linearity in the upstream gradient."""
     from bastile_b200.ops.swiglu import SwiGLUMLPFunction
 

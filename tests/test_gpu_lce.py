@@ -252,7 +252,7 @@ def test_lce_vocab_shards_emulated_on_one_gpu():
 
 
 def test_lce_full_size_properties():
-    """BASELINE shape hidden[16384,4096] x W[151936,4096], 5 % ignored: loss near ln(V) for
+    """Benchmark shape hidden[16384,4096] x W[151936,4096], 5 % ignored: loss near ln(V) for
     small weights, sampled-row loss and dx against the oracle, zero gradient on ignored rows,
     rows of dW for unused vocabulary entries all <= 0 scaled softmax mass."""
     torch.manual_seed(2)

@@ -110,7 +110,7 @@ def test_rmsnorm_bwd_scratch_is_left_zero_and_reusable():
 
 
 def test_rmsnorm_full_size_properties():
-    """BASELINE per-op shape x[8192,4096] bf16: scale equivariance and unit RMS of y/w."""
+    """Per-op benchmark shape x[8192,4096] bf16: scale equivariance and unit RMS of y/w."""
     from bastile_b200.ops.rms_norm import rms_norm
 
     torch.manual_seed(1)
@@ -200,7 +200,7 @@ def test_rope_reference_unit_tests():
 
 
 def test_rope_full_size_roundtrip():
-    """BASELINE shape q[1,32,8192,128], k[1,8,8192,128]: norm preservation and fwd->bwd round trip."""
+    """Benchmark shape q[1,32,8192,128], k[1,8,8192,128]: norm preservation and fwd->bwd round trip."""
     from bastile_b200 import _lib
     from bastile_b200.ops.rope import _launch
 

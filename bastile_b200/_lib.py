@@ -73,10 +73,13 @@ SIGNATURES = {
     "bt_lce_num_vtiles": (c_int64, [c_int64]),
     "bt_lce_row_stats": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "bt_lce_dlogits": (c_int, [c_void_p] * 5 + [c_int64] * 5 + [c_int, c_int, c_void_p]),
-    "bt_lce_count_valid": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
+    "bt_lce_count_valid": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p,
+                                   c_void_p]),
     "bt_lce_reduce_loss": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "bt_adamw_step": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_float,
                               c_float, c_float, c_int64, c_int, c_int, c_void_p]),
+    "bt_adamw_master_step": (c_int, [c_void_p] * 5 + [c_int64] + [c_float] * 5 + [c_int64, c_float, c_int, c_int,
+                                     c_void_p]),
     "bt_scale_cast": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]),
 }
 
@@ -234,29 +237,56 @@ class timed:
         return False
 
 
+STATUS_WAIT_MASK, STATUS_BAD_LABEL = 0x0F, 0x10  # BT_STATUS_* of include/bastile_b200.h
+
+
+def _describe_status(v: int) -> str:
+    parts = []
+    if v & STATUS_WAIT_MASK:
+        parts.append(f"a bounded device-side wait ran out (bits {v & STATUS_WAIT_MASK:#x}): results are invalid")
+    if v & STATUS_BAD_LABEL:
+        parts.append("fused_linear_cross_entropy got a label that is neither ignore_index nor a vocabulary row")
+    return "; ".join(parts) or f"status {v:#x}"
+
+
+def _reset_zero_workspaces() -> None:
+    """A kernel that gave up may have left its 'zero on entry, zero on exit' scratch dirty."""
+    for buf in _zero_ws.values():
+        buf.zero_()
+
+
 def check_status(dev: torch.device, what: str) -> None:
-    """Synchronising read of the device status word (tests / debugging only)."""
+    """Synchronising read of the current stream's status word on ``dev``; raises if it is set."""
     st = status_word(dev)
     v = int(st.item())
     if v != 0:
         st.zero_()
-        raise BastileB200Error(f"{what}: a bounded device-side wait ran out (status {v:#x})")
+        if v & STATUS_WAIT_MASK:
+            _reset_zero_workspaces()
+        raise BastileB200Error(f"{what}: {_describe_status(v)}")
 
 
 def check_all_status() -> None:
-    """Synchronising check of every status word the ops have handed to the tensor-core kernels and
-    of the bulk-copy wait flag of the RMSNorm kernels; raises if a bounded device-side wait ever
-    ran out (the results of that call were invalid).  The ops never call this themselves - they
-    do not synchronise - so a training loop can call it at a point where it syncs anyway."""
-    bad = []
+    """Synchronising check of every status word the ops have handed to the kernels and of the
+    bulk-copy wait flag of the RMSNorm kernels.  Raises if a bounded device-side wait ever ran out
+    (the results of that call were invalid) or a loss call saw an out-of-range label; after a wait
+    error every cached zero-scratch buffer is cleared again, so that later calls start from the
+    state they expect.  The ops never call this themselves - they do not synchronise - so a
+    training loop calls it where it syncs anyway (``AdamW(check_device_status=True)`` does it at
+    the end of ``step()``; reading the loss with ``.item()`` is another natural place)."""
+    bad, waits = [], False
     for (dev_idx, _stream), word in _status.items():
         v = int(word.item())
         if v:
             word.zero_()
-            bad.append(f"cuda:{dev_idx} GEMM status {v:#x}")
+            waits |= bool(v & STATUS_WAIT_MASK)
+            bad.append(f"cuda:{dev_idx}: {_describe_status(v)}")
     if _lib is not None and torch.cuda.is_available():
         v = int(_lib.bt_device_wait_errors())
         if v:
+            waits = True
             bad.append(f"RMSNorm bulk-copy wait flag {v:#x}")
+    if waits:
+        _reset_zero_workspaces()
     if bad:
-        raise BastileB200Error("a bounded device-side wait ran out: " + "; ".join(bad))
+        raise BastileB200Error("; ".join(bad))

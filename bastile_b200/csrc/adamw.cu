@@ -134,6 +134,96 @@ int many_t(const Table& t, int64_t max_n, const Hyper& h, cudaStream_t s) {
   return BT_OK;
 }
 
+// ---- fp32 master weights --------------------------------------------------------------
+// The optimizer state (master parameter, both moments) is fp32; the gradient arrives in the
+// model's 16-bit (or fp32) type T and the updated parameter is also written back in T for the
+// next forward pass.  Per element: 3 fp32 reads + 1 T read, 3 fp32 writes + 1 T write.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+adamw_master(float* __restrict__ p32, float* __restrict__ m, float* __restrict__ v,
+             const T* __restrict__ g, T* __restrict__ p_out, int64_t n, int vec_ok, float gscale,
+             Hyper h) {
+  constexpr int E = Cvt<T>::N;   // elements per 16-byte vector of T
+  constexpr int Q = E / 4;       // float4 vectors of fp32 state per vector of T
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  const int64_t nvec = vec_ok ? n / E : 0;
+  const float decay = 1.0f - h.lr * h.wd;
+  const float step = h.lr * h.inv_bc1;
+  for (int64_t i = tid; i < nvec; i += stride) {
+    const int64_t off = i * E;
+    uint4 pr[Q], mr[Q], vr[Q];
+    const uint4 gr = ld_stream_v4(g + off);
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+      pr[q] = ld_stream_v4(p32 + off + 4 * q);
+      mr[q] = ld_stream_v4(m + off + 4 * q);
+      vr[q] = ld_stream_v4(v + off + 4 * q);
+    }
+    float gf[E], out[E];
+    Cvt<T>::unpack(gr, gf);
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+      float pf[4], mf[4], vf[4];
+      Cvt<float>::unpack(pr[q], pf);
+      Cvt<float>::unpack(mr[q], mf);
+      Cvt<float>::unpack(vr[q], vf);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float ge = gf[4 * q + e] * gscale;
+        mf[e] = h.beta1 * mf[e] + (1.0f - h.beta1) * ge;
+        vf[e] = h.beta2 * vf[e] + (1.0f - h.beta2) * ge * ge;
+        const float denom = sqrtf(vf[e]) * h.inv_sqrt_bc2 + h.eps;
+        pf[e] = pf[e] * decay - step * (mf[e] / denom);
+        out[4 * q + e] = pf[e];
+      }
+      st_global_v4(p32 + off + 4 * q, Cvt<float>::pack(pf));
+      st_global_v4(m + off + 4 * q, Cvt<float>::pack(mf));
+      st_global_v4(v + off + 4 * q, Cvt<float>::pack(vf));
+    }
+    st_global_v4(p_out + off, Cvt<T>::pack(out));
+  }
+  for (int64_t i = nvec * E + tid; i < n; i += stride) {
+    const float ge = Cvt<T>::to_f(g[i]) * gscale;
+    const float mf = h.beta1 * m[i] + (1.0f - h.beta1) * ge;
+    const float vf = h.beta2 * v[i] + (1.0f - h.beta2) * ge * ge;
+    const float denom = sqrtf(vf) * h.inv_sqrt_bc2 + h.eps;
+    const float pf = p32[i] * decay - step * (mf / denom);
+    p32[i] = pf;
+    m[i] = mf;
+    v[i] = vf;
+    p_out[i] = Cvt<T>::from_f(pf);
+  }
+}
+
+template <typename T>
+int master_t(float* p32, float* m, float* v, const void* g, void* p_out, int64_t n, float gscale,
+             const Hyper& h, int ctas_per_sm, cudaStream_t s) {
+  constexpr int E = Cvt<T>::N;
+  const int vec_ok = aligned16(p32) && aligned16(m) && aligned16(v) && aligned16(g) && aligned16(p_out);
+  const int64_t work = vec_ok ? ceil_div(n, E) : n;
+  const int64_t blocks = ceil_div(work, kThreads);
+  const int64_t cap = static_cast<int64_t>(sm_count()) * ctas_per_sm;
+  adamw_master<T><<<static_cast<unsigned>(blocks < 1 ? 1 : (blocks < cap ? blocks : cap)), kThreads,
+                    0, s>>>(p32, m, v, static_cast<const T*>(g), static_cast<T*>(p_out), n, vec_ok,
+                            gscale, h);
+  BT_CHECK_LAUNCH("adamw_master");
+  return BT_OK;
+}
+
+Hyper make_hyper(float lr, float beta1, float beta2, float eps, float weight_decay, int64_t step) {
+  Hyper h;
+  h.lr = lr;
+  h.beta1 = beta1;
+  h.beta2 = beta2;
+  h.eps = eps;
+  h.wd = weight_decay;
+  h.inv_bc1 = static_cast<float>(1.0 / (1.0 - pow(static_cast<double>(beta1), static_cast<double>(step))));
+  h.inv_sqrt_bc2 =
+      static_cast<float>(1.0 / sqrt(1.0 - pow(static_cast<double>(beta2), static_cast<double>(step))));
+  return h;
+}
+
 }  // namespace
 }  // namespace bt
 
@@ -149,15 +239,7 @@ extern "C" int bt_adamw_step(void* const* params, const void* const* grads, void
                "adamw_step: null table");
   BT_CHECK_ARG(dtype == BT_BF16 || dtype == BT_FP16 || dtype == BT_FP32, "adamw_step: unknown dtype %d",
                dtype);
-  Hyper h;
-  h.lr = lr;
-  h.beta1 = beta1;
-  h.beta2 = beta2;
-  h.eps = eps;
-  h.wd = weight_decay;
-  h.inv_bc1 = static_cast<float>(1.0 / (1.0 - pow(static_cast<double>(beta1), static_cast<double>(step))));
-  h.inv_sqrt_bc2 =
-      static_cast<float>(1.0 / sqrt(1.0 - pow(static_cast<double>(beta2), static_cast<double>(step))));
+  const Hyper h = make_hyper(lr, beta1, beta2, eps, weight_decay, step);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   constexpr int64_t kSmall = 1 << 16;  // tensors up to 64 Ki elements are batched
   Table t;
@@ -200,4 +282,28 @@ extern "C" int bt_adamw_step(void* const* params, const void* const* grads, void
     if (rc) return rc;
   }
   return flush();
+}
+
+extern "C" int bt_adamw_master_step(float* master, float* exp_avg, float* exp_avg_sq, const void* grad,
+                                    void* param_out, int64_t numel, float lr, float beta1, float beta2,
+                                    float eps, float weight_decay, int64_t step, float grad_scale,
+                                    int ctas_per_sm, int dtype, void* stream) {
+  using namespace bt;
+  BT_CHECK_ARG(numel >= 0 && step >= 1, "adamw_master_step: bad element count or step");
+  BT_CHECK_ARG(ctas_per_sm >= 0 && ctas_per_sm <= 32, "adamw_master_step: ctas_per_sm must be 0..32");
+  if (ctas_per_sm == 0) ctas_per_sm = 16;
+  BT_CHECK_ARG(dtype == BT_BF16 || dtype == BT_FP16 || dtype == BT_FP32,
+               "adamw_master_step: unknown dtype %d", dtype);
+  if (numel == 0) return BT_OK;
+  BT_CHECK_ARG(master && exp_avg && exp_avg_sq && grad && param_out, "adamw_master_step: null pointer");
+  const Hyper h = make_hyper(lr, beta1, beta2, eps, weight_decay, step);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case BT_BF16:
+      return master_t<__nv_bfloat16>(master, exp_avg, exp_avg_sq, grad, param_out, numel, grad_scale, h, ctas_per_sm, s);
+    case BT_FP16:
+      return master_t<__half>(master, exp_avg, exp_avg_sq, grad, param_out, numel, grad_scale, h, ctas_per_sm, s);
+    default:
+      return master_t<float>(master, exp_avg, exp_avg_sq, grad, param_out, numel, grad_scale, h, ctas_per_sm, s);
+  }
 }

@@ -90,10 +90,19 @@ lce_dlogits_kernel(T* __restrict__ logits, const float* __restrict__ row_stats,
 
 __global__ void __launch_bounds__(kThreads)
 lce_count_valid_kernel(const int64_t* __restrict__ labels, int64_t n, int64_t ignore_index,
-                       int mean, float* __restrict__ n_valid, float* __restrict__ grad_scale) {
+                       int mean, float* __restrict__ n_valid, float* __restrict__ grad_scale,
+                       int64_t vocab, int32_t* __restrict__ status) {
   __shared__ unsigned long long s_cnt[kThreads / 32];
   unsigned long long c = 0;
-  for (int64_t i = threadIdx.x; i < n; i += kThreads) c += (labels[i] != ignore_index) ? 1ull : 0ull;
+  bool bad = false;
+  for (int64_t i = threadIdx.x; i < n; i += kThreads) {
+    const int64_t l = labels[i];
+    c += (l != ignore_index) ? 1ull : 0ull;
+    bad |= (l != ignore_index) && (l < 0 || l >= vocab);
+  }
+  // a label that is neither ignore_index nor a vocabulary row (F.cross_entropy asserts on it)
+  if (vocab > 0 && status != nullptr && __syncthreads_or(bad) && threadIdx.x == 0)
+    atomicOr(status, BT_STATUS_BAD_LABEL);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
   if ((threadIdx.x & 31) == 0) s_cnt[threadIdx.x >> 5] = c;
@@ -240,11 +249,12 @@ extern "C" int bt_lce_dlogits(void* logits, const float* row_stats, const int64_
 }
 
 extern "C" int bt_lce_count_valid(const int64_t* labels, int64_t n, int64_t ignore_index, int mean,
-                                  float* n_valid, float* grad_scale, void* stream) {
+                                  float* n_valid, float* grad_scale, int64_t vocab_size, int32_t* status,
+                                  void* stream) {
   using namespace bt;
   BT_CHECK_ARG(n >= 0 && n_valid && grad_scale && (n == 0 || labels), "lce_count_valid: bad args");
   lce_count_valid_kernel<<<1, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      labels, n, ignore_index, mean, n_valid, grad_scale);
+      labels, n, ignore_index, mean, n_valid, grad_scale, vocab_size, status);
   BT_CHECK_LAUNCH("lce_count_valid");
   return BT_OK;
 }

@@ -58,7 +58,7 @@ def merge_shard_stats(gathered: Tensor) -> Tensor:
 class LinearCrossEntropyFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, target, ignore_index, reduction, chunk_size, v_chunk_size,
-                group=None, vocab_start=0, shard_tokens=False, grad_hidden_scale=1.0):
+                group=None, vocab_start=0, shard_tokens=False, grad_hidden_scale=1.0, vocab_size=None):
         dev = _lib.require_cuda(x, weight, target)
         lib = _lib.get_lib()
         if x.dtype not in _GEMM_DTYPES:
@@ -125,8 +125,10 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
 
         n_k = 2 + 5 * n_chunks - (1 if n_chunks else 0)
         with _lib.device_of(dev), _lib.timed("lce_fwd", n_k, dev):
+            v_total = vloc if group is None else int(vocab_size or 0)  # 0: bound unknown, labels unchecked
             _lib.check(lib.bt_lce_count_valid(labels.data_ptr(), bt, ignore_index, 1 if reduction == "mean" else 0,
-                                              scal[0:].data_ptr(), scal[1:].data_ptr(), stream), "bt_lce_count_valid")
+                                              scal[0:].data_ptr(), scal[1:].data_ptr(), v_total, st.data_ptr(),
+                                              stream), "bt_lce_count_valid")
             last_rows = 0
             x_last = None
             for i in range(n_chunks):
@@ -209,7 +211,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
                                            st.data_ptr(), stream), "bt_gemm(dW last)")
                 if dw_out.dtype != w_dtype:
                     dw_out = dw_out.to(w_dtype)
-        return dx_out, dw_out, None, None, None, None, None, None, None, None, None
+        return dx_out, dw_out, None, None, None, None, None, None, None, None, None, None
 
 
 ChunkedLinearCrossEntropyFunction = LinearCrossEntropyFunction
@@ -219,7 +221,7 @@ def fused_linear_cross_entropy(hidden_states: Tensor, weight: Tensor, target: Te
                                ignore_index: int = -100, chunk_size: int = 4096, reduction: str = "mean",
                                v_chunk_size: int | None = None, vocab_parallel_group=None,
                                vocab_start: int = 0, shard_tokens: bool = False,
-                               grad_hidden_scale: float = 1.0) -> Tensor:
+                               grad_hidden_scale: float = 1.0, vocab_size: int | None = None) -> Tensor:
     """Loss of ``cross_entropy(hidden_states @ weight.T, target)`` without ever holding
     ``[tokens, vocab]`` logits; same arguments as the reference (:405-438).
 
@@ -232,6 +234,12 @@ def fused_linear_cross_entropy(hidden_states: Tensor, weight: Tensor, target: Te
     tokens, and each rank gets the gradient of its own rows back (reduce-scatter), multiplied
     by ``grad_hidden_scale`` (set it to the world size under data-parallel wrappers that
     average gradients over ranks).
+
+    A label that is neither ``ignore_index`` nor a vocabulary row (``F.cross_entropy``, which the
+    reference calls at :127 and :427, asserts on it) does not stop the call - nothing here waits
+    for the device - but sets ``BT_STATUS_BAD_LABEL`` in the stream's status word, which
+    ``bastile_b200._lib.check_all_status()`` turns into an exception.  With a vocabulary-parallel
+    group pass ``vocab_size`` (rows of the full ``lm_head``) to have labels checked.
     """
     if hidden_states.ndim == 3:
         hidden_states = hidden_states.reshape(-1, hidden_states.shape[-1])
@@ -243,17 +251,19 @@ def fused_linear_cross_entropy(hidden_states: Tensor, weight: Tensor, target: Te
         return F.cross_entropy(logits, target, ignore_index=ignore_index, reduction=reduction)
     return LinearCrossEntropyFunction.apply(hidden_states, weight, target, ignore_index, reduction, chunk_size,
                                             v_chunk_size, vocab_parallel_group, vocab_start, shard_tokens,
-                                            grad_hidden_scale)
+                                            grad_hidden_scale, vocab_size)
 
 
 # Set by set_vocab_parallel(): the model forward then treats ``lm_head.weight`` as this rank's
 # slice of vocabulary rows and the ranks' tokens as shards of one batch.
-_VOCAB_PARALLEL = {"group": None, "vocab_start": 0, "grad_hidden_scale": 1.0}
+_VOCAB_PARALLEL = {"group": None, "vocab_start": 0, "grad_hidden_scale": 1.0, "vocab_size": None}
 
 
-def set_vocab_parallel(group, vocab_start: int = 0, grad_hidden_scale: float = 1.0) -> None:
+def set_vocab_parallel(group, vocab_start: int = 0, grad_hidden_scale: float = 1.0,
+                       vocab_size: int | None = None) -> None:
     """Switch ``bastile_lce_forward`` to the vocabulary-parallel loss (``group=None`` switches back)."""
-    _VOCAB_PARALLEL.update(group=group, vocab_start=int(vocab_start), grad_hidden_scale=float(grad_hidden_scale))
+    _VOCAB_PARALLEL.update(group=group, vocab_start=int(vocab_start), grad_hidden_scale=float(grad_hidden_scale),
+                           vocab_size=vocab_size)
 
 
 def bastile_lce_forward(self, input_ids=None, attention_mask=None, position_ids=None, past_key_values=None,
@@ -294,7 +304,8 @@ def bastile_lce_forward(self, input_ids=None, attention_mask=None, position_ids=
         else:
             loss = fused_linear_cross_entropy(shift_hidden, self.lm_head.weight, shift_labels, ignore_index=-100,
                                               vocab_parallel_group=vp["group"], vocab_start=vp["vocab_start"],
-                                              shard_tokens=True, grad_hidden_scale=vp["grad_hidden_scale"])
+                                              shard_tokens=True, grad_hidden_scale=vp["grad_hidden_scale"],
+                                              vocab_size=vp["vocab_size"])
     else:
         keep = slice(-logits_to_keep, None) if isinstance(logits_to_keep, int) else logits_to_keep
         logits = self.lm_head(hidden_states[:, keep, :])

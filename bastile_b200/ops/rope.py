@@ -7,6 +7,15 @@ backward is the same kernel with ``sin`` negated inside the kernel, reading the
 incoming gradients with their own strides and writing fresh tensors - no
 ``-sin`` tensor and no ``.contiguous()`` copies (rope.py:132-136 made both).
 Only the first ``D/2`` columns of ``cos``/``sin`` are read (rope.py:100-105).
+
+Like the reference, the forward does NOT call ``ctx.mark_dirty(q, k)``.  It cannot: HF hands
+over transposed VIEWS (``q_norm(...).transpose(1, 2)``), and torch refuses a Function that
+modifies a view input in place and returns more than one tensor ("your Function cannot return
+more than one Tensor"; tests/test_patch_engine.py keeps a stand-in of that shape to notice if
+torch ever lifts the rule).  The consequence is the reference's: whatever produced ``q`` / ``k``
+must not need its own OUTPUT in its backward - true for ``Qwen3RMSNorm`` here and there, which
+saves its input.  ``apply(fused_layers=True)`` replaces the pair q/k-norm + RoPE by one
+out-of-place kernel and has no such caveat.
 """
 
 from __future__ import annotations

@@ -35,6 +35,13 @@ extern "C" {
 #define BT_ERR_DRIVER (-4)   /* tensor-map encode / driver entry point failure   */
 #define BT_ERR_LIMIT (-5)    /* size beyond a stated maximum                     */
 
+/* Bits of the caller-owned int32 device status word that several entry points take.  The
+ * low four are set by the tensor-core kernels when a bounded barrier wait runs out (producer,
+ * MMA issuer waiting for an accumulator / for operands, epilogue): the results of that launch
+ * are invalid.  BT_STATUS_BAD_LABEL reports invalid INPUT, not a device problem. */
+#define BT_STATUS_WAIT_MASK 0x0f
+#define BT_STATUS_BAD_LABEL 0x10
+
 /* Library version (major*10000 + minor*100 + patch). No reference counterpart
  * (the reference is a JIT Python package: src/bastile/__init__.py:23). */
 int bt_version(void);
@@ -326,9 +333,15 @@ int bt_lce_dlogits(void* logits, const float* row_stats, const int64_t* labels,
 /* Counts labels != ignore_index into n_valid[0] (fp32) and writes
  * grad_scale[0] = mean ? (n_valid > 0 ? 1/n_valid : 0) : 1 without a host
  * round trip (replaces the .item() sync of
- * src/bastile/ops/fused_linear_cross_entropy.py:334-343). */
+ * src/bastile/ops/fused_linear_cross_entropy.py:334-343).  With vocab_size > 0 and a status
+ * word, a label that is neither ignore_index nor inside [0, vocab_size) sets
+ * BT_STATUS_BAD_LABEL in *status: the reference computes its loss with F.cross_entropy
+ * (:127, :427), which asserts on such a label; here the row would silently count as valid with
+ * no target term, so the caller is told instead (vocab_size is the FULL vocabulary when the
+ * rows of lm_head are sharded over ranks). */
 int bt_lce_count_valid(const int64_t* labels, int64_t n, int64_t ignore_index,
-                       int mean, float* n_valid, float* grad_scale, void* stream);
+                       int mean, float* n_valid, float* grad_scale,
+                       int64_t vocab_size, int32_t* status, void* stream);
 
 /* loss[0] = sum(loss_row[0:n]) * (mean ? grad_scale[0] : 1)  (:333, 367). */
 int bt_lce_reduce_loss(const float* loss_row, int64_t n, const float* grad_scale,
@@ -359,6 +372,19 @@ int bt_adamw_step(void* const* params, const void* const* grads,
                   const int64_t* numel, int n_tensors,
                   float lr, float beta1, float beta2, float eps, float weight_decay,
                   int64_t step, int ctas_per_sm, int dtype, void* stream);
+
+/* The same step with fp32 MASTER weights, for one flat tensor: `master`, `exp_avg` and
+ * `exp_avg_sq` are fp32 arrays of `numel` elements, `grad` holds the gradient in the model's
+ * storage type `dtype`, and the updated parameter is written to `param_out` in that type for
+ * the next forward pass ("bf16 parameters / fp32 master" of the reference's FSDP recipe,
+ * tests/benchmarks/e2e/qwen_8b_fsdp.py:148-168, where FSDP mixed precision keeps fp32 shards
+ * and hands bf16 copies to the layers).  The gradient is multiplied by `grad_scale` first
+ * (1 / world size after a summing reduce-scatter, a clipping coefficient, ...).  A rank of
+ * a sharded data-parallel job calls this on its slice of a flat bucket. */
+int bt_adamw_master_step(float* master, float* exp_avg, float* exp_avg_sq,
+                         const void* grad, void* param_out, int64_t numel,
+                         float lr, float beta1, float beta2, float eps, float weight_decay,
+                         int64_t step, float grad_scale, int ctas_per_sm, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

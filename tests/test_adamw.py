@@ -98,3 +98,96 @@ def test_overlap_backward_is_inert_without_cuda_gradients():
     assert not opt._early and not opt._side_streams
     with pytest.raises(RuntimeError):
         opt.step()
+
+
+@pytest.mark.gpu
+def test_overlap_backward_with_tied_weights_matches_plain_step_bit_for_bit():
+    """A weight used twice in the graph (tied embedding / output projection): autograd sums both
+    contributions before the single accumulation that fires the hook, so the early update sees the
+    complete gradient."""
+    from bastile_b200.optim import _OVERLAP_MIN_NUMEL, AdamW
+
+    class Tied(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            torch.manual_seed(5)
+            self.emb = torch.nn.Embedding(2048, 1024)
+            self.mid = torch.nn.Linear(1024, 1024, bias=False)
+
+        def forward(self, ids):
+            return torch.nn.functional.linear(torch.tanh(self.mid(self.emb(ids))), self.emb.weight)
+
+    nets = [Tied().cuda().to(torch.bfloat16), Tied().cuda().to(torch.bfloat16)]
+    assert nets[0].emb.weight.numel() >= _OVERLAP_MIN_NUMEL
+    hp = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    opts = [AdamW(nets[0].parameters(), **hp), AdamW(nets[1].parameters(), overlap_backward=True, **hp)]
+    torch.manual_seed(6)
+    for _ in range(3):
+        ids = torch.randint(0, 2048, (4, 64), device="cuda")
+        for net, opt in zip(nets, opts):
+            opt.zero_grad(set_to_none=True)
+            torch.nn.functional.cross_entropy(net(ids).float().view(-1, 2048), ids.view(-1)).backward()
+            opt.step()
+    torch.cuda.synchronize()
+    for (name, a), b in zip(nets[0].named_parameters(), nets[1].parameters()):
+        assert torch.equal(a, b), name
+    # a second backward pass before step() is refused, not silently half-applied
+    ids = torch.randint(0, 2048, (4, 64), device="cuda")
+    opts[1].zero_grad(set_to_none=True)
+    torch.nn.functional.cross_entropy(nets[1](ids).float().view(-1, 2048), ids.view(-1)).backward()
+    with pytest.raises(RuntimeError):
+        torch.nn.functional.cross_entropy(nets[1](ids).float().view(-1, 2048), ids.view(-1)).backward()
+    opts[1].step()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [1 << 20, 4099, 7])
+def test_cuda_adamw_master_weights_match_oracle(n):
+    """bf16 parameter / gradient, fp32 master and moments (bt_adamw_master_step) against the float64 oracle."""
+    from bastile_b200.optim import AdamW
+
+    torch.manual_seed(8)
+    p = torch.randn(n, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    hp = dict(lr=3e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.05)
+    opt = AdamW([p], master_weights=True, **hp)
+    pn, m, v = p.detach().double().cpu().numpy(), np.zeros(n), np.zeros(n)
+    for step in range(1, 5):
+        g = torch.randn(n, device="cuda").to(torch.bfloat16)
+        p.grad = g.clone()
+        opt.step()
+        pn, m, v = oracle.adamw_step(pn, g.double().cpu().numpy(), m, v, step, hp["lr"], 0.9, 0.95, 1e-8, 0.05)
+    st = opt.state[p]
+    assert set(st) == {"step", "exp_avg", "exp_avg_sq", "master"} and st["master"].dtype == torch.float32
+    assert_close(st["master"], pn, what="master", rtol=1e-5, atol=1e-6)
+    assert_close(st["exp_avg"], m, what="m", rtol=1e-5, atol=1e-7)
+    assert_close(st["exp_avg_sq"], v, what="v", rtol=1e-5, atol=1e-7)
+    assert torch.equal(p.detach(), st["master"].to(torch.bfloat16))  # the 16-bit copy is the rounded master
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("master", [False, True])
+def test_sharded_adamw_single_rank_matches_plain_adamw(master):
+    """One rank: ShardedAdamW is a flat, overlapped AdamW - same bits as AdamW on the same model."""
+    from bastile_b200.optim import AdamW, ShardedAdamW
+
+    def build():
+        torch.manual_seed(9)
+        return torch.nn.Sequential(torch.nn.Linear(1024, 2048, bias=True), torch.nn.GELU(),
+                                   torch.nn.Linear(2048, 1024, bias=False), torch.nn.LayerNorm(1024),
+                                   torch.nn.Linear(1024, 512, bias=False)).cuda().to(torch.bfloat16)
+
+    nets = [build(), build()]
+    hp = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    opts = [AdamW(nets[0].parameters(), master_weights=master, **hp),
+            ShardedAdamW(nets[1].parameters(), bucket_mb=4, master_weights=master, **hp)]
+    assert len(opts[1].buckets) >= 2
+    torch.manual_seed(10)
+    for _ in range(4):
+        x = torch.randn(256, 1024, device="cuda", dtype=torch.bfloat16)
+        for net, opt in zip(nets, opts):
+            opt.zero_grad(set_to_none=True)
+            net(x).float().pow(2).mean().backward()
+            opt.step()
+    torch.cuda.synchronize()
+    for (name, a), b in zip(nets[0].named_parameters(), nets[1].parameters()):
+        assert torch.equal(a, b), name

@@ -207,7 +207,7 @@ def test_lce_vocab_shards_emulated_on_one_gpu():
     ld = (vs + 7) // 8 * 8
     n_vt = int(lib.bt_lce_num_vtiles(vs))
     scal = torch.empty(3, device=DEV)
-    _lib.check(lib.bt_lce_count_valid(t.data_ptr(), bt, -100, 1, scal[0:].data_ptr(), scal[1:].data_ptr(), stream), "cv")
+    _lib.check(lib.bt_lce_count_valid(t.data_ptr(), bt, -100, 1, scal[0:].data_ptr(), scal[1:].data_ptr(), v, st.data_ptr(), stream), "cv")
     logits, stats = [], []
     for r in range(n):
         lg = torch.empty(bt, ld, device=DEV, dtype=torch.bfloat16)
@@ -285,3 +285,27 @@ def test_lce_full_size_properties():
     # gradient of the weight sums to ~0 over the vocabulary for every hidden unit (softmax - onehot sums to 0)
     col_sum = dw.float().sum(0)
     assert float(col_sum.abs().max()) < 5e-2
+
+
+def test_lce_out_of_range_label_sets_status_bit():
+    """A label >= V (or negative and not ignore_index) makes F.cross_entropy - which the reference
+    calls for its loss (:127, :427) - assert on the device.  Here the call completes without waiting
+    for the device and the stream's status word carries BT_STATUS_BAD_LABEL, which
+    check_all_status() raises on; clean labels leave the word untouched."""
+    from bastile_b200 import _lib
+    from bastile_b200.ops.fused_linear_cross_entropy import fused_linear_cross_entropy
+
+    torch.manual_seed(12)
+    x = torch.randn(64, 128, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(512, 128, device=DEV) * 0.05).to(torch.bfloat16)
+    t = torch.randint(0, 512, (64,), device=DEV)
+    t[3] = -100
+    fused_linear_cross_entropy(x, w, t)
+    _lib.check_all_status()  # nothing set
+    for bad in (512, -7):
+        t2 = t.clone()
+        t2[5] = bad
+        fused_linear_cross_entropy(x, w, t2)
+        with pytest.raises(_lib.BastileB200Error, match="label"):
+            _lib.check_all_status()
+        _lib.check_all_status()  # the word was cleared by the failed check

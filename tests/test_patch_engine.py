@@ -189,3 +189,30 @@ def test_fused_forwards_fall_back_to_plain_modules_on_cpu(qwen3):
     finally:
         bastile.reset()
     assert torch.equal(got, want)
+
+
+def test_two_output_inplace_function_on_views_cannot_mark_dirty():
+    """Why RoPEFunction mutates q and k without ``ctx.mark_dirty`` (as the reference does,
+    src/bastile/ops/rope.py:125-130): HF passes transposed views, and torch rejects a Function
+    that modifies view inputs in place and returns two tensors.  If this ever stops raising,
+    RoPEFunction can mark its inputs dirty."""
+    import torch
+
+    class TwoInPlace(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, q, k):
+            q.mul_(2.0)
+            k.mul_(2.0)
+            ctx.mark_dirty(q, k)
+            return q, k
+
+        @staticmethod
+        def backward(ctx, dq, dk):
+            return dq * 2.0, dk * 2.0
+
+    lin = torch.nn.Linear(8, 16)
+    h = torch.randn(1, 4, 8)
+    q = lin(h).view(1, 4, 2, 8).transpose(1, 2)
+    k = lin(h).view(1, 4, 2, 8).transpose(1, 2)
+    with pytest.raises(RuntimeError, match="cannot return more than one Tensor"):
+        TwoInPlace.apply(q, k)

@@ -7,30 +7,42 @@ One "step" is a full training step (forward, backward, AdamW step) of a random-i
 Qwen3-8B-shaped model (36 layers, hidden 4096, 32/8 heads, head_dim 128,
 intermediate 12288, vocab 151936, bf16) on one sequence of 8192 synthetic tokens,
 with RMSNorm, RoPE, the SwiGLU MLP and the fused lm_head + cross-entropy running on
-the bastile_b200 kernels and the optimizer step on bastile_b200.optim.AdamW (--optimizer torch
+the bastile_b200 kernels and the optimizer step on bastile_b200.optim (--optimizer torch
 selects torch.optim.AdamW as in the reference's own benchmark,
 tests/benchmarks/e2e/qwen_8b_seqlen.py:80-203); attention and the q/k/v/o projections are
 stock PyTorch.  By default the patch set is `apply(fused_layers=True)` (residual adds folded into
 the norm / down-projection kernels, q/k-norm + RoPE as one kernel; --no-fused-layers for exactly
 the reference's four patches) and, on one GPU, the optimizer updates each large parameter
 underneath the backward pass as soon as its gradient is complete (--no-overlap-optimizer).
-With N > 1 (launched by torchrun,
-one rank per GPU) every rank steps its own sequence and gradients are averaged by
-DistributedDataParallel over NCCL: weak scaling by tokens; the GEMM then draws its tiles at
-run time (--tiles) because NCCL kernels share the SMs with the backward pass.
+
+With N > 1 (launched by torchrun, one rank per GPU) every rank steps its own sequence: weak
+scaling by tokens.  --parallel selects how the ranks cooperate:
+  sharded  (default) bastile_b200.optim.ShardedAdamW: gradients reduce-scattered per bucket over
+           NCCL while the backward pass still runs, AdamW on this rank's 1/N of every bucket,
+           parameters all-gathered in place;
+  ddp      DistributedDataParallel + the AdamW step after the backward pass;
+  fsdp, fsdp-vp  FullyShardedDataParallel FULL_SHARD per decoder layer (the reference's
+           tests/benchmarks/e2e/qwen_8b_fsdp.py:161-168), with -vp the lm_head rows sharded over
+           the ranks and the fused loss run vocabulary-parallel.
 
 Rank 0 prints ONE JSON line.  `value` is tokens/s with the step's inputs already on
 the device; `e2e` is the same loop fed from pinned host buffers with the loss read
 back every step.  `roofline` describes the dominant kernel (the tcgen05 GEMM that
 runs the MLP block) from CUDA events recorded around its launches inside the timed
-steps.  `per_op` holds the forward+backward micro-benchmarks of the four ops at the
-per-op benchmark shapes.  `cpu_baseline` (N = 1 only) times HF eager on the host cores on a
-bounded sample.  `--impl reference` prints that CPU measurement as its own line.
+steps.  At N = 1 the line also carries `per_op` (forward+backward micro-benchmarks of the ops at
+the per-op benchmark shapes), `seq_sweep`, `comparators` (HF eager and Liger on the same GPU, as
+in the reference's own benchmark) and `cpu_baseline` (HF eager on the host cores, bounded sample).
+At N > 1 it carries `per_op` for the vocabulary-parallel fused loss with `vp_parity` (a self-check
+against the unsharded op on the same inputs; a mismatch makes the run exit non-zero), `ddp` (the
+same step under DistributedDataParallel, with the losses of both compared) and `sharded` (FSDP +
+vocabulary-parallel loss at 8192 and 32768 tokens per rank).  `--impl reference` prints the CPU
+measurement as its own line.
 """
 
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import subprocess
@@ -49,6 +61,8 @@ QWEN3_8B = dict(vocab_size=151936, hidden_size=4096, intermediate_size=12288, nu
                 attention_dropout=0.0, use_cache=False)
 METRIC = "Qwen3-8B train tokens/s/B200"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# reference README bar chart (other GPU software stack, intermediate 14336): context only
+REFERENCE_CHART = {"bastile_tokens_per_s_seq8192": 12.0e3, "bastile_over_pytorch": 1.24, "bastile_over_liger": 1.165}
 
 
 def load_peaks():
@@ -199,22 +213,31 @@ def run_reference_arm(args):
     import torch
 
     seq = 256
-    vals = []
+    vals, walls = [], []
     for _ in range(max(0, min(args.warmup, 1))):
         cpu_reference_sample(seq)
     t_begin = time.perf_counter()
     for _ in range(max(1, args.steps)):
+        t0 = time.perf_counter()
         v, times, threads = cpu_reference_sample(seq)
+        walls.append(time.perf_counter() - t0)
         vals.append(v)
         if time.perf_counter() - t_begin > 240:  # stay within a few minutes whatever K is
             break
     vals.sort()
+    walls.sort()
     value = vals[len(vals) // 2]
     sample = (f"HF transformers eager Qwen3 (what bastile.reset() restores), fp32, Qwen3-8B shapes at {seq} tokens: "
               f"36 x (decoder layer fwd+bwd) + (final norm + lm_head + cross-entropy fwd+bwd) + AdamW scaled to 8.19 B "
               f"parameters; median of {len(vals)} samples; last: {json.dumps({k: round(v, 3) for k, v in times.items()})}")
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": len(vals), "warmup": min(args.warmup, 1), "ms_per_step": SEQ_LEN / value * 1e3,
+            "extrapolated": True,
+            "ms_per_step_sample": walls[len(walls) // 2] * 1e3,
+            "extrapolation": "ms_per_step is the time a full 8192-token, 36-layer step would take at the sampled rate "
+                             "(it is NOT run: hours on these cores); ms_per_step_sample is the wall time of one sample "
+                             "as actually executed (one layer + head/loss + one layer's AdamW at 256 tokens, each run "
+                             "twice, model construction included)",
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"qwen3-8b ({QWEN3_8B['num_hidden_layers']} layers, hidden 4096, intermediate "
                                    f"{QWEN3_8B['intermediate_size']}, vocab 151936) seq {SEQ_LEN} batch 1 fwd+bwd+AdamW, "
@@ -265,6 +288,23 @@ def _tensor(ms, flops, peaks):
             "frac_of_bf16_sustained": t / peaks["bf16_tflops_sustained"], "algorithmic_TFLOP": flops / 1e12}
 
 
+def _lce_inputs(dev, rows=16384, hdim=4096, vocab=151936, full_weight=False, rank=0, world=1):
+    """Config-3 inputs, identical on every rank: hidden ~ N(0,1), labels uniform with 5 % ignored,
+    lm_head ~ N(0, 0.02) (the whole matrix, or this rank's rows of it)."""
+    import torch
+
+    bf = torch.bfloat16
+    gen = torch.Generator(device=dev).manual_seed(1)
+    hid = torch.randn(rows, hdim, device=dev, dtype=bf, generator=gen)
+    lab = torch.randint(0, vocab, (rows,), device=dev, generator=gen)
+    lab[torch.rand(rows, device=dev, generator=gen) < 0.05] = -100
+    w = torch.randn(vocab, hdim, device=dev, dtype=bf, generator=gen) * 0.02
+    if not full_weight:
+        vloc = vocab // world
+        w = w[rank * vloc:(rank + 1) * vloc].clone()
+    return hid, lab, w
+
+
 def per_op_bench(peaks, only=None, iters=None):
     """Forward+backward of each op at the per-op benchmark shapes (bf16, seed 1), called through
     the public ops; the time is that of the kernels (events around the library calls)."""
@@ -273,9 +313,9 @@ def per_op_bench(peaks, only=None, iters=None):
     from bastile_b200.ops.fused_linear_cross_entropy import fused_linear_cross_entropy
     from bastile_b200.ops.rms_norm import rms_norm
     from bastile_b200.ops.rope import RoPEFunction
-    from bastile_b200.ops.swiglu import SwiGLUMLPFunction
+    from bastile_b200.ops.swiglu import SwiGLUMLPFunction, swiglu
 
-    dev = "cuda"
+    dev = torch.device("cuda", torch.cuda.current_device())
     torch.manual_seed(1)
     flush = torch.zeros(64 << 20, dtype=torch.int32, device=dev)  # 256 MiB
     out = {}
@@ -355,6 +395,20 @@ def per_op_bench(peaks, only=None, iters=None):
         out["rope_q32_k8_8192x128_fwd_bwd"] = _hbm(_kernel_ms(rope, flush, iters or 20, 5), 339.74e6, peaks)
         del q, k, dq, dk
 
+    if want("swiglu"):
+        m, n = 8192, 12288
+        g = torch.randn(m, n, device=dev, dtype=bf).requires_grad_(True)
+        u = torch.randn(m, n, device=dev, dtype=bf).requires_grad_(True)
+        dh = torch.randn(m, n, device=dev, dtype=bf)
+
+        def swi():
+            g.grad = u.grad = None
+            swiglu(g, u).backward(dh)
+
+        # fwd: gate, up in, h out; bwd: dh, gate, up in, dgate, dup out
+        out[f"swiglu_elementwise_{m}x{n}_fwd_bwd"] = _hbm(_kernel_ms(swi, flush, iters or 20, 5), 8 * m * n * 2, peaks)
+        del g, u, dh
+
     if want("mlp"):
         xm = torch.randn(8192, 4096, device=dev, dtype=bf).requires_grad_(True)
         wg = (torch.randn(12288, 4096, device=dev) * 0.02).to(bf).requires_grad_(True)
@@ -375,45 +429,374 @@ def per_op_bench(peaks, only=None, iters=None):
         world = dist.get_world_size() if dist.is_initialized() else 1
         rank = dist.get_rank() if dist.is_initialized() else 0
         vloc = 151936 // world  # 75968 / 37984 / 18992 rows of lm_head per rank at 2 / 4 / 8 GPUs
-        gen = torch.Generator(device=dev).manual_seed(1)  # same hidden states and labels on every rank
-        hid = torch.randn(16384, 4096, device=dev, dtype=bf, generator=gen).requires_grad_(True)
-        lab = torch.randint(0, 151936, (16384,), device=dev, generator=gen)
-        lab[torch.rand(16384, device=dev, generator=gen) < 0.05] = -100
-        wl = (torch.randn(vloc, 4096, device=dev, dtype=bf) * 0.02).requires_grad_(True)
+        hid, lab, wl = _lce_inputs(dev, rank=rank, world=world)
+        hid.requires_grad_(True)
+        wl.requires_grad_(True)
         group = dist.group.WORLD if world > 1 else None
 
         def lce():
             hid.grad = wl.grad = None
-            fused_linear_cross_entropy(hid, wl, lab, vocab_parallel_group=group, vocab_start=rank * vloc).backward()
+            fused_linear_cross_entropy(hid, wl, lab, vocab_parallel_group=group, vocab_start=rank * vloc,
+                                       vocab_size=151936).backward()
 
-        if world == 1:
-            ms = _kernel_ms(lce, flush, iters or 5, 2)
-        else:  # collectives sit between the kernels: time the whole call, max over ranks
-            for _ in range(2):
-                lce()
+        def timed_whole(fn, n):  # collectives sit between the kernels: time the whole call, max over ranks
             ts = []
-            for _ in range(iters or 5):
+            for _ in range(n):
                 flush.sum()
                 dist.barrier()
                 torch.cuda.synchronize()
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record()
-                lce()
+                fn()
                 b.record()
                 torch.cuda.synchronize()
                 t = torch.tensor([a.elapsed_time(b)], device=dev)
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 ts.append(float(t))
             ts.sort()
-            ms = ts[len(ts) // 2]
+            return ts[len(ts) // 2]
+
+        if world == 1:
+            ms = _kernel_ms(lce, flush, iters or 5, 2)
+        else:
+            for _ in range(2):
+                lce()
+            ms = timed_whole(lce, iters or 5)
         res = _tensor(ms, 61.1775e12, peaks)
         if world > 1:
+            # the two exchanges of the call, timed by themselves on buffers of the call's sizes
+            chunk = 8192
+            mine = torch.zeros(chunk, 3, device=dev)
+            gathered = torch.empty(world, chunk, 3, device=dev)
+            dxf = torch.zeros(16384, 4096, device=dev)
+
+            def stats_gather():
+                dist.all_gather_into_tensor(gathered.view(-1), mine.view(-1))
+
+            def dx_reduce():
+                dist.all_reduce(dxf)
+
+            for f in (stats_gather, dx_reduce):
+                for _ in range(2):
+                    f()
             res = {"ms": ms, "TFLOPs_all_gpus": res["TFLOPs"], "TFLOPs_per_gpu": res["TFLOPs"] / world,
                    "frac_of_bf16_burst_per_gpu": res["frac_of_bf16_burst"] / world, "n_gpus": world,
+                   "collectives_ms": {"stats_all_gather_per_chunk": timed_whole(stats_gather, 5),
+                                      "chunks": 2, "dhidden_all_reduce_fp32": timed_whole(dx_reduce, 5)},
                    "sharding": f"vocabulary: {vloc} lm_head rows per rank; one all-gather of [rows,3] fp32 statistics per "
                                "chunk, one fp32 all-reduce of d(hidden)", "algorithmic_TFLOP": 61.1775}
+            del mine, gathered, dxf
         out["fused_linear_ce_16384x4096x151936_fwd_bwd"] = res
+        del hid, lab, wl
     return out
+
+
+def vp_parity_check(dev, rank, world):
+    """Vocabulary-parallel fused loss over NCCL against the unsharded op on the same inputs
+    (16384 x 4096 x 151936, config 3), both with all rows on every rank and with the rows sharded
+    over the ranks.  Returns max-over-ranks errors; `ok` is False beyond loss 1e-3 / gradients 2e-2
+    (relative to the largest reference magnitude)."""
+    import torch
+    import torch.distributed as dist
+
+    from bastile_b200.ops.fused_linear_cross_entropy import fused_linear_cross_entropy
+
+    vocab, rows = 151936, 16384
+    vloc = vocab // world
+    hid, lab, w_full = _lce_inputs(dev, full_weight=True)
+    x0 = hid.clone().requires_grad_(True)
+    w0 = w_full.clone().requires_grad_(True)
+    loss0 = fused_linear_cross_entropy(x0, w0, lab)
+    loss0.backward()
+    dx_ref, dw_ref = x0.grad.float(), w0.grad[rank * vloc:(rank + 1) * vloc].float()
+    sx, sw = float(dx_ref.abs().max()), float(w0.grad.float().abs().max())
+    del w0, x0
+    out = {}
+    for shard_tokens in (False, True):
+        xs = hid if not shard_tokens else hid[rank * (rows // world):(rank + 1) * (rows // world)]
+        ls = lab if not shard_tokens else lab[rank * (rows // world):(rank + 1) * (rows // world)]
+        x1 = xs.clone().requires_grad_(True)
+        w1 = w_full[rank * vloc:(rank + 1) * vloc].clone().requires_grad_(True)
+        loss1 = fused_linear_cross_entropy(x1, w1, ls, vocab_parallel_group=dist.group.WORLD, vocab_start=rank * vloc,
+                                           shard_tokens=shard_tokens, vocab_size=vocab)
+        loss1.backward()
+        ref_rows = dx_ref if not shard_tokens else dx_ref[rank * (rows // world):(rank + 1) * (rows // world)]
+        errs = torch.stack([(loss1.float() - loss0.float()).abs() / loss0.float().abs(),
+                            (x1.grad.float() - ref_rows).abs().max() / sx,
+                            (w1.grad.float() - dw_ref).abs().max() / sw]).to(torch.float64)
+        dist.all_reduce(errs, op=dist.ReduceOp.MAX)
+        e = [float(v) for v in errs.tolist()]
+        out["shard_tokens" if shard_tokens else "all_rows_on_every_rank"] = {
+            "loss_rel_err": e[0], "dx_max_abs_over_max": e[1], "dw_shard_max_abs_over_max": e[2]}
+        del x1, w1
+    out["loss_unsharded"] = float(loss0)
+    out["tolerance"] = {"loss_rel_err": 1e-3, "gradients": 2e-2}
+    out["ok"] = all(v["loss_rel_err"] <= 1e-3 and v["dx_max_abs_over_max"] <= 2e-2 and
+                    v["dw_shard_max_abs_over_max"] <= 2e-2 for k, v in out.items() if isinstance(v, dict) and
+                    "loss_rel_err" in v)
+    return out
+
+
+# ---------------------------------------------------------------------- one training run
+class _LigerPatches:
+    """apply_liger_kernel_to_qwen3 replaces attributes of transformers' qwen3 module for good;
+    this puts them back afterwards."""
+
+    NAMES = ("apply_rotary_pos_emb", "Qwen3RMSNorm", "Qwen3MLP")
+
+    def __enter__(self):
+        import transformers.models.qwen3.modeling_qwen3 as q3
+        from liger_kernel.transformers import apply_liger_kernel_to_qwen3
+
+        self.mod = q3
+        self.saved = {n: getattr(q3, n) for n in self.NAMES}
+        self.saved_fwd = q3.Qwen3ForCausalLM.forward
+        # what the reference's benchmark applies (tests/benchmarks/e2e/qwen_8b_seqlen.py, phase "liger")
+        apply_liger_kernel_to_qwen3(rope=True, rms_norm=True, swiglu=True, cross_entropy=False,
+                                    fused_linear_cross_entropy=True)
+        return self
+
+    def __exit__(self, *exc):
+        for n, v in self.saved.items():
+            setattr(self.mod, n, v)
+        self.mod.Qwen3ForCausalLM.forward = self.saved_fwd
+        return False
+
+
+def train_run(*, dev, rank, world, local, patches="bastile", parallel="single", optimizer="bastile", seq=SEQ_LEN,
+              layers=36, intermediate=12288, steps=5, warmup=3, fused_layers=True, gemm_projections="off",
+              overlap_opt=True, tiles="auto", grad_checkpoint=False, measure_e2e=True, sample_clocks=False,
+              master_weights=False, sweep=()):
+    """Build the model under the given patches / parallel wrapper / optimizer, run `warmup` untimed
+    and `steps` timed steps (and, optionally, the same loop fed from pinned host memory), then the
+    `sweep` entries (dicts with seq, steps, warmup, grad_checkpoint) on the same model.  Everything
+    is torn down before returning."""
+    import contextlib
+
+    import torch
+    import torch.distributed as dist
+    from transformers import Qwen3Config
+
+    import bastile_b200
+    from bastile_b200 import _lib
+
+    res = {"patches": patches, "parallel": parallel, "optimizer": optimizer}
+    stack = contextlib.ExitStack()
+    dynamic_tiles = tiles == "dynamic" or (tiles == "auto" and world > 1)
+    applied = []
+    if patches == "bastile":
+        _lib.get_lib().bt_set_gemm_dynamic_tiles(1 if dynamic_tiles else 0)
+        applied = bastile_b200.apply(fused_layers=fused_layers, gemm_projections=gemm_projections)
+        expected = ["rms_norm_qwen3", "rope_qwen3", "swiglu_qwen3"]
+        expected += ["decoder_layer_qwen3", "attention_qwen3"] if fused_layers else []
+        assert applied == expected + ["fused_linear_cross_entropy"], applied
+    else:
+        bastile_b200.reset()
+        if patches == "liger":
+            stack.enter_context(_LigerPatches())
+            applied = ["liger_kernel rope, rms_norm, swiglu, fused_linear_cross_entropy"]
+    res["applied"] = applied
+    import transformers.models.qwen3.modeling_qwen3 as q3
+
+    cfg = Qwen3Config(**{**QWEN3_8B, "num_hidden_layers": layers, "intermediate_size": intermediate})
+    cfg._attn_implementation = "sdpa"
+    torch.manual_seed(1234)  # same initial weights on every rank
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    with torch.device(dev):
+        model = q3.Qwen3ForCausalLM(cfg)
+    torch.set_default_dtype(prev)
+    model.train()
+    ckpt_kwargs = {"gradient_checkpointing_kwargs": {"use_reentrant": False}}
+    if grad_checkpoint:
+        model.gradient_checkpointing_enable(**ckpt_kwargs)
+    net = model
+    parallelism = "single GPU"
+    vp_on = False
+    if world > 1 and parallel in ("fsdp", "fsdp-vp"):
+        import functools
+
+        from torch.distributed.fsdp import FullyShardedDataParallel as FSDP
+        from torch.distributed.fsdp import MixedPrecision, ShardingStrategy
+        from torch.distributed.fsdp.wrap import transformer_auto_wrap_policy
+
+        ignored = None
+        if parallel == "fsdp-vp":
+            # this rank keeps rows [rank*V/n, (rank+1)*V/n) of lm_head as an ordinary local parameter
+            from bastile_b200.ops.fused_linear_cross_entropy import set_vocab_parallel
+
+            vloc = cfg.vocab_size // world
+            shard = model.lm_head.weight.data[rank * vloc:(rank + 1) * vloc].clone()
+            model.lm_head.weight = torch.nn.Parameter(shard)
+            set_vocab_parallel(dist.group.WORLD, vocab_start=rank * vloc, grad_hidden_scale=float(world),
+                               vocab_size=cfg.vocab_size)
+            vp_on = True
+            ignored = [model.lm_head]
+        mp = MixedPrecision(param_dtype=torch.bfloat16, reduce_dtype=torch.bfloat16, buffer_dtype=torch.bfloat16)
+        net = FSDP(model, sharding_strategy=ShardingStrategy.FULL_SHARD, mixed_precision=mp,
+                   auto_wrap_policy=functools.partial(transformer_auto_wrap_policy,
+                                                      transformer_layer_cls={q3.Qwen3DecoderLayer}),
+                   use_orig_params=True, device_id=dev, ignored_modules=ignored)
+        parallelism = (f"fsdp{world} FULL_SHARD bf16, per-layer wrap" +
+                       (", lm_head vocabulary-parallel" if vp_on else ""))
+    elif world > 1 and parallel == "ddp":
+        from torch.nn.parallel import DistributedDataParallel as DDP
+
+        net = DDP(model, device_ids=[local], gradient_as_bucket_view=True, bucket_cap_mb=256)
+        parallelism = f"dp{world} (DistributedDataParallel, NCCL all-reduce, AdamW after the backward pass)"
+    elif world > 1 and parallel == "sharded":
+        parallelism = (f"dp{world} (bastile_b200.optim.ShardedAdamW: per-bucket NCCL reduce-scatter, AdamW on 1/{world} "
+                       "of each bucket, all-gather of the parameters, all underneath the backward pass)")
+    elif world > 1:
+        raise SystemExit(f"--parallel {parallel} is not a multi-GPU mode")
+
+    overlap = optimizer == "bastile" and world == 1 and overlap_opt
+    if optimizer == "bastile" and world > 1 and parallel == "sharded":
+        from bastile_b200.optim import ShardedAdamW
+
+        opt = ShardedAdamW(net.parameters(), lr=1e-4, group=dist.group.WORLD, master_weights=master_weights)
+        opt_name = "bastile_b200.optim.ShardedAdamW" + (", fp32 master weights" if master_weights else
+                                                        ", bf16 params and state")
+    elif optimizer == "bastile":
+        from bastile_b200.optim import AdamW
+
+        # one process: every large parameter is updated as soon as its gradient is complete, on a side
+        # stream underneath the rest of the backward pass (under DDP / FSDP gradients are only final after
+        # the reduction, so the update stays in step())
+        opt = AdamW(net.parameters(), lr=1e-4, overlap_backward=overlap, master_weights=master_weights)
+        opt_name = ("bastile_b200.optim.AdamW" + (", updates overlapped with the backward pass" if overlap else "") +
+                    (", fp32 master weights" if master_weights else ", bf16 params and state"))
+    else:
+        if parallel == "sharded" and world > 1:
+            raise SystemExit("--parallel sharded needs --optimizer bastile")
+        opt = torch.optim.AdamW(net.parameters(), lr=1e-4, fused=True)
+        opt_name = "torch.optim.AdamW(fused=True), bf16 params and state"
+    res.update(parallelism=parallelism, optimizer_name=opt_name, gemm_tiles="dynamic" if dynamic_tiles else "fixed")
+
+    torch.manual_seed(4321 + rank)  # different tokens per rank
+    n_bufs = 4
+    tail_events = []
+
+    def step(ids, record_tail=False):
+        opt.zero_grad(set_to_none=True)
+        loss = net(input_ids=ids, labels=ids).loss
+        loss.backward()
+        if record_tail:
+            a = torch.cuda.Event(enable_timing=True)
+            a.record()
+        opt.step()
+        if record_tail:
+            b = torch.cuda.Event(enable_timing=True)
+            b.record()
+            tail_events.append((a, b))
+        return loss
+
+    def fence():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def measure(seq_len, n_steps, n_warm, e2e, clocks_on, record_ops):
+        host_ids = [torch.randint(0, cfg.vocab_size, (1, seq_len)).pin_memory() for _ in range(n_bufs)]
+        dev_ids = [h.to(dev) for h in host_ids]
+        ids_in = torch.empty((1, seq_len), dtype=torch.int64, device=dev)
+        out = {"seq": seq_len, "steps": n_steps, "warmup": n_warm}
+        first = []
+        for i in range(n_warm):
+            ids_in.copy_(host_ids[i % n_bufs], non_blocking=True)
+            first.append(float(step(ids_in).item()))
+        out["first_losses"] = first
+        if patches == "bastile":
+            _lib.check_status(dev, "warm-up steps")
+        torch.cuda.reset_peak_memory_stats()
+        # ---- device-resident loop: `value`
+        if record_ops:
+            _lib.instr.reset(enabled=True)
+        tail_events.clear()
+        with (ClockSampler(local) if clocks_on else contextlib.nullcontext()) as clocks:
+            fence()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(n_steps):
+                loss = step(dev_ids[i % n_bufs], record_tail=True)
+            e1.record()
+            fence()
+            ms_value = e0.elapsed_time(e1)
+        if record_ops:
+            out["launches"] = _lib.instr.launches
+            out["op_ms"] = _lib.instr.elapsed_ms()
+            _lib.instr.reset(enabled=False)
+        out["tail_ms"] = sum(a.elapsed_time(b) for a, b in tail_events) / max(1, len(tail_events))
+        out["last_loss"] = float(loss.item())
+        if clocks_on:
+            out["clocks"] = clocks.summary()
+        ms_e2e = 0.0
+        if e2e:
+            # ---- end-to-end loop: pinned host ids -> device every step, loss read back every step
+            fence()
+            e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e2.record()
+            for i in range(n_steps):
+                ids_in.copy_(host_ids[i % n_bufs], non_blocking=True)
+                step(ids_in).item()
+            e3.record()
+            fence()
+            ms_e2e = e2.elapsed_time(e3)
+        if patches == "bastile":
+            _lib.check_all_status()
+        t = torch.tensor([ms_value, ms_e2e, out["tail_ms"]], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_value, ms_e2e, out["tail_ms"] = (float(v) for v in t.tolist())
+        tokens = seq_len * world * n_steps
+        out.update(ms_value=ms_value, ms_per_step=ms_value / n_steps, tokens_per_s=tokens / (ms_value / 1e3),
+                   peak_mem_GB=torch.cuda.max_memory_allocated() / 1e9)
+        if e2e:
+            out.update(ms_e2e=ms_e2e, e2e_tokens_per_s=tokens / (ms_e2e / 1e3), e2e_ms_per_step=ms_e2e / n_steps)
+        return out
+
+    try:
+        res["main"] = measure(seq, steps, warmup, measure_e2e, sample_clocks, patches == "bastile")
+        res["sweep"] = []
+        for entry in sweep:
+            try:
+                if entry.get("grad_checkpoint") and not grad_checkpoint:
+                    model.gradient_checkpointing_enable(**ckpt_kwargs)
+                    grad_checkpoint = True
+                r = measure(entry["seq"], entry.get("steps", 3), entry.get("warmup", 2), False, False, False)
+                r["activation_checkpointing"] = bool(grad_checkpoint)
+                res["sweep"].append(r)
+            except torch.OutOfMemoryError as exc:
+                res["sweep"].append({"seq": entry["seq"], "skipped": f"out of memory: {str(exc)[:80]}"})
+                torch.cuda.empty_cache()
+    finally:
+        if vp_on:
+            from bastile_b200.ops.fused_linear_cross_entropy import set_vocab_parallel
+
+            set_vocab_parallel(None)
+        del net, model, opt
+        stack.close()
+        gc.collect()
+        torch.cuda.empty_cache()
+    return res
+
+
+def _slim(m):
+    """The fields of a measure() result worth printing for a secondary run."""
+    keep = ("seq", "steps", "warmup", "tokens_per_s", "ms_per_step", "peak_mem_GB", "tail_ms", "first_losses",
+            "activation_checkpointing", "skipped")
+    return {k: m[k] for k in keep if k in m}
+
+
+def _traffic_from_profile():
+    """DRAM bytes per launch of the dominant kernel, from the committed summary of its ncu capture."""
+    p = ROOT / "profiles" / "gemm_kernel_pair_mlp_8192x4096x12288.json"
+    try:
+        d = json.loads(p.read_text())
+        return float(d["dram_bytes_per_launch_mean"]), {"from_profile": True, "file": f"profiles/{p.name}",
+                                                        "capture": d.get("command"), "note": d.get("note")}
+    except Exception as exc:
+        return None, {"from_profile": False, "error": repr(exc)}
 
 
 # -------------------------------------------------------------------------- main arm
@@ -427,16 +810,17 @@ def main():
     ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
     ap.add_argument("--intermediate", type=int, default=QWEN3_8B["intermediate_size"],
                     help="MLP width (the reference's chart used 14336; Qwen3-8B itself has 12288)")
-    ap.add_argument("--fsdp", action="store_true",
-                    help="N > 1: FullyShardedDataParallel FULL_SHARD with bf16 mixed precision, wrapped per decoder layer "
-                         "(the reference's tests/benchmarks/e2e/qwen_8b_fsdp.py:161-168) instead of DDP")
-    ap.add_argument("--vocab-parallel", action="store_true",
-                    help="with --fsdp: lm_head rows sharded over ranks and the fused loss run vocabulary-parallel")
+    ap.add_argument("--parallel", default="auto", choices=["auto", "sharded", "ddp", "fsdp", "fsdp-vp"],
+                    help="N > 1: how the ranks cooperate (see the module docstring); auto = sharded")
+    ap.add_argument("--fsdp", action="store_true", help="same as --parallel fsdp")
+    ap.add_argument("--vocab-parallel", action="store_true", help="with --fsdp: same as --parallel fsdp-vp")
+    ap.add_argument("--master-weights", action="store_true",
+                    help="fp32 master parameters and moments in the bastile optimizers (bf16 parameters / fp32 master)")
     ap.add_argument("--grad-checkpoint", action="store_true",
                     help="recompute each decoder layer in the backward (needed for seq 32768 per rank: the saved "
                          "activations of 36 layers alone would exceed 180 GB)")
     ap.add_argument("--optimizer", default="bastile", choices=["bastile", "torch"],
-                    help="bastile: bastile_b200.optim.AdamW (one streaming kernel per tensor); torch: "
+                    help="bastile: bastile_b200.optim (streaming AdamW kernels); torch: "
                          "torch.optim.AdamW(fused=True), what the reference's benchmark loop uses")
     ap.add_argument("--no-fused-layers", action="store_true",
                     help="leave Qwen3DecoderLayer.forward / Qwen3Attention.forward as HF has them (by default the "
@@ -453,10 +837,12 @@ def main():
                          "a global counter at run time (dynamic: bt_set_gemm_dynamic_tiles(1)); auto = dynamic when "
                          "NCCL collectives share the GPU with the backward pass (more than one rank), else fixed")
     ap.add_argument("--no-per-op", action="store_true")
-    ap.add_argument("--only-op", default=None, choices=["rmsnorm", "rope", "mlp", "lce"],
+    ap.add_argument("--only-op", default=None, choices=["rmsnorm", "rope", "swiglu", "mlp", "lce"],
                     help="run just this op's forward+backward micro-benchmark (small case for profilers)")
     ap.add_argument("--op-iters", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="only the main timed loop: no sequence sweep, comparators, DDP / FSDP companion runs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -477,12 +863,10 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    import bastile_b200
     from bastile_b200 import _lib
-    from transformers import Qwen3Config, Qwen3ForCausalLM
 
+    peaks, peak_kind = load_peaks()
     if args.only_op:
-        peaks, peak_kind = load_peaks()
         res = per_op_bench(peaks, only=args.only_op, iters=args.op_iters)
         _lib.check_status(dev, "per-op benchmark")
         if rank == 0:
@@ -492,179 +876,121 @@ def main():
             dist.destroy_process_group()
         return
 
+    parallel = args.parallel
+    if args.fsdp:
+        parallel = "fsdp-vp" if args.vocab_parallel else "fsdp"
+    if parallel == "auto":
+        parallel = "sharded" if (world > 1 and args.optimizer == "bastile") else ("ddp" if world > 1 else "single")
+    if world == 1:
+        parallel = "single"
     fused_layers = not args.no_fused_layers
-    dynamic_tiles = args.tiles == "dynamic" or (args.tiles == "auto" and world > 1)
-    _lib.get_lib().bt_set_gemm_dynamic_tiles(1 if dynamic_tiles else 0)
-    applied = bastile_b200.apply(fused_layers=fused_layers, gemm_projections=args.gemm_projections)
-    expected = ["rms_norm_qwen3", "rope_qwen3", "swiglu_qwen3"]
-    expected += ["decoder_layer_qwen3", "attention_qwen3"] if fused_layers else []
-    assert applied == expected + ["fused_linear_cross_entropy"], applied
-    peaks, peak_kind = load_peaks()
+    grad_checkpoint = args.grad_checkpoint or args.seq >= 32768
+    common = dict(dev=dev, rank=rank, world=world, local=local, layers=args.layers, fused_layers=fused_layers,
+                  gemm_projections=args.gemm_projections, tiles=args.tiles)
+    extras = not args.no_extras and args.layers == QWEN3_8B["num_hidden_layers"]
 
-    cfg = Qwen3Config(**{**QWEN3_8B, "num_hidden_layers": args.layers, "intermediate_size": args.intermediate})
-    cfg._attn_implementation = "sdpa"
-    torch.manual_seed(1234)  # same initial weights on every rank
-    prev = torch.get_default_dtype()
-    torch.set_default_dtype(torch.bfloat16)
-    with torch.device(dev):
-        model = Qwen3ForCausalLM(cfg)
-    torch.set_default_dtype(prev)
-    model.train()
-    if args.grad_checkpoint or args.seq >= 32768:
-        args.grad_checkpoint = True
-        model.gradient_checkpointing_enable(gradient_checkpointing_kwargs={"use_reentrant": False})
-    net = model
-    parallelism = "single GPU"
-    if world > 1 and args.fsdp:
-        import functools
-
-        from torch.distributed.fsdp import FullyShardedDataParallel as FSDP
-        from torch.distributed.fsdp import MixedPrecision, ShardingStrategy
-        from torch.distributed.fsdp.wrap import transformer_auto_wrap_policy
-        from transformers.models.qwen3.modeling_qwen3 import Qwen3DecoderLayer
-
-        ignored = None
-        if args.vocab_parallel:
-            # this rank keeps rows [rank*V/n, (rank+1)*V/n) of lm_head as an ordinary local parameter
-            from bastile_b200.ops.fused_linear_cross_entropy import set_vocab_parallel
-
-            vloc = cfg.vocab_size // world
-            shard = model.lm_head.weight.data[rank * vloc:(rank + 1) * vloc].clone()
-            model.lm_head.weight = torch.nn.Parameter(shard)
-            set_vocab_parallel(dist.group.WORLD, vocab_start=rank * vloc, grad_hidden_scale=float(world))
-            ignored = [model.lm_head]
-        mp = MixedPrecision(param_dtype=torch.bfloat16, reduce_dtype=torch.bfloat16, buffer_dtype=torch.bfloat16)
-        net = FSDP(model, sharding_strategy=ShardingStrategy.FULL_SHARD, mixed_precision=mp,
-                   auto_wrap_policy=functools.partial(transformer_auto_wrap_policy,
-                                                      transformer_layer_cls={Qwen3DecoderLayer}),
-                   use_orig_params=True, device_id=dev, ignored_modules=ignored)
-        parallelism = (f"fsdp{world} FULL_SHARD bf16, per-layer wrap" +
-                       (", lm_head vocabulary-parallel" if args.vocab_parallel else ""))
-    elif world > 1:
-        from torch.nn.parallel import DistributedDataParallel as DDP
-
-        net = DDP(model, device_ids=[local], gradient_as_bucket_view=True, bucket_cap_mb=256)
-        parallelism = f"dp{world} (DistributedDataParallel, NCCL)"
-    overlap_opt = args.optimizer == "bastile" and world == 1 and not args.no_overlap_optimizer
-    if args.optimizer == "bastile":
-        from bastile_b200.optim import AdamW
-
-        # one process: every large parameter is updated as soon as its gradient is complete, on a side
-        # stream underneath the rest of the backward pass (under DDP / FSDP gradients are only final after
-        # the reduction, so the update stays in step())
-        opt = AdamW(net.parameters(), lr=1e-4, overlap_backward=overlap_opt)
-    else:
-        opt = torch.optim.AdamW(net.parameters(), lr=1e-4, fused=True)
-
-    torch.manual_seed(4321 + rank)  # different tokens per rank
+    sweep = []
+    if extras and world == 1 and args.seq == SEQ_LEN and not grad_checkpoint:
+        # the reference's chart runs 256 ... 32768 (tests/benchmarks/e2e/qwen_8b_seqlen.py:47): the short ones
+        # show host time per step, the long ones the attention share
+        sweep = [{"seq": 256, "steps": 5, "warmup": 3}, {"seq": 512, "steps": 5, "warmup": 3},
+                 {"seq": 2048, "steps": 3, "warmup": 2}, {"seq": 4096, "steps": 3, "warmup": 2},
+                 {"seq": 16384, "steps": 3, "warmup": 2}]
+    main_run = train_run(**common, patches="bastile", parallel=parallel, optimizer=args.optimizer, seq=args.seq,
+                         intermediate=args.intermediate, steps=args.steps, warmup=args.warmup,
+                         overlap_opt=not args.no_overlap_optimizer, grad_checkpoint=grad_checkpoint,
+                         measure_e2e=True, sample_clocks=True, master_weights=args.master_weights, sweep=sweep)
+    m = main_run["main"]
+    op_ms = m["op_ms"]
     seq = args.seq
-    n_bufs = 4
-    host_ids = [torch.randint(0, cfg.vocab_size, (1, seq)).pin_memory() for _ in range(n_bufs)]
-    dev_ids = [h.to(dev) for h in host_ids]
-    ids_in = torch.empty((1, seq), dtype=torch.int64, device=dev)
-
-    def step(ids):
-        opt.zero_grad(set_to_none=True)
-        loss = net(input_ids=ids, labels=ids).loss
-        loss.backward()
-        opt.step()
-        return loss
-
-    def fence():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for i in range(args.warmup):
-        ids_in.copy_(host_ids[i % n_bufs], non_blocking=True)
-        step(ids_in).item()
-    _lib.check_status(dev, "warm-up steps")
-
-    # ---- device-resident loop: `value`
-    _lib.instr.reset(enabled=True)
-    with ClockSampler(local) as clocks:
-        fence()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(args.steps):
-            loss = step(dev_ids[i % n_bufs])
-        e1.record()
-        fence()
-        ms_value = e0.elapsed_time(e1)
-    launches = _lib.instr.launches
-    op_ms = _lib.instr.elapsed_ms()
-    _lib.instr.reset(enabled=False)
-    last_loss = float(loss.item())
-
-    # ---- end-to-end loop: pinned host ids -> device every step, loss read back every step
-    fence()
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record()
-    for i in range(args.steps):
-        ids_in.copy_(host_ids[i % n_bufs], non_blocking=True)
-        step(ids_in).item()
-    e3.record()
-    fence()
-    ms_e2e = e2.elapsed_time(e3)
-    _lib.check_all_status()
-
-    t = torch.tensor([ms_value, ms_e2e], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_value, ms_e2e = (float(v) for v in t.tolist())
-    tokens = seq * world * args.steps
-    value = tokens / (ms_value / 1e3)
-    e2e_value = tokens / (ms_e2e / 1e3)
 
     # ---- roofline of the dominant kernel: the tcgen05 GEMM under the MLP block
-    hdim, inter = cfg.hidden_size, cfg.intermediate_size
+    hdim, inter = QWEN3_8B["hidden_size"], args.intermediate
     mlp_calls, mlp_ms = 0, 0.0
     for name in ("mlp_fwd", "mlp_bwd"):
-        c, m = op_ms.get(name, (0, 0.0))
+        c, t = op_ms.get(name, (0, 0.0))
         mlp_calls += c
-        mlp_ms += m
-    gemm_launches = 6 * (mlp_calls // 2) if mlp_calls else 0
-    mlp_flops = 9 * 2.0 * seq * hdim * inter * (mlp_calls // 2)
-    achieved = mlp_flops / (mlp_ms / 1e3) / 1e12 if mlp_ms > 0 else None
+        mlp_ms += t
+    blocks = mlp_calls // 2
+    if grad_checkpoint:  # every block's forward runs twice; events cover all of it, so do the flops
+        blocks_flops = 12 * 2.0 * seq * hdim * inter * op_ms.get("mlp_bwd", (0, 0))[0]
+        gemm_launches = 2 * op_ms.get("mlp_fwd", (0, 0))[0] + 4 * op_ms.get("mlp_bwd", (0, 0))[0]
+    else:
+        blocks_flops = 9 * 2.0 * seq * hdim * inter * blocks
+        gemm_launches = 6 * blocks
+    achieved = blocks_flops / (mlp_ms / 1e3) / 1e12 if mlp_ms > 0 else None
     peak_tf = peaks["bf16_tflops_sustained"]
+    traffic, traffic_src = _traffic_from_profile()
     roofline = {"bound": "tensor", "kernel": "bt::gemm::gemm_kernel_pair, tcgen05 cta_group::2 (6 launches per MLP block: gate|up fused, "
                                              "down (+ residual), dh->dgate/dup, dWd, dWg|dWu stacked, dx)",
                 "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf if achieved else None,
                 "peak_kind": f"{peak_kind} cuBLAS bf16, sustained (kernel timed inside a long step); burst {peaks['bf16_tflops']}",
                 "frac_of_burst": achieved / peaks["bf16_tflops"] if achieved else None,
-                "flops_per_launch": mlp_flops / gemm_launches if gemm_launches else None,
+                "flops_per_launch": blocks_flops / gemm_launches if gemm_launches else None,
                 "avg_launch_ms": mlp_ms / gemm_launches if gemm_launches else None, "launches_timed": gemm_launches,
-                "traffic": 1.56e9, "traffic_note": "dram read+write bytes per launch, mean of the 6 launches of a block, ncu --set full "
-                                                        "capture of bench.py --only-op mlp (profiles/gemm_kernel_pair_mlp_8192x4096x12288.md)"}
+                "traffic": traffic, "traffic_source": traffic_src}
 
-    line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_value / args.steps, "higher_is_better": True, "scaling": "weak",
+    line = {"metric": METRIC, "value": m["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": m["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"qwen3-8b ({args.layers} layers, hidden 4096, intermediate {args.intermediate}, vocab 151936) seq {seq} "
                                    "batch 1 fwd+bwd+AdamW, random init",
                        "global_batch_tokens": seq * world, "seq_len": seq,
-                       "parallelism": parallelism,
-                       "attention": "torch SDPA", "activation_checkpointing": bool(args.grad_checkpoint), "gemm_tiles": "dynamic" if dynamic_tiles else "fixed", "fused_layers": fused_layers, "gemm_projections": args.gemm_projections if fused_layers else "off", "optimizer": (("bastile_b200.optim.AdamW" + (", updates overlapped with the backward pass" if overlap_opt else "")) if args.optimizer == "bastile" else "torch.optim.AdamW(fused=True)")
-                                    + ", bf16 params and state",
+                       "parallelism": main_run["parallelism"],
+                       "attention": "torch SDPA", "activation_checkpointing": bool(grad_checkpoint),
+                       "gemm_tiles": main_run["gemm_tiles"], "fused_layers": fused_layers,
+                       "gemm_projections": args.gemm_projections if fused_layers else "off",
+                       "optimizer": main_run["optimizer_name"],
                        "l2": "each step streams ~65 GB of weights, gradients and optimizer state: far larger than the 126 MB L2"},
-            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": seq * 8, "d2h_bytes_per_step": 4,
-                    "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": launches, "clocks": clocks.summary(), "roofline": roofline, "loss": last_loss,
+            "e2e": {"value": m["e2e_tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": seq * 8,
+                    "d2h_bytes_per_step": 4, "ms_per_step": m["e2e_ms_per_step"]},
+            "gpu_launches": m["launches"], "clocks": m["clocks"], "roofline": roofline, "loss": m["last_loss"],
             "op_ms_per_step": {k: v[1] / args.steps for k, v in op_ms.items()},
-            "peak_mem_GB": torch.cuda.max_memory_allocated() / 1e9, "applied": applied}
+            "optimizer_tail_ms_per_step": m["tail_ms"],
+            "optimizer_tail_note": "device time from the end of the backward pass on the main stream to the end of "
+                                   "optimizer.step(): what the optimizer and (N > 1) the gradient / parameter "
+                                   "collectives leave exposed",
+            "peak_mem_GB": m["peak_mem_GB"], "applied": main_run["applied"]}
+    if main_run["sweep"]:
+        line["seq_sweep"] = [_slim(r) for r in main_run["sweep"]]
+    rc = 0
 
-    if rank == 0:
-        published = 12.0e3  # reference README bar chart, seq 8192 (intermediate 14336, other software stack)
-        line["reference_published_tokens_per_s_seq8192"] = published
-    if world == 1:
-        del net, model, opt
-        torch.cuda.empty_cache()
-        if not args.no_per_op:
-            try:
-                line["per_op"] = per_op_bench(peaks)
-            except Exception as exc:  # the headline number stands on its own
-                line["per_op"] = {"error": repr(exc)}
+    def guarded(name, fn):
+        """A companion measurement must not void the headline: record its failure instead."""
+        try:
+            return fn()
+        except Exception as exc:  # noqa: BLE001
+            gc.collect()
             torch.cuda.empty_cache()
+            return {"skipped": f"{type(exc).__name__}: {str(exc)[:200]}", "what": name}
+
+    if world == 1:
+        line["reference_published"] = REFERENCE_CHART
+        if not args.no_per_op:
+            line["per_op"] = guarded("per_op", lambda: per_op_bench(peaks))
+            torch.cuda.empty_cache()
+        if extras and seq == SEQ_LEN:
+            sw = guarded("intermediate 14336", lambda: train_run(
+                **common, patches="bastile", parallel="single", optimizer=args.optimizer, seq=seq, intermediate=14336,
+                steps=3, warmup=3, measure_e2e=False))
+            line.setdefault("seq_sweep", []).append(
+                {"intermediate": 14336, "note": "the reference chart's MLP width (12.0 K tokens/s on its stack)",
+                 **(_slim(sw["main"]) if "main" in sw else sw)})
+            comps = {}
+            for name, kw in (("hf_eager_cuda", dict(patches="eager", optimizer="torch")),
+                             ("liger", dict(patches="liger", optimizer="torch"))):
+                r = guarded(name, lambda kw=kw: train_run(**common, parallel="single", seq=seq,
+                                                          intermediate=args.intermediate, steps=3, warmup=3,
+                                                          measure_e2e=False, **kw))
+                if "main" in r:
+                    comps[name] = {**_slim(r["main"]), "optimizer": r["optimizer_name"], "applied": r["applied"]}
+                    comps["x_over_" + name.replace("hf_eager_cuda", "eager")] = m["tokens_per_s"] / r["main"]["tokens_per_s"]
+                else:
+                    comps[name] = r
+            comps["note"] = ("same GPU, same loop, same model shape and torch; hf_eager_cuda is what reset() restores; "
+                             "liger = liger_kernel's qwen3 patches as the reference's benchmark applies them. The "
+                             "reference's chart has bastile/pytorch = 1.24 and bastile/liger = 1.165 at seq 8192.")
+            line["comparators"] = comps
         if not args.no_cpu_baseline:
             v, times, threads = cpu_reference_sample(256)
             line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "reference",
@@ -672,11 +998,49 @@ def main():
                                               "36 x (decoder layer fwd+bwd) + (final norm + lm_head + cross-entropy fwd+bwd) "
                                               "+ AdamW scaled to 8.19 B parameters; "
                                               + json.dumps({k: round(v, 3) for k, v in times.items()})}
+    else:
+        if not args.no_per_op:
+            line["per_op"] = guarded("per_op lce", lambda: per_op_bench(peaks, only="lce"))
+            vp = guarded("vp_parity", lambda: vp_parity_check(dev, rank, world))
+            line["vp_parity"] = vp
+            if vp.get("ok") is False:
+                rc = 3
+            torch.cuda.empty_cache()
+        if extras and seq == SEQ_LEN:
+            if parallel != "ddp":
+                d = guarded("ddp", lambda: train_run(**common, patches="bastile", parallel="ddp",
+                                                     optimizer=args.optimizer, seq=seq, intermediate=args.intermediate,
+                                                     steps=3, warmup=args.warmup, measure_e2e=False))
+                if "main" in d:
+                    mine, theirs = m["first_losses"], d["main"]["first_losses"]
+                    rel = max(abs(a - b) / abs(b) for a, b in zip(mine, theirs))
+                    line["ddp"] = {**_slim(d["main"]), "parallelism": d["parallelism"],
+                                   "first_losses_main": mine, "loss_rel_diff_vs_main": rel, "tolerance": 2e-3}
+                    if rel > 2e-3:
+                        rc = rc or 4
+                else:
+                    line["ddp"] = d
+            f = guarded("fsdp-vp", lambda: train_run(
+                **common, patches="bastile", parallel="fsdp-vp", optimizer=args.optimizer, seq=seq,
+                intermediate=args.intermediate, steps=3, warmup=3, measure_e2e=False,
+                sweep=[{"seq": 32768, "steps": 2, "warmup": 2, "grad_checkpoint": True}]))
+            if "main" in f:
+                line["sharded"] = {"parallelism": f["parallelism"], "optimizer": f["optimizer_name"],
+                                   "seq_8192_per_rank": _slim(f["main"]),
+                                   "seq_32768_per_rank": [_slim(r) for r in f["sweep"]],
+                                   "note": "FSDP FULL_SHARD per decoder layer (the reference's qwen_8b_fsdp.py recipe) with "
+                                           "the lm_head rows sharded over the ranks and the fused loss vocabulary-parallel; "
+                                           "32768 tokens per rank runs with activation checkpointing; tokens/s is the "
+                                           "whole job's"}
+            else:
+                line["sharded"] = f
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if rc:
+        sys.exit(rc)
 
 
 if __name__ == "__main__":

@@ -840,8 +840,68 @@ struct Operand {
   int box_mn = 0;    // rows of the K-major box (BM, BN or BN/2)
 };
 
+// A tensor map is a pure function of (address, extents, row stride, box, element type), so an
+// encoded map can be reused for as long as the process lives, whatever has happened to the
+// memory in between.  Each host thread keeps a small direct-mapped cache of the maps it has
+// encoded (no locking; a training step asks for the same few hundred descriptions every time),
+// which takes the driver's encode call - two to four per GEMM - off the launch path.
+struct TmapKey {
+  const void* ptr;
+  int64_t mn, k, ld;
+  int kmajor, box_mn, dtype;
+  bool operator==(const TmapKey& o) const {
+    return ptr == o.ptr && mn == o.mn && k == o.k && ld == o.ld && kmajor == o.kmajor &&
+           box_mn == o.box_mn && dtype == o.dtype;
+  }
+};
+constexpr int kTmapCacheSize = 1024;  // entries per thread (power of two)
+struct TmapCache {
+  TmapKey key[kTmapCacheSize];
+  CUtensorMap map[kTmapCacheSize];
+  bool used[kTmapCacheSize];
+  uint64_t hits = 0, misses = 0;
+  TmapCache() {
+    for (int i = 0; i < kTmapCacheSize; ++i) used[i] = false;
+  }
+};
+inline TmapCache& tmap_cache() {
+  thread_local TmapCache* c = new TmapCache();  // lives as long as the thread's library use
+  return *c;
+}
+inline size_t tmap_hash(const TmapKey& k) {
+  uint64_t h = reinterpret_cast<uintptr_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+  h ^= static_cast<uint64_t>(k.mn) * 0xC2B2AE3D27D4EB4Full + static_cast<uint64_t>(k.k) * 0x165667B19E3779F9ull;
+  h ^= static_cast<uint64_t>(k.ld) * 0x27D4EB2F165667C5ull +
+       static_cast<uint64_t>(k.kmajor * 4 + k.dtype + k.box_mn * 16);
+  return static_cast<size_t>((h >> 29) & (kTmapCacheSize - 1));
+}
+inline bool& tmap_cache_enabled() {
+  static bool on = true;
+  return on;
+}
+
+int encode_tmap(CUtensorMap* tm, const Operand& o, int dtype, const char* what);
+
 // `dtype`: BT_BF16 / BT_FP16 / BT_FP32 (fp32 operands feed the tensor cores as tf32).
 inline int make_tmap(CUtensorMap* tm, const Operand& o, int dtype, const char* what) {
+  if (!tmap_cache_enabled()) return encode_tmap(tm, o, dtype, what);
+  const TmapKey key{o.ptr, o.mn, o.k, o.ld, o.kmajor, o.box_mn, dtype};
+  TmapCache& c = tmap_cache();
+  const size_t slot = tmap_hash(key);
+  if (c.used[slot] && c.key[slot] == key) {
+    ++c.hits;
+    *tm = c.map[slot];
+    return BT_OK;
+  }
+  ++c.misses;
+  if (int rc = encode_tmap(tm, o, dtype, what)) return rc;
+  c.key[slot] = key;
+  c.map[slot] = *tm;
+  c.used[slot] = true;
+  return BT_OK;
+}
+
+inline int encode_tmap(CUtensorMap* tm, const Operand& o, int dtype, const char* what) {
   const int esize = dtype == BT_FP32 ? 4 : 2;
   const int row_elems = kRowBytes / esize;  // elements in one 128-byte row of a tile
   EncodeTiledFn fn = encode_fn();
@@ -927,6 +987,22 @@ inline unsigned long long* sched_pool() {
   return pools[dev];
 }
 
+// Slot of the scheduler pool owned by (current device, stream): handed out first come, first
+// served, kept for the life of the process; -1 when all kSchedSlots are taken on this device.
+inline int sched_slot_of(cudaStream_t s) {
+  static std::mutex mu;
+  static cudaStream_t owner[64][kSchedSlots];
+  static int used[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < used[dev]; ++i)
+    if (owner[dev][i] == s) return i;
+  if (used[dev] >= kSchedSlots) return -1;
+  owner[dev][used[dev]] = s;
+  return used[dev]++;
+}
+
 template <int EPI, typename T>
 int launch_pair_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1,
                   const CUtensorMap& b1, const Params& p, cudaStream_t s) {
@@ -946,19 +1022,25 @@ int launch_pair_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMa
   Params q = p;
   q.sched = nullptr;
   if (dynamic_tiles() != 0 && pairs <= kSchedMaxPairs && p.num_tiles > pairs) {
-    // a slot of the scheduler pool, cleared on the stream ahead of the kernel
-    static std::atomic<unsigned> next_slot{0};
-    unsigned long long* pool = sched_pool();
-    if (pool == nullptr) {
-      set_error("gemm: cannot locate the tile-scheduler pool");
-      return BT_ERR_DRIVER;
-    }
-    q.sched = pool + static_cast<size_t>(next_slot.fetch_add(1) % kSchedSlots) * kSchedWords;
-    const cudaError_t me =
-        cudaMemsetAsync(q.sched, 0, sizeof(unsigned long long) * (1 + pairs * kSchedRing), s);
-    if (me != cudaSuccess) {
-      set_error("gemm: clearing the tile scheduler failed: %s", cudaGetErrorString(me));
-      return BT_ERR_LAUNCH;
+    // This stream's slot of the scheduler pool, cleared on the stream ahead of the kernel.  A
+    // slot belongs to one (device, stream): within a stream the memset is ordered after the
+    // previous launch, so it can never clear a ring that a kernel is still reading, and launches
+    // on other streams use other slots.  A stream that finds no free slot deals its tiles
+    // round-robin (q.sched stays null).
+    const int slot = sched_slot_of(s);
+    if (slot >= 0) {
+      unsigned long long* pool = sched_pool();
+      if (pool == nullptr) {
+        set_error("gemm: cannot locate the tile-scheduler pool");
+        return BT_ERR_DRIVER;
+      }
+      q.sched = pool + static_cast<size_t>(slot) * kSchedWords;
+      const cudaError_t me =
+          cudaMemsetAsync(q.sched, 0, sizeof(unsigned long long) * (1 + pairs * kSchedRing), s);
+      if (me != cudaSuccess) {
+        set_error("gemm: clearing the tile scheduler failed: %s", cudaGetErrorString(me));
+        return BT_ERR_LAUNCH;
+      }
     }
   }
   cudaLaunchConfig_t cfg = {};

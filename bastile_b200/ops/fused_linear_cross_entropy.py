@@ -44,6 +44,9 @@ _GEMM_DTYPES = (torch.bfloat16, torch.float16, torch.float32)
 DEFAULT_CHUNK = 4096
 AUTO_CHUNK_ROWS = 8192
 AUTO_CHUNK_BYTES = 3 << 30
+# a [B, T', H] input that cannot be flattened without a copy is processed batch entry by batch entry
+# when T' is at least this (shorter entries are copied once instead: many small launches cost more)
+_SEGMENT_MIN_ROWS = 1024
 
 
 def merge_shard_stats(gathered: Tensor) -> Tensor:
@@ -70,20 +73,31 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         code = _lib.dtype_code(x.dtype)
         batch_shape = x.shape[:-1]
         hdim = x.shape[-1]
-        xf = x.reshape(-1, hdim)
-        if xf.stride(-1) != 1 or (xf.shape[0] > 1 and xf.stride(0) % 8 != 0):
-            xf = xf.contiguous()
-        bt_local = xf.shape[0]
+        # The rows as a list of 2-D views with a uniform row stride.  A [B, T', H] slice of a larger
+        # [B, T, H] tensor (hidden_states[:, :-1]) cannot be flattened without a copy, but each
+        # batch entry by itself can be handed to the GEMMs with its row stride: no copy when the
+        # entries are long enough to make chunks of their own.
+        if (x.dim() == 3 and x.shape[0] > 1 and x.shape[1] >= _SEGMENT_MIN_ROWS and x.stride(-1) == 1
+                and x.stride(1) % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(0) != x.shape[1] * x.stride(1)
+                and not (group is not None and shard_tokens)):
+            segments = [x[b] for b in range(x.shape[0])]
+        else:
+            xf = x.reshape(-1, hdim)
+            if xf.stride(-1) != 1 or (xf.shape[0] > 1 and xf.stride(0) % 8 != 0):
+                xf = xf.contiguous()
+            segments = [xf]
+        bt_local = sum(seg.shape[0] for seg in segments)
         if group is not None and shard_tokens:
             # every rank brought its own rows: assemble all rows of all ranks (same count each)
+            xf = segments[0]
             world_sz = dist.get_world_size(group)
             x_all = torch.empty((world_sz * bt_local, hdim), dtype=x.dtype, device=dev)
             dist.all_gather_into_tensor(x_all, xf.contiguous(), group=group)
             t_local = target.reshape(-1).to(torch.int64).contiguous()
             t_all = torch.empty(world_sz * bt_local, dtype=torch.int64, device=dev)
             dist.all_gather_into_tensor(t_all, t_local, group=group)
-            xf, target = x_all, t_all
-        bt = xf.shape[0]
+            segments, target = [x_all], t_all
+        bt = sum(seg.shape[0] for seg in segments)
         w = weight.detach()
         if w.dtype != x.dtype:
             w = w.to(x.dtype)
@@ -102,8 +116,14 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         rows_wanted = int(chunk_size)
         if rows_wanted == DEFAULT_CHUNK and AUTO_CHUNK_ROWS * ld_logits * 2 <= AUTO_CHUNK_BYTES:
             rows_wanted = AUTO_CHUNK_ROWS
-        chunk = max(1, min(rows_wanted, bt)) if bt > 0 else 1
-        n_chunks = (bt + chunk - 1) // chunk if bt > 0 else 0
+        chunk = max(1, min(rows_wanted, max(seg.shape[0] for seg in segments))) if bt > 0 else 1
+        # (view of the rows, first global row) per chunk; chunks never straddle two segments
+        chunks, first = [], 0
+        for seg in segments:
+            for s0 in range(0, seg.shape[0], chunk):
+                chunks.append((seg[s0:s0 + chunk], first + s0))
+            first += seg.shape[0]
+        n_chunks = len(chunks) if bt > 0 else 0
         n_vt = int(lib.bt_lce_num_vtiles(vloc))
         stream = _lib.stream_ptr(dev)
         st = _lib.status_word(dev)
@@ -131,14 +151,15 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
                                               stream), "bt_lce_count_valid")
             last_rows = 0
             x_last = None
+            ld_last = hdim
             for i in range(n_chunks):
-                s = i * chunk
-                rows = min(chunk, bt - s)
-                xc = xf[s:s + rows]
+                xc, s = chunks[i]
+                rows = xc.shape[0]
+                ld_xc = xc.stride(0) if rows > 1 else hdim
                 lc = labels[s:s + rows]
                 _lib.check(lib.bt_lce_logits_stats(xc.data_ptr(), w.data_ptr(), lc.data_ptr(), logits_buf.data_ptr(),
                                                    tile_stats.data_ptr(), tgt_logit.data_ptr(), rows, hdim, vloc,
-                                                   xf.stride(0) if bt > 1 else hdim, ld_logits, int(vocab_start),
+                                                   ld_xc, ld_logits, int(vocab_start),
                                                    ignore_index, code, st.data_ptr(), stream),
                            "bt_lce_logits_stats")
                 _lib.check(lib.bt_lce_row_stats(tile_stats.data_ptr(), tgt_logit.data_ptr(), row_stats.data_ptr(),
@@ -157,11 +178,11 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
                 if i < n_chunks - 1:
                     # dW += dlogits^T[V, rows] @ x_chunk[rows, H], fp32 accumulation across chunks
                     _lib.check(lib.bt_gemm(logits_buf.data_ptr(), xc.data_ptr(), dw_acc.data_ptr(), vloc, hdim, rows,
-                                           ld_logits, xf.stride(0) if bt > 1 else hdim, hdim, 0, 0, code,
+                                           ld_logits, ld_xc, hdim, 0, 0, code,
                                            _lib.BT_FP32, dw_acc.data_ptr() if i > 0 else None, hdim, None,
                                            st.data_ptr(), stream), "bt_gemm(dW)")
                 else:
-                    last_rows, x_last = rows, xc
+                    last_rows, x_last, ld_last = rows, xc, ld_xc
             _lib.check(lib.bt_lce_reduce_loss(loss_row.data_ptr(), bt, scal[1:].data_ptr() if reduction == "mean"
                                               else None, scal[2:].data_ptr(), stream), "bt_lce_reduce_loss")
         if group is not None and bt > 0:
@@ -173,10 +194,9 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             else:
                 dist.all_reduce(dx, group=group)
 
-        ctx.save_for_backward(dx, w, logits_buf, x_last if x_last is not None else xf[:0],
+        ctx.save_for_backward(dx, w, logits_buf, x_last if x_last is not None else segments[0][:0],
                               dw_acc if dw_acc is not None else scal[:0])
-        ctx.meta = (batch_shape, hdim, vloc, last_rows, ld_logits, x.dtype, weight.dtype, n_chunks,
-                    xf.stride(0) if bt > 1 else hdim)
+        ctx.meta = (batch_shape, hdim, vloc, last_rows, ld_logits, x.dtype, weight.dtype, n_chunks, ld_last)
         ctx.grad_hidden_scale = float(grad_hidden_scale)
         return scal[2].clone()
 
@@ -241,10 +261,10 @@ def fused_linear_cross_entropy(hidden_states: Tensor, weight: Tensor, target: Te
     ``bastile_b200._lib.check_all_status()`` turns into an exception.  With a vocabulary-parallel
     group pass ``vocab_size`` (rows of the full ``lm_head``) to have labels checked.
     """
-    if hidden_states.ndim == 3:
-        hidden_states = hidden_states.reshape(-1, hidden_states.shape[-1])
-        target = target.reshape(-1)
     if bias is not None:
+        if hidden_states.ndim == 3:
+            hidden_states = hidden_states.reshape(-1, hidden_states.shape[-1])
+            target = target.reshape(-1)
         if vocab_parallel_group is not None:
             raise ValueError("fused_linear_cross_entropy: bias is not supported with a vocabulary-parallel group")
         logits = F.linear(hidden_states, weight, bias)
@@ -292,17 +312,19 @@ def bastile_lce_forward(self, input_ids=None, attention_mask=None, position_ids=
     hidden_states = outputs[0]
     logits = loss = None
     if self.training and labels is not None:
-        # Drop the last position / first label; the fused loss takes row strides,
-        # so the shifted hidden states are only copied when batch > 1 makes the
-        # flattened view non-uniform.
-        shift_hidden = hidden_states[..., :-1, :]
-        shift_labels = labels[..., 1:]
+        # Next-token labels for EVERY position: position t is scored against labels[t + 1] and the
+        # last position of each sequence against ignore_index.  Those rows add nothing to the loss,
+        # to n_valid or to any gradient, so the result is that of the reference's
+        # hidden[..., :-1, :].contiguous() / labels[..., 1:].contiguous() (:483-492) - without either
+        # copy at any batch size, and without the zero-padded gradient that autograd's backward of
+        # the slice would allocate: d(hidden) comes back for all positions at once.
+        shift_labels = F.pad(labels[..., 1:], (0, 1), value=-100)
         vp = _VOCAB_PARALLEL
         if vp["group"] is None:
-            loss = fused_linear_cross_entropy(shift_hidden, self.lm_head.weight, shift_labels,
+            loss = fused_linear_cross_entropy(hidden_states, self.lm_head.weight, shift_labels,
                                               bias=getattr(self.lm_head, "bias", None), ignore_index=-100)
         else:
-            loss = fused_linear_cross_entropy(shift_hidden, self.lm_head.weight, shift_labels, ignore_index=-100,
+            loss = fused_linear_cross_entropy(hidden_states, self.lm_head.weight, shift_labels, ignore_index=-100,
                                               vocab_parallel_group=vp["group"], vocab_start=vp["vocab_start"],
                                               shard_tokens=True, grad_hidden_scale=vp["grad_hidden_scale"],
                                               vocab_size=vp["vocab_size"])

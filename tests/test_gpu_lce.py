@@ -309,3 +309,32 @@ def test_lce_out_of_range_label_sets_status_bit():
         with pytest.raises(_lib.BastileB200Error, match="label"):
             _lib.check_all_status()
         _lib.check_all_status()  # the word was cleared by the failed check
+
+
+def test_lce_batched_slice_runs_without_flattening_copy():
+    """hidden[:, :-1] of a [B, T, H] tensor with B > 1 cannot be flattened without a copy; with
+    entries of >= 1024 rows the op walks the batch entries with their row stride instead (chunks
+    never straddle two entries).  Results must equal the oracle's on the flattened rows, and the
+    short-entry case (which copies) must agree too."""
+    from bastile_b200.ops import fused_linear_cross_entropy as mod
+    from bastile_b200.ops.fused_linear_cross_entropy import fused_linear_cross_entropy
+
+    torch.manual_seed(13)
+    for b, t, chunk in ((2, 1101, 4096), (3, 1030, 512), (4, 65, 4096)):
+        h, v = 128, 777
+        full = torch.randn(b, t, h, device=DEV, dtype=torch.bfloat16)
+        x = full[:, :-1].detach().requires_grad_(True)  # a leaf that is itself a non-flattenable slice
+        assert x.stride(0) != x.shape[1] * x.stride(1)
+        w = (torch.randn(v, h, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_(True)
+        y = torch.randint(0, v, (b, t - 1), device=DEV)
+        y[:, ::13] = -100
+        assert (t - 1 >= mod._SEGMENT_MIN_ROWS) == (t > 1000)
+        loss = fused_linear_cross_entropy(x, w, y, chunk_size=chunk)
+        loss.backward()
+        l_ref, dx_ref, dw_ref = oracle.lce_fwd_bwd(x.detach().float().cpu().numpy().reshape(-1, h),
+                                                   w.detach().float().cpu().numpy(), y.cpu().numpy().reshape(-1),
+                                                   -100, "mean")
+        assert abs(loss.item() - float(l_ref)) <= 2e-3 * abs(float(l_ref))
+        assert x.grad.shape == x.shape
+        assert_close(x.grad.reshape(-1, h), dx_ref, what=f"dx b={b}", rtol=2e-2, atol=2e-2 * float(np.abs(dx_ref).max()))
+        assert_close(w.grad, dw_ref, what=f"dw b={b}", rtol=2e-2, atol=2e-2 * float(np.abs(dw_ref).max()))

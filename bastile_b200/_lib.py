@@ -30,7 +30,11 @@ class GemmDesc(ctypes.Structure):
                 ("a_kmajor", ctypes.c_int32), ("b_kmajor", ctypes.c_int32),
                 ("in_dtype", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
                 ("addend", c_void_p), ("ld_addend", c_int64), ("addend_t", c_void_p), ("ld_addend_t", c_int64),
-                ("alpha", c_void_p)]
+                ("alpha", c_void_p),
+                ("A2", c_void_p), ("lda2", c_int64), ("K2", c_int64),
+                ("a_split", ctypes.c_int32), ("d_split", ctypes.c_int32), ("M0", c_int64), ("M1", c_int64),
+                ("D1", c_void_p), ("D2", c_void_p), ("ldd1", c_int64), ("ldd2", c_int64), ("N0", c_int64),
+                ("N1", c_int64)]
 
 
 I64x3 = c_int64 * 3

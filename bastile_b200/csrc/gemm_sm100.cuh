@@ -72,9 +72,15 @@ enum : int { EPI_PLAIN = 0, EPI_SWIGLU_FWD = 1, EPI_SWIGLU_BWD = 2, EPI_LCE = 3 
 // Status-word bits set when a bounded wait runs out.
 enum : int { ST_PRODUCER = 1, ST_MMA_ACC = 2, ST_MMA_FULL = 4, ST_EPILOGUE = 8 };
 
+// How the A operand is assembled from up to three tensors (one B tensor in both cases).
+enum : int { A_WHOLE = 0, A_SPLIT_K = 1, A_SPLIT_M = 2 };
+
 struct Params {
   int M, N;        // output extent; with dual_b, N is the width of ONE of the two outputs
   int K0, K1;      // contraction lengths of pair 0 and pair 1 (K1 = 0: single pair)
+  int K2;          // A_SPLIT_K: contraction length of the third A tensor (B spans K0 + K1 + K2)
+  int a_split;     // A_WHOLE, A_SPLIT_K or A_SPLIT_M
+  int m_seg0, m_seg1;  // A_SPLIT_M: rows [0, m_seg0) come from A0, the next m_seg1 from A1, the rest from A2
   int tiles_m, tiles_n, num_tiles;
   int group_m;     // rasterisation: row-tiles walked per column-tile before moving on
   int a_kmajor, b_kmajor, dual_b;
@@ -88,6 +94,12 @@ struct Params {
   // --- plain epilogue: out = T(alpha * (acc + addend))
   void* out;
   int64_t ldo;
+  // plain epilogue, result split along N over three tensors (n_seg0 > 0): columns [0, n_seg0) go
+  // to out, the next n_seg1 to out1, the rest to out2; segment widths are whole tiles
+  void* out1;
+  void* out2;
+  int64_t ldo1, ldo2;
+  int n_seg0, n_seg1;
   int out_fp32;
   int vec_ok;  // rows of every global tensor the epilogue touches are 16-byte aligned
   const float* addend;
@@ -193,11 +205,29 @@ __device__ __forceinline__ void epi_plain(const Params& p, uint32_t taddr, int64
                                           int half) {
   const float alpha = p.alpha != nullptr ? __ldg(p.alpha) : 1.0f;
   const bool row_ok = row < p.M;
+  // where this tile's columns live: one result tensor, or one of three side by side
+  void* out = p.out;
+  int64_t ldo = p.ldo;
+  int col_shift = 0, n_end = p.N;
+  if (p.n_seg0 > 0) {
+    if (n0 < p.n_seg0) {
+      n_end = p.n_seg0;
+    } else if (n0 < p.n_seg0 + p.n_seg1) {
+      out = p.out1;
+      ldo = p.ldo1;
+      col_shift = p.n_seg0;
+      n_end = p.n_seg0 + p.n_seg1;
+    } else {
+      out = p.out2;
+      ldo = p.ldo2;
+      col_shift = p.n_seg0 + p.n_seg1;
+    }
+  }
 #pragma unroll 1
   for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
     float v[32], res[32];
     const int col0 = n0 + c * 32;
-    const int valid = p.N - col0;
+    const int valid = n_end - col0;
     const bool add_res = p.addend_t != nullptr && row_ok && valid > 0;
     if (add_res)  // in flight while the accumulator chunk is fetched
       load_row32<T>(static_cast<const T*>(p.addend_t) + row * p.ld_add_t + col0, res, valid,
@@ -228,9 +258,9 @@ __device__ __forceinline__ void epi_plain(const Params& p, uint32_t taddr, int64
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] *= alpha;
       if (p.out_fp32)
-        store_row32_f32(static_cast<float*>(p.out) + row * p.ldo + col0, v, valid, p.vec_ok);
+        store_row32_f32(static_cast<float*>(out) + row * ldo + (col0 - col_shift), v, valid, p.vec_ok);
       else
-        store_row32<T>(static_cast<T*>(p.out) + row * p.ldo + col0, v, valid, p.vec_ok);
+        store_row32<T>(static_cast<T*>(out) + row * ldo + (col0 - col_shift), v, valid, p.vec_ok);
     }
   }
 }
@@ -354,12 +384,52 @@ __device__ __forceinline__ void epi_lce(const Params& p, uint32_t taddr, int64_t
   }
 }
 
+// Which tensor map, and which coordinates inside it, hold the A tile of rows m0.. for k-block kb.
+struct ASource {
+  const CUtensorMap* map;
+  int k, m;
+};
+__device__ __forceinline__ ASource a_source(const Params& p, const CUtensorMap* a0,
+                                            const CUtensorMap* a1, const CUtensorMap* a2, int kb,
+                                            int nkb0, int nkb1, int m0, int kbk) {
+  ASource r;
+  if (p.a_split == A_SPLIT_M) {
+    // the M extent is three tensors stacked (segment lengths are multiples of the tile height)
+    r.k = kb * kbk;
+    if (m0 < p.m_seg0) {
+      r.map = a0;
+      r.m = m0;
+    } else if (m0 < p.m_seg0 + p.m_seg1) {
+      r.map = a1;
+      r.m = m0 - p.m_seg0;
+    } else {
+      r.map = a2;
+      r.m = m0 - p.m_seg0 - p.m_seg1;
+    }
+    return r;
+  }
+  // the K extent is one tensor, two operand pairs (A_WHOLE with K1 > 0) or three A tensors side
+  // by side against one B tensor (A_SPLIT_K; K0 and K1 are whole numbers of k-blocks)
+  r.m = m0;
+  if (kb < nkb0) {
+    r.map = a0;
+    r.k = kb * kbk;
+  } else if (kb < nkb0 + nkb1) {
+    r.map = a1;
+    r.k = (kb - nkb0) * kbk;
+  } else {
+    r.map = a2;
+    r.k = (kb - nkb0 - nkb1) * kbk;
+  }
+  return r;
+}
+
 // --------------------------------------------------------------------- kernel
 template <int EPI, typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
             const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
-            const Params p) {
+            const __grid_constant__ CUtensorMap tmA2, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -386,8 +456,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmA0);
     ptx::prefetch_tensormap(&tmB0);
-    if (p.K1 > 0 || p.dual_b) ptx::prefetch_tensormap(&tmB1);
-    if (p.K1 > 0) ptx::prefetch_tensormap(&tmA1);
+    if ((p.K1 > 0 && p.a_split == A_WHOLE) || p.dual_b) ptx::prefetch_tensormap(&tmB1);
+    if (p.K1 > 0 || p.a_split != A_WHOLE) ptx::prefetch_tensormap(&tmA1);
+    if (p.a_split != A_WHOLE) ptx::prefetch_tensormap(&tmA2);
   }
   if (warp == 1) {
     ptx::tmem_alloc(tmem_slot, kTmemCols);
@@ -401,7 +472,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
   constexpr int kBk = Geo<T>::kBk, kMnBox = Geo<T>::kMnBox, kBoxBytes = Geo<T>::kBoxBytes;
   const int nkb0 = (p.K0 + kBk - 1) / kBk;
   const int nkb1 = (p.K1 + kBk - 1) / kBk;
-  const int nkb = nkb0 + nkb1;
+  const int nkb = nkb0 + nkb1 + (p.K2 + kBk - 1) / kBk;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -420,28 +491,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
             break;
           }
           ptx::mbar_arrive_expect_tx(&full[stage], kStageBytes);
-          const bool second = kb >= nkb0;
-          const int k0 = (second ? kb - nkb0 : kb) * kBk;
-          const CUtensorMap* ta = second ? &tmA1 : &tmA0;
+          const ASource as = a_source(p, &tmA0, &tmA1, &tmA2, kb, nkb0, nkb1, m0, kBk);
+          const bool second = p.a_split == A_WHOLE && kb >= nkb0;
+          const int kb_b = second ? (kb - nkb0) * kBk : kb * kBk;  // A_SPLIT_K: B's K range runs on
+          const CUtensorMap* ta = as.map;
           const CUtensorMap* tb = second ? &tmB1 : &tmB0;
           uint8_t* sa = smem + stage * kStageBytes;
           uint8_t* sb = sa + kABytes;
           if (p.a_kmajor) {
-            ptx::tma_load_2d(sa, ta, k0, m0, &full[stage]);
+            ptx::tma_load_2d(sa, ta, as.k, as.m, &full[stage]);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / kMnBox; ++j)
-              ptx::tma_load_2d(sa + j * kBoxBytes, ta, m0 + j * kMnBox, k0, &full[stage]);
+              ptx::tma_load_2d(sa + j * kBoxBytes, ta, as.m + j * kMnBox, as.k, &full[stage]);
           }
           if (p.dual_b) {
-            ptx::tma_load_2d(sb, &tmB0, k0, n0, &full[stage]);
-            ptx::tma_load_2d(sb + kBBytes / 2, &tmB1, k0, n0, &full[stage]);
+            ptx::tma_load_2d(sb, &tmB0, kb_b, n0, &full[stage]);
+            ptx::tma_load_2d(sb + kBBytes / 2, &tmB1, kb_b, n0, &full[stage]);
           } else if (p.b_kmajor) {
-            ptx::tma_load_2d(sb, tb, k0, n0, &full[stage]);
+            ptx::tma_load_2d(sb, tb, kb_b, n0, &full[stage]);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / kMnBox; ++j)
-              ptx::tma_load_2d(sb + j * kBoxBytes, tb, n0 + j * kMnBox, k0, &full[stage]);
+              ptx::tma_load_2d(sb + j * kBoxBytes, tb, n0 + j * kMnBox, kb_b, &full[stage]);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -603,7 +675,7 @@ template <int EPI, typename T>
 __global__ void __launch_bounds__(kThreadsPair, 1)
 gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
                  const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
-                 const Params p) {
+                 const __grid_constant__ CUtensorMap tmA2, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -632,8 +704,9 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmA0);
     ptx::prefetch_tensormap(&tmB0);
-    if (p.K1 > 0 || p.dual_b) ptx::prefetch_tensormap(&tmB1);
-    if (p.K1 > 0) ptx::prefetch_tensormap(&tmA1);
+    if ((p.K1 > 0 && p.a_split == A_WHOLE) || p.dual_b) ptx::prefetch_tensormap(&tmB1);
+    if (p.K1 > 0 || p.a_split != A_WHOLE) ptx::prefetch_tensormap(&tmA1);
+    if (p.a_split != A_WHOLE) ptx::prefetch_tensormap(&tmA2);
   }
   if (warp == 1) {
     ptx::tmem_alloc_pair(tmem_slot, kTmemCols);
@@ -648,7 +721,7 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
   constexpr int kBk = Geo<T>::kBk, kMnBox = Geo<T>::kMnBox, kBoxBytes = Geo<T>::kBoxBytes;
   const int nkb0 = (p.K0 + kBk - 1) / kBk;
   const int nkb1 = (p.K1 + kBk - 1) / kBk;
-  const int nkb = nkb0 + nkb1;
+  const int nkb = nkb0 + nkb1 + (p.K2 + kBk - 1) / kBk;
   const int pair = blockIdx.x >> 1;
   const int npairs = gridDim.x >> 1;
 
@@ -689,20 +762,20 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
             ok = false;
             break;
           }
-          const bool second = kb >= nkb0;
-          const int k0 = (second ? kb - nkb0 : kb) * kBk;
+          const bool second = p.a_split == A_WHOLE && kb >= nkb0;
           uint8_t* sa = smem + stage * kStageBytes2;
           if (do_a) {
             if (leader) ptx::mbar_arrive_expect_tx(&full[stage], 2 * kStageBytes2);
-            const CUtensorMap* ta = second ? &tmA1 : &tmA0;
+            const ASource as = a_source(p, &tmA0, &tmA1, &tmA2, kb, nkb0, nkb1, m0, kBk);
             if (p.a_kmajor) {
-              ptx::tma_load_2d_pair(sa, ta, k0, m0, &full[stage]);
+              ptx::tma_load_2d_pair(sa, as.map, as.k, as.m, &full[stage]);
             } else {
 #pragma unroll
               for (int j = 0; j < BM / kMnBox; ++j)
-                ptx::tma_load_2d_pair(sa + j * kBoxBytes, ta, m0 + j * kMnBox, k0, &full[stage]);
+                ptx::tma_load_2d_pair(sa + j * kBoxBytes, as.map, as.m + j * kMnBox, as.k, &full[stage]);
             }
           } else {
+            const int k0 = second ? (kb - nkb0) * kBk : kb * kBk;  // A_SPLIT_K: B's K range runs on
             const CUtensorMap* tb = p.dual_b ? (rank ? &tmB1 : &tmB0) : (second ? &tmB1 : &tmB0);
             uint8_t* sb = sa + kABytes;
             if (p.b_kmajor) {
@@ -948,7 +1021,7 @@ inline int encode_tmap(CUtensorMap* tm, const Operand& o, int dtype, const char*
 
 template <int EPI, typename T>
 int launch_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1,
-             const CUtensorMap& b1, const Params& p, cudaStream_t s) {
+             const CUtensorMap& b1, const CUtensorMap& a2, const Params& p, cudaStream_t s) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   auto* kern = gemm_kernel<EPI, T>;
@@ -961,7 +1034,7 @@ int launch_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1
     return BT_ERR_LAUNCH;
   }
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  kern<<<grid, kThreads, kSmemBytes, s>>>(a0, b0, a1, b1, p);
+  kern<<<grid, kThreads, kSmemBytes, s>>>(a0, b0, a1, b1, a2, p);
   BT_CHECK_LAUNCH("gemm_kernel");
   return BT_OK;
 }
@@ -1005,7 +1078,7 @@ inline int sched_slot_of(cudaStream_t s) {
 
 template <int EPI, typename T>
 int launch_pair_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1,
-                  const CUtensorMap& b1, const Params& p, cudaStream_t s) {
+                  const CUtensorMap& b1, const CUtensorMap& a2, const Params& p, cudaStream_t s) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   auto* kern = gemm_kernel_pair<EPI, T>;
@@ -1055,7 +1128,7 @@ int launch_pair_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMa
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a0, b0, a1, b1, q);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a0, b0, a1, b1, a2, q);
   if (e != cudaSuccess) {
     set_error("gemm_kernel_pair: %s", cudaGetErrorString(e));
     return BT_ERR_LAUNCH;
@@ -1071,9 +1144,10 @@ inline int& pair_mode() {
 
 // Describes one GEMM launch; pair 1 and b1 are optional.
 struct Launch {
-  Operand a0, b0, a1, b1;
+  Operand a0, b0, a1, b1, a2;
   bool dual_b = false;    // b1 is the second half of the B tile (same K range as pair 0)
   bool two_pairs = false; // (a1, b1) is a second contraction into the same accumulator
+  int a_split = A_WHOLE;  // A_SPLIT_K / A_SPLIT_M: A is (a0, a1, a2), B is b0 alone
   int dtype = BT_BF16;    // storage of the operands: BT_BF16, BT_FP16 or BT_FP32 (tf32 math)
   Params p{};
 };
@@ -1097,6 +1171,34 @@ int launch(Launch& L, cudaStream_t s) {
   const int n_tile = L.dual_b ? BN / 2 : BN;
   p.K0 = static_cast<int>(L.a0.k);
   p.K1 = L.two_pairs ? static_cast<int>(L.a1.k) : 0;
+  p.K2 = 0;
+  p.a_split = L.a_split;
+  p.m_seg0 = p.m_seg1 = 0;
+  if (L.a_split != A_WHOLE) {
+    const int kbk = kRowBytes / (L.dtype == BT_FP32 ? 4 : 2);
+    const int tile_m = pair ? 2 * BM : BM;
+    if (L.two_pairs || L.dual_b || L.a1.kmajor != L.a0.kmajor || L.a2.kmajor != L.a0.kmajor) {
+      set_error("gemm: a split A operand excludes the other main-loop modes and needs one layout");
+      return BT_ERR_ARG;
+    }
+    if (L.a_split == A_SPLIT_K) {
+      if (L.a0.k % kbk != 0 || L.a1.k % kbk != 0 || L.a1.k <= 0 || L.a2.k <= 0 ||
+          L.b0.k != L.a0.k + L.a1.k + L.a2.k) {
+        set_error("gemm: K-split A needs K and K1 in whole k-blocks of %d and B spanning K + K1 + K2", kbk);
+        return BT_ERR_ARG;
+      }
+      p.K1 = static_cast<int>(L.a1.k);
+      p.K2 = static_cast<int>(L.a2.k);
+    } else {
+      if (L.a0.mn % tile_m != 0 || L.a1.mn % tile_m != 0 || L.a1.mn <= 0 || L.a2.mn <= 0 ||
+          L.a0.mn + L.a1.mn + L.a2.mn != p.M || L.a1.k != L.a0.k || L.a2.k != L.a0.k) {
+        set_error("gemm: M-split A needs segments in whole tiles of %d rows that add up to M", tile_m);
+        return BT_ERR_ARG;
+      }
+      p.m_seg0 = static_cast<int>(L.a0.mn);
+      p.m_seg1 = static_cast<int>(L.a1.mn);
+    }
+  }
   p.tiles_m = static_cast<int>(ceil_div(p.M, pair ? 2 * BM : BM));
   p.tiles_n = static_cast<int>(ceil_div(p.N, n_tile));
   const int64_t nt = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
@@ -1125,13 +1227,19 @@ int launch(Launch& L, cudaStream_t s) {
   const int b_box = pair ? BN / 2 : n_tile;
   L.a0.box_mn = BM;
   L.b0.box_mn = b_box;
-  CUtensorMap ta0, tb0, ta1, tb1;
+  CUtensorMap ta0, tb0, ta1, tb1, ta2;
   int rc;
   if ((rc = make_tmap(&ta0, L.a0, L.dtype, "gemm A")) != BT_OK) return rc;
   if ((rc = make_tmap(&tb0, L.b0, L.dtype, "gemm B")) != BT_OK) return rc;
   ta1 = ta0;
   tb1 = tb0;
-  if (L.two_pairs) {
+  ta2 = ta0;
+  if (L.a_split != A_WHOLE) {
+    L.a1.box_mn = BM;
+    L.a2.box_mn = BM;
+    if ((rc = make_tmap(&ta1, L.a1, L.dtype, "gemm A1")) != BT_OK) return rc;
+    if ((rc = make_tmap(&ta2, L.a2, L.dtype, "gemm A2")) != BT_OK) return rc;
+  } else if (L.two_pairs) {
     if (L.a1.kmajor != L.a0.kmajor || L.b1.kmajor != L.b0.kmajor) {
       set_error("gemm: both operand pairs must share their layouts");
       return BT_ERR_ARG;
@@ -1150,15 +1258,15 @@ int launch(Launch& L, cudaStream_t s) {
   }
   if (pair) {
     switch (L.dtype) {
-      case BT_BF16: return launch_pair_t<EPI, __nv_bfloat16>(ta0, tb0, ta1, tb1, p, s);
-      case BT_FP16: return launch_pair_t<EPI, __half>(ta0, tb0, ta1, tb1, p, s);
-      default: return launch_pair_t<EPI, float>(ta0, tb0, ta1, tb1, p, s);
+      case BT_BF16: return launch_pair_t<EPI, __nv_bfloat16>(ta0, tb0, ta1, tb1, ta2, p, s);
+      case BT_FP16: return launch_pair_t<EPI, __half>(ta0, tb0, ta1, tb1, ta2, p, s);
+      default: return launch_pair_t<EPI, float>(ta0, tb0, ta1, tb1, ta2, p, s);
     }
   }
   switch (L.dtype) {
-    case BT_BF16: return launch_t<EPI, __nv_bfloat16>(ta0, tb0, ta1, tb1, p, s);
-    case BT_FP16: return launch_t<EPI, __half>(ta0, tb0, ta1, tb1, p, s);
-    default: return launch_t<EPI, float>(ta0, tb0, ta1, tb1, p, s);
+    case BT_BF16: return launch_t<EPI, __nv_bfloat16>(ta0, tb0, ta1, tb1, ta2, p, s);
+    case BT_FP16: return launch_t<EPI, __half>(ta0, tb0, ta1, tb1, ta2, p, s);
+    default: return launch_t<EPI, float>(ta0, tb0, ta1, tb1, ta2, p, s);
   }
 }
 

@@ -35,18 +35,44 @@ int check_dims(const char* what, int64_t m, int64_t n, int64_t k) {
   return BT_OK;
 }
 
+// A operand given as three tensors (bt_gemm_desc.a_split)
+struct ASplit {
+  int mode;
+  const void* A2;
+  int64_t lda2, K2, M0, M1;
+};
+// result given as three tensors side by side along N (bt_gemm_desc.d_split)
+struct DSplit {
+  void* D1;
+  void* D2;
+  int64_t ldd1, ldd2, N0, N1;
+};
+
 // out[M,N] = T(alpha * (op(A) op(B) + addend))
 int plain_gemm(const void* A, bool a_kmajor, int64_t lda, const void* B, bool b_kmajor, int64_t ldb,
                const void* A1, int64_t lda1, const void* B1, int64_t ldb1, int64_t K1, void* D,
                int64_t ldd, int64_t M, int64_t N, int64_t K, int dtype, bool out_fp32,
                const float* addend, int64_t ld_add, const float* alpha, int32_t* status,
-               cudaStream_t s, const void* addend_t = nullptr, int64_t ld_add_t = 0) {
+               cudaStream_t s, const void* addend_t = nullptr, int64_t ld_add_t = 0,
+               const ASplit* split = nullptr, const DSplit* dsplit = nullptr) {
   Launch L;
   L.dtype = dtype;
   out_fp32 = out_fp32 || dtype == BT_FP32;
   L.a0 = operand(A, a_kmajor, M, K, lda);
   L.b0 = operand(B, b_kmajor, N, K, ldb);
-  if (A1 != nullptr) {
+  if (split != nullptr && split->mode == gemm::A_SPLIT_K) {
+    // A = [A | A1 | A2] along K, one B spanning the whole contraction
+    L.a_split = gemm::A_SPLIT_K;
+    L.a1 = operand(A1, a_kmajor, M, K1, lda1);
+    L.a2 = operand(split->A2, a_kmajor, M, split->K2, split->lda2);
+    L.b0 = operand(B, b_kmajor, N, K + K1 + split->K2, ldb);
+  } else if (split != nullptr && split->mode == gemm::A_SPLIT_M) {
+    // the rows of op(A) are three tensors stacked along M
+    L.a_split = gemm::A_SPLIT_M;
+    L.a0 = operand(A, a_kmajor, split->M0, K, lda);
+    L.a1 = operand(A1, a_kmajor, split->M1, K, lda1);
+    L.a2 = operand(split->A2, a_kmajor, M - split->M0 - split->M1, K, split->lda2);
+  } else if (A1 != nullptr) {
     L.two_pairs = true;
     L.a1 = operand(A1, a_kmajor, M, K1, lda1);
     L.b1 = operand(B1, b_kmajor, N, K1, ldb1);
@@ -64,6 +90,16 @@ int plain_gemm(const void* A, bool a_kmajor, int64_t lda, const void* B, bool b_
   L.p.ld_add_t = ld_add_t;
   L.p.vec_ok = rows_aligned(D, ldd, out_fp32 ? 4 : 2) && rows_aligned(addend, ld_add, 4) &&
                rows_aligned(addend_t, ld_add_t, esize(dtype));
+  if (dsplit != nullptr) {
+    L.p.out1 = dsplit->D1;
+    L.p.out2 = dsplit->D2;
+    L.p.ldo1 = dsplit->ldd1;
+    L.p.ldo2 = dsplit->ldd2;
+    L.p.n_seg0 = static_cast<int>(dsplit->N0);
+    L.p.n_seg1 = static_cast<int>(dsplit->N1);
+    L.p.vec_ok = L.p.vec_ok && rows_aligned(dsplit->D1, dsplit->ldd1, out_fp32 ? 4 : 2) &&
+                 rows_aligned(dsplit->D2, dsplit->ldd2, out_fp32 ? 4 : 2);
+  }
   return gemm::launch<gemm::EPI_PLAIN>(L, s);
 }
 
@@ -107,19 +143,40 @@ extern "C" int bt_gemm_ex(const bt_gemm_desc* d, int32_t* status, void* stream) 
                "gemm_ex: result must have the operand dtype or be fp32");
   BT_CHECK_ARG(d->A && d->B && d->D, "gemm_ex: null pointer");
   if (int rc = check_dims("gemm_ex", d->M, d->N, d->K)) return rc;
+  BT_CHECK_ARG(d->a_split >= 0 && d->a_split <= 2, "gemm_ex: a_split must be 0, 1 or 2");
+  ASplit split{d->a_split, d->A2, d->lda2, d->K2, d->M0, d->M1};
+  if (d->a_split != 0) {
+    BT_CHECK_ARG(d->A1 != nullptr && d->A2 != nullptr && d->B1 == nullptr,
+                 "gemm_ex: a split A operand needs A, A1 and A2 and takes no B1");
+    if (d->a_split == 1) {
+      if (int rc = check_dims("gemm_ex (K-split)", d->M, d->K1, d->K2)) return rc;
+    } else {
+      BT_CHECK_ARG(d->M0 > 0 && d->M1 > 0 && d->M0 + d->M1 < d->M, "gemm_ex: M-split needs 0 < M0, M1 and M0 + M1 < M");
+    }
+  }
+  DSplit dsplit{d->D1, d->D2, d->ldd1, d->ldd2, d->N0, d->N1};
+  if (d->d_split != 0) {
+    BT_CHECK_ARG(d->D1 != nullptr && d->D2 != nullptr && d->addend == nullptr && d->addend_t == nullptr,
+                 "gemm_ex: a split result needs D, D1 and D2 and takes no addend");
+    BT_CHECK_ARG(d->N0 > 0 && d->N1 > 0 && d->N0 + d->N1 < d->N && d->N0 % 256 == 0 && d->N1 % 256 == 0,
+                 "gemm_ex: split result needs 0 < N0, N1 in multiples of 256 with N0 + N1 < N");
+    BT_CHECK_ARG(d->ldd >= d->N0 && d->ldd1 >= d->N1 && d->ldd2 >= d->N - d->N0 - d->N1,
+                 "gemm_ex: split result stride too small");
+  }
   const bool second = d->A1 != nullptr;
-  if (second) {
+  if (second && d->a_split == 0) {
     BT_CHECK_ARG(d->B1 != nullptr, "gemm_ex: second product has A1 but no B1");
     if (int rc = check_dims("gemm_ex (second product)", d->M, d->N, d->K1)) return rc;
   }
-  BT_CHECK_ARG(d->ldd >= d->N && (d->addend == nullptr || d->ld_addend >= d->N) &&
+  BT_CHECK_ARG((d->d_split != 0 || d->ldd >= d->N) && (d->addend == nullptr || d->ld_addend >= d->N) &&
                    (d->addend_t == nullptr || d->ld_addend_t >= d->N),
                "gemm_ex: result / addend stride too small");
   return plain_gemm(d->A, d->a_kmajor != 0, d->lda, d->B, d->b_kmajor != 0, d->ldb,
                     second ? d->A1 : nullptr, d->lda1, second ? d->B1 : nullptr, d->ldb1,
                     second ? d->K1 : 0, d->D, d->ldd, d->M, d->N, d->K, d->in_dtype,
                     d->out_dtype == BT_FP32, d->addend, d->ld_addend, d->alpha, status,
-                    static_cast<cudaStream_t>(stream), d->addend_t, d->ld_addend_t);
+                    static_cast<cudaStream_t>(stream), d->addend_t, d->ld_addend_t,
+                    d->a_split != 0 ? &split : nullptr, d->d_split != 0 ? &dsplit : nullptr);
 }
 
 extern "C" int bt_mlp_fwd(const void* x, const void* wg, const void* wu, const void* wd, void* gate,

@@ -240,8 +240,12 @@ _GEMM_DTYPES = (torch.bfloat16, torch.float16, torch.float32)
 # How the patched attention forward runs the q/k/v/o projections (install(projections=...)):
 #   "off": nn.Linear;  "dx": nn.Linear's GEMMs for the outputs and the weight gradients, but the
 #   shared input gradient dX = dQ Wq + dK Wk + dV Wv from two bt_gemm_ex launches (no accumulation
-#   passes);  "all": every product of q/k/v/o_proj on bt_gemm_ex.
-PROJECTION_MODES = ("off", "dx", "all")
+#   passes);  "all": every product of q/k/v/o_proj on bt_gemm_ex;  "qkv": the q, k and v
+#   projections as ONE product each way (forward, input gradient, weight gradients: three launches
+#   instead of nine GEMMs and two accumulation passes) wherever the three weights lie one after the
+#   other in memory (stack_qkv_weights), o_proj on nn.Linear; layers whose weights are not stacked
+#   run as in "off".
+PROJECTION_MODES = ("off", "dx", "all", "qkv")
 _projection_mode = "off"
 
 
@@ -359,6 +363,143 @@ class SharedInputLinearFunction(torch.autograd.Function):
         return (None, dx, *dws)
 
 
+def _stacked(wq, wk, wv) -> bool:
+    """True when the three [n_i, k] weights lie one after the other in memory, in this order."""
+    es = wq.element_size()
+    return (wq.dtype == wk.dtype == wv.dtype and wq.is_contiguous() and wk.is_contiguous() and wv.is_contiguous()
+            and wq.shape[1] == wk.shape[1] == wv.shape[1]
+            and wk.data_ptr() == wq.data_ptr() + wq.numel() * es and wv.data_ptr() == wk.data_ptr() + wk.numel() * es)
+
+
+@torch.no_grad()
+def stack_qkv_weights(model) -> int:
+    """Move ``q_proj.weight``, ``k_proj.weight`` and ``v_proj.weight`` of every attention block of
+    ``model`` into one ``[nq + nk + nv, hidden]`` buffer per block (the parameters stay three
+    separate ``nn.Parameter`` objects with unchanged names, shapes and values: only their storage
+    moves).  ``apply(fused_layers=True, gemm_projections="qkv")`` then runs the three projections
+    as one product each way.  Call it after the model is on its device and before the optimizer
+    and any data-parallel wrapper are created; anything that re-allocates the parameters later
+    (``model.to(...)``) undoes it, and the layers fall back to separate projections by themselves.
+    Returns the number of blocks stacked."""
+    done = 0
+    for mod in model.modules():
+        q, k, v = (getattr(mod, n, None) for n in ("q_proj", "k_proj", "v_proj"))
+        if not all(_plain_linear(m) if m is not None else False for m in (q, k, v)):
+            continue
+        wq, wk, wv = q.weight, k.weight, v.weight
+        if wq.dtype != wk.dtype or wq.dtype != wv.dtype or wq.shape[1] != wk.shape[1] or wq.shape[1] != wv.shape[1]:
+            continue
+        if not _stacked(wq.data, wk.data, wv.data):
+            buf = torch.empty((wq.shape[0] + wk.shape[0] + wv.shape[0], wq.shape[1]), dtype=wq.dtype, device=wq.device)
+            row = 0
+            for w in (wq, wk, wv):
+                view = buf[row:row + w.shape[0]]
+                view.copy_(w.data)
+                w.data = view
+                row += w.shape[0]
+        done += 1
+    return done
+
+
+class QKVProjectionFunction(torch.autograd.Function):
+    """``(x @ wq.T, x @ wk.T, x @ wv.T)`` for three weights that are stacked in memory:
+    forward = one product ``x [Wq; Wk; Wv]^T`` whose epilogue writes three dense results;
+    ``dx = [dq | dk | dv] [Wq; Wk; Wv]`` = one product whose A operand is read from the three
+    gradient tensors where they lie; ``[dWq; dWk; dWv] = [dq | dk | dv]^T x`` = one product into a
+    stacked buffer of which the three weight gradients are views."""
+
+    @staticmethod
+    def forward(ctx, x, wq, wk, wv):
+        dev = _lib.require_cuda(x, wq, wk, wv)
+        lib = _lib.get_lib()
+        k = x.shape[-1]
+        x2 = _rows2d(x)
+        m = x2.shape[0]
+        ns = (wq.shape[0], wk.shape[0], wv.shape[0])
+        w_all = torch.as_strided(wq.detach(), (sum(ns), k), (k, 1))  # the three weights as one matrix
+        outs = [torch.empty((m, n), dtype=x.dtype, device=dev) for n in ns]
+        if m > 0:
+            d = _lib.GemmDesc()
+            d.A, d.B, d.lda, d.ldb, d.K = x2.data_ptr(), w_all.data_ptr(), _ld(x2), k, k
+            d.D, d.ldd, d.M, d.N = outs[0].data_ptr(), ns[0], m, sum(ns)
+            d.a_kmajor, d.b_kmajor = 1, 1
+            d.in_dtype = d.out_dtype = _lib.dtype_code(x.dtype)
+            d.d_split, d.D1, d.D2, d.ldd1, d.ldd2, d.N0, d.N1 = 1, outs[1].data_ptr(), outs[2].data_ptr(), ns[1], ns[2], ns[0], ns[1]
+            st = _lib.status_word(dev)
+            with _lib.device_of(dev), _lib.timed("proj_fwd", 1, dev):
+                rc = lib.bt_gemm_ex(ctypes.byref(d), st.data_ptr(), _lib.stream_ptr(dev))
+            _lib.check(rc, "bt_gemm_ex(qkv)")
+        ctx.save_for_backward(x2, w_all)
+        ctx.ns = ns
+        ctx.x_shape = x.shape
+        ctx.set_materialize_grads(False)
+        return tuple(o.view(*x.shape[:-1], n) for o, n in zip(outs, ns))
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        x2, w_all = ctx.saved_tensors
+        dev = x2.device
+        lib = _lib.get_lib()
+        m, k = x2.shape
+        ns = ctx.ns
+        gs = []
+        for g, n in zip((dq, dk, dv), ns):
+            if g is None:
+                g = torch.zeros((m, n), dtype=x2.dtype, device=dev)
+            gs.append(_rows2d(g.to(x2.dtype)))
+        code = _lib.dtype_code(x2.dtype)
+        st = _lib.status_word(dev)
+        dx = dw = None
+        if m == 0:
+            dx = torch.zeros(ctx.x_shape, dtype=x2.dtype, device=dev) if ctx.needs_input_grad[0] else None
+            dws = [torch.zeros((n, k), dtype=x2.dtype, device=dev) for n in ns]
+            return (dx, *dws)
+        if ctx.needs_input_grad[0]:
+            # dx[m, k] = [dq | dk | dv][m, sum ns] @ W_all[sum ns, k]: A in three pieces along the contraction
+            dx = torch.empty((m, k), dtype=x2.dtype, device=dev)
+            d = _lib.GemmDesc()
+            d.A, d.lda, d.K = gs[0].data_ptr(), _ld(gs[0]), ns[0]
+            d.A1, d.lda1, d.K1 = gs[1].data_ptr(), _ld(gs[1]), ns[1]
+            d.A2, d.lda2, d.K2 = gs[2].data_ptr(), _ld(gs[2]), ns[2]
+            d.a_split = 1
+            d.B, d.ldb = w_all.data_ptr(), k
+            d.D, d.ldd, d.M, d.N = dx.data_ptr(), k, m, k
+            d.a_kmajor, d.b_kmajor = 1, 0
+            d.in_dtype = d.out_dtype = code
+            with _lib.device_of(dev), _lib.timed("proj_bwd", 1, dev):
+                rc = lib.bt_gemm_ex(ctypes.byref(d), st.data_ptr(), _lib.stream_ptr(dev))
+            _lib.check(rc, "bt_gemm_ex(qkv dx)")
+            dx = dx.view(ctx.x_shape)
+        if any(ctx.needs_input_grad[1:]):
+            # [dWq; dWk; dWv][sum ns, k] = [dq | dk | dv]^T @ x: A in three pieces along M
+            dw = torch.empty((sum(ns), k), dtype=x2.dtype, device=dev)
+            d = _lib.GemmDesc()
+            d.A, d.lda, d.K = gs[0].data_ptr(), _ld(gs[0]), m
+            d.A1, d.lda1 = gs[1].data_ptr(), _ld(gs[1])
+            d.A2, d.lda2 = gs[2].data_ptr(), _ld(gs[2])
+            d.a_split, d.M0, d.M1 = 2, ns[0], ns[1]
+            d.B, d.ldb = x2.data_ptr(), _ld(x2)
+            d.D, d.ldd, d.M, d.N = dw.data_ptr(), k, sum(ns), k
+            d.a_kmajor, d.b_kmajor = 0, 0
+            d.in_dtype = d.out_dtype = code
+            with _lib.device_of(dev), _lib.timed("proj_bwd", 1, dev):
+                rc = lib.bt_gemm_ex(ctypes.byref(d), st.data_ptr(), _lib.stream_ptr(dev))
+            _lib.check(rc, "bt_gemm_ex(qkv dW)")
+        dws, row = [], 0
+        for i, n in enumerate(ns):
+            dws.append(dw[row:row + n] if (dw is not None and ctx.needs_input_grad[1 + i]) else None)
+            row += n
+        return (dx, *dws)
+
+
+def _qkv_fusable(x, wq, wk, wv) -> bool:
+    """One product for the three projections: stacked weights of the input's dtype, and segment
+    sizes the kernel's tiles divide (256 result columns / rows, 64-element contraction blocks)."""
+    return (x.is_cuda and x.dtype in _GEMM_DTYPES and wq.dtype == x.dtype and x.shape[-1] % 8 == 0
+            and wq.shape[0] % 256 == 0 and wk.shape[0] % 256 == 0 and wv.shape[0] % 8 == 0
+            and _stacked(wq, wk, wv))
+
+
 def shared_input_linear(x, *weights, dx_only: bool = False):
     """``dx_only``: outputs and weight gradients from torch.mm, only the input gradient fused."""
     return SharedInputLinearFunction.apply(dx_only, x, *weights)
@@ -400,10 +541,14 @@ def attention_forward(self, hidden_states, position_embeddings, attention_mask, 
 
     lead = hidden_states.shape[:-1]
     cos, sin = position_embeddings
-    on_gemm = (_projection_mode != "off" and hidden_states.is_cuda and hidden_states.dtype in _GEMM_DTYPES
-               and hidden_states.shape[-1] % 8 == 0 and self.head_dim % 8 == 0
-               and all(_plain_linear(m) for m in (self.q_proj, self.k_proj, self.v_proj, self.o_proj)))
-    if on_gemm:
+    plain = all(_plain_linear(m) for m in (self.q_proj, self.k_proj, self.v_proj, self.o_proj))
+    on_gemm = (_projection_mode in ("dx", "all") and hidden_states.is_cuda and hidden_states.dtype in _GEMM_DTYPES
+               and hidden_states.shape[-1] % 8 == 0 and self.head_dim % 8 == 0 and plain)
+    if (_projection_mode == "qkv" and plain
+            and _qkv_fusable(hidden_states, self.q_proj.weight, self.k_proj.weight, self.v_proj.weight)):
+        q_lin, k_lin, v_lin = QKVProjectionFunction.apply(hidden_states, self.q_proj.weight, self.k_proj.weight,
+                                                          self.v_proj.weight)
+    elif on_gemm:
         q_lin, k_lin, v_lin = shared_input_linear(hidden_states, self.q_proj.weight, self.k_proj.weight,
                                                   self.v_proj.weight, dx_only=_projection_mode == "dx")
     else:

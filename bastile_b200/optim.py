@@ -73,8 +73,16 @@ class AdamW(torch.optim.Optimizer):
         group = self.param_groups[-1]
         for p in group["params"]:
             self._group_of[p] = group
-            if p.requires_grad and hasattr(p, "register_post_accumulate_grad_hook"):
+            if self.overlap_backward and p.requires_grad and hasattr(p, "register_post_accumulate_grad_hook"):
                 self._hooks.append(p.register_post_accumulate_grad_hook(self._on_grad_ready))
+
+    def close(self):
+        """Remove the gradient hooks.  A hook ties parameter -> optimizer -> parameter through a
+        reference that Python's cycle collector cannot see, so an optimizer created with
+        ``overlap_backward=True`` (and its model and state) is only freed after ``close()``."""
+        for h in self._hooks:
+            h.remove()
+        self._hooks.clear()
 
     @torch.no_grad()
     def _on_grad_ready(self, p):
@@ -244,16 +252,18 @@ class ShardedAdamW:
         open_buckets: dict = {}
 
         def close(key):
-            items = open_buckets.pop(key, None)
-            if not items:
+            units = open_buckets.pop(key, None)
+            if not units:
                 return
             dev, dtype = key
             b = _Bucket()
             b.params, b.offsets, off = [], [], 0
-            for p in items:
-                b.params.append(p)
-                b.offsets.append(off)
-                off += (p.numel() + align - 1) // align * align
+            for unit in units:
+                off = (off + align - 1) // align * align
+                for p in unit:  # members of a unit stay back to back, as they were
+                    b.params.append(p)
+                    b.offsets.append(off)
+                    off += p.numel()
             b.numel = (off + quantum - 1) // quantum * quantum
             b.device, b.dtype = dev, dtype
             b.flat_p = torch.zeros(b.numel, dtype=dtype, device=dev)
@@ -276,13 +286,25 @@ class ShardedAdamW:
                 self._hooks.append(p.register_post_accumulate_grad_hook(self._on_grad))
             self.buckets.append(b)
 
-        sizes: dict = {}
-        for p in reversed(params):
+        # Units: runs of parameters that already lie one after the other in memory, in registration
+        # order (q/k/v weights stacked for the one-product projections, for instance).  A unit keeps
+        # its order and stays in one bucket, so whatever relies on that layout still finds it.
+        units: list = []
+        for p in params:
             if not p.is_contiguous():
                 raise RuntimeError("ShardedAdamW needs contiguous parameters")
-            key = (p.device, p.dtype)
-            open_buckets.setdefault(key, []).append(p)
-            sizes[key] = sizes.get(key, 0) + p.numel() * p.element_size()
+            prev = units[-1][-1] if units else None
+            if (prev is not None and prev.device == p.device and prev.dtype == p.dtype
+                    and p.data_ptr() == prev.data_ptr() + prev.numel() * prev.element_size()
+                    and (prev.numel() * prev.element_size()) % 16 == 0):
+                units[-1].append(p)
+            else:
+                units.append([p])
+        sizes: dict = {}
+        for unit in reversed(units):  # reverse registration order: the order in which gradients become final
+            key = (unit[0].device, unit[0].dtype)
+            open_buckets.setdefault(key, []).append(unit)
+            sizes[key] = sizes.get(key, 0) + sum(p.numel() * p.element_size() for p in unit)
             if sizes[key] >= bucket_bytes:
                 close(key)
                 sizes[key] = 0
@@ -375,6 +397,13 @@ class ShardedAdamW:
         for dev, side in self._streams.items():
             torch.cuda.current_stream(dev).wait_stream(side)
         self.step_count += 1
+
+    def close(self):
+        """Remove the gradient hooks (they tie parameters and this object together through a
+        reference the cycle collector cannot see: without this call neither is ever freed)."""
+        for h in self._hooks:
+            h.remove()
+        self._hooks.clear()
 
     def state_bytes(self) -> int:
         """Bytes of optimizer state (moments, master copy) this rank holds."""

@@ -607,6 +607,10 @@ def train_run(*, dev, rank, world, local, patches="bastile", parallel="single", 
         model = q3.Qwen3ForCausalLM(cfg)
     torch.set_default_dtype(prev)
     model.train()
+    if patches == "bastile" and fused_layers and gemm_projections == "qkv":
+        from bastile_b200.ops.fused_layers import stack_qkv_weights
+
+        res["qkv_blocks_stacked"] = stack_qkv_weights(model)
     ckpt_kwargs = {"gradient_checkpointing_kwargs": {"use_reentrant": False}}
     if grad_checkpoint:
         model.gradient_checkpointing_enable(**ckpt_kwargs)
@@ -774,6 +778,8 @@ def train_run(*, dev, rank, world, local, patches="bastile", parallel="single", 
             from bastile_b200.ops.fused_linear_cross_entropy import set_vocab_parallel
 
             set_vocab_parallel(None)
+        if hasattr(opt, "close"):
+            opt.close()  # gradient hooks keep model and optimizer alive otherwise
         del net, model, opt
         stack.close()
         gc.collect()
@@ -826,9 +832,10 @@ def main():
                     help="leave Qwen3DecoderLayer.forward / Qwen3Attention.forward as HF has them (by default the "
                          "bench applies bastile_b200.apply(fused_layers=True): residual adds folded into the norm "
                          "and down-projection kernels, q/k-norm + RoPE as one kernel)")
-    ap.add_argument("--gemm-projections", default="off", choices=["off", "dx", "all"],
+    ap.add_argument("--gemm-projections", default="off", choices=["off", "dx", "all", "qkv"],
                     help="with fused layers: off = q/k/v/o_proj stay on nn.Linear (cuBLAS); dx = their shared input "
-                         "gradient from two bt_gemm_ex launches; all = every product of theirs on bt_gemm_ex")
+                         "gradient from two bt_gemm_ex launches; all = every product of theirs on bt_gemm_ex; qkv = "
+                         "q/k/v weights stacked in memory and the three projections run as one product each way")
     ap.add_argument("--no-overlap-optimizer", action="store_true",
                     help="single GPU: run the whole AdamW step after the backward pass instead of updating each "
                          "large parameter underneath it as soon as its gradient is complete")
@@ -960,9 +967,11 @@ def main():
         try:
             return fn()
         except Exception as exc:  # noqa: BLE001
-            gc.collect()
-            torch.cuda.empty_cache()
-            return {"skipped": f"{type(exc).__name__}: {str(exc)[:200]}", "what": name}
+            failure = {"skipped": f"{type(exc).__name__}: {str(exc)[:200]}", "what": name}
+        # the exception (and the frames its traceback held) is gone here: now memory can be returned
+        gc.collect()
+        torch.cuda.empty_cache()
+        return failure
 
     if world == 1:
         line["reference_published"] = REFERENCE_CHART

@@ -203,6 +203,24 @@ typedef struct bt_gemm_desc {
   const float* addend;  int64_t ld_addend;     /* fp32, or NULL */
   const void* addend_t; int64_t ld_addend_t;   /* operand dtype, or NULL */
   const float* alpha;                          /* device scalar, or NULL */
+  /* A given as THREE tensors against one B (B1 unused); 0 = off.
+   *   a_split = 1: side by side along K: D = [A | A1 | A2] * B with contraction lengths K, K1,
+   *     K2 (K and K1 multiples of 64 elements, 32 for fp32) and B spanning K + K1 + K2 - the
+   *     shared input gradient dX = [dQ | dK | dV] * [Wq; Wk; Wv] of the q/k/v projections
+   *     (transformers modeling_qwen3.py:256-258) as ONE launch when the three weights lie one
+   *     after the other in memory, without first copying dQ, dK, dV side by side.
+   *   a_split = 2: stacked along M: rows [0, M0) of op(A) come from A, the next M1 from A1, the
+   *     rest from A2 (M0, M1 multiples of 256; all three with contraction length K) - the three
+   *     weight gradients [dQ | dK | dV]^T * X as one product into one stacked result. */
+  const void* A2; int64_t lda2, K2;
+  int32_t a_split;
+  /* d_split = 1: the result is THREE tensors side by side along N: columns [0, N0) go to D (row
+   * stride ldd), the next N1 to D1, the rest to D2 (N0, N1 multiples of 256; no addends) - the
+   * q, k and v projections as one product x * [Wq; Wk; Wv]^T that still hands each its own
+   * dense tensor. */
+  int32_t d_split;
+  int64_t M0, M1;
+  void* D1; void* D2; int64_t ldd1, ldd2, N0, N1;
 } bt_gemm_desc;
 int bt_gemm_ex(const bt_gemm_desc* desc, int32_t* status, void* stream);
 

@@ -277,8 +277,93 @@ def test_shared_input_linear_partial_gradients():
     assert_close(x.grad, ref.cpu().numpy(), what="dx", rtol=2e-2, atol=2e-2 * float(ref.abs().max()))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("pairs", [1, 0])
+@pytest.mark.parametrize("rows,hidden,nq,nk", [(333, 256, 512, 256), (1024, 512, 1024, 256), (40, 128, 256, 256)])
+def test_qkv_projection_one_product_each_way_vs_float64(rows, hidden, nq, nk, dtype, pairs):
+    """q/k/v projections over weights stacked in memory: forward with the result split over three
+    dense tensors, dx with the A operand read from three gradient tensors along the contraction,
+    the three weight gradients as one product with A in three pieces along M - against float64."""
+    from bastile_b200 import _lib
+    from bastile_b200.ops.fused_layers import QKVProjectionFunction, _qkv_fusable
+
+    lib = _lib.get_lib()
+    prev = lib.bt_set_gemm_cta_pairs(pairs)
+    try:
+        torch.manual_seed(rows + nq)
+        x = torch.randn(rows, hidden, device=DEV).to(dtype).requires_grad_(True)
+        buf = torch.randn(nq + 2 * nk, hidden, device=DEV).mul(0.05).to(dtype)
+        ws = [buf[:nq].requires_grad_(True), buf[nq:nq + nk].requires_grad_(True), buf[nq + nk:].requires_grad_(True)]
+        assert _qkv_fusable(x, *ws)
+        dys = [torch.randn(rows, n, device=DEV).to(dtype) for n in (nq, nk, nk)]
+        ys = QKVProjectionFunction.apply(x, *ws)
+        assert all(y.is_contiguous() for y in ys)
+        torch.autograd.backward(list(ys), dys)
+        _lib.check_status(x.device, "qkv projection")
+        x64 = x.detach().double().cpu()
+        tol = dict(rtol=2e-2, atol=2e-2) if dtype != torch.float32 else dict(rtol=5e-3, atol=5e-3)
+        dx_ref = torch.zeros_like(x64)
+        for y, w, dy in zip(ys, ws, dys):
+            w64, dy64 = w.detach().double().cpu(), dy.double().cpu()
+            assert_close(y, (x64 @ w64.T).numpy(), what="y", **tol)
+            dw_ref = (dy64.T @ x64).numpy()
+            assert_close(w.grad, dw_ref, what="dW", rtol=tol["rtol"], atol=tol["atol"] * float(np.abs(dw_ref).max()))
+            dx_ref += dy64 @ w64
+        assert_close(x.grad, dx_ref.numpy(), what="dx", rtol=tol["rtol"], atol=tol["atol"] * float(dx_ref.abs().max()))
+    finally:
+        lib.bt_set_gemm_cta_pairs(prev)
+
+
+def test_qkv_mode_whole_model_matches_separate_projections():
+    """A small Qwen3 whose q/k/v widths the fused product takes (512 | 256 | 256): after
+    stack_qkv_weights() the "qkv" mode must give the loss and gradients of the same model with
+    nn.Linear projections, parameter names and shapes unchanged; a layer whose weights are not
+    stacked falls back by itself."""
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+
+    import bastile_b200
+    from bastile_b200 import _lib
+    from bastile_b200.ops import fused_layers
+
+    cfg = Qwen3Config(vocab_size=1024, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                      num_attention_heads=8, num_key_value_heads=4, head_dim=64, rms_norm_eps=1e-6, rope_theta=1e6,
+                      tie_word_embeddings=False, use_cache=False)
+    cfg._attn_implementation = "sdpa"
+    ids = torch.randint(0, 1024, (2, 96), generator=torch.Generator().manual_seed(3)).to(DEV)
+    results = {}
+    try:
+        for mode in ("off", "qkv"):
+            bastile_b200.reset()
+            bastile_b200.apply(fused_layers=True, gemm_projections=mode)
+            torch.manual_seed(21)
+            model = Qwen3ForCausalLM(cfg).to(DEV, torch.bfloat16).train()
+            names = [n for n, _ in model.named_parameters()]
+            if mode == "qkv":
+                assert fused_layers.stack_qkv_weights(model) == 2
+                att = model.model.layers[0].self_attn
+                assert fused_layers._stacked(att.q_proj.weight, att.k_proj.weight, att.v_proj.weight)
+                assert [n for n, _ in model.named_parameters()] == names
+                # un-stack the second layer: it must take the separate projections again
+                att1 = model.model.layers[1].self_attn
+                att1.k_proj.weight.data = att1.k_proj.weight.data.clone()
+                assert not fused_layers._stacked(att1.q_proj.weight, att1.k_proj.weight, att1.v_proj.weight)
+            _lib.instr.reset(enabled=False)
+            out = model(input_ids=ids, labels=ids)
+            out.loss.backward()
+            _lib.check_status(torch.device(DEV, torch.cuda.current_device()), mode)
+            results[mode] = (float(out.loss), {n: p.grad.detach().float().clone() for n, p in model.named_parameters()})
+    finally:
+        bastile_b200.reset()
+    (l0, g0), (l1, g1) = results["off"], results["qkv"]
+    assert abs(l0 - l1) <= 1e-3 * abs(l0)
+    for n in g0:
+        scale = float(g0[n].abs().max()) + 1e-12
+        assert float((g0[n] - g1[n]).abs().max()) <= 3e-2 * scale, n
+
+
+
 # ------------------------------------------------------------------ whole model
-@pytest.fixture(params=["off", "dx", "all"])
+@pytest.fixture(params=["off", "dx", "all", "qkv"])
 def fused(request):
     """apply(fused_layers=True) in each mode of the q/k/v/o projections."""
     import bastile_b200

@@ -57,7 +57,12 @@ constexpr int kBBytes = BN * BK * 2;
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = 512;
 constexpr int kGroupM = 16;  // tile rasterisation: walk 16 row-tiles per column-tile
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+// Result staging for tile stores: every epilogue warp owns two 2 KB buffers (32 rows x 64 bytes,
+// 64-byte swizzle) that it fills from registers and hands to cp.async.bulk.tensor stores.
+constexpr int kStageOutBytes = 2048;
+constexpr int kOutBytes = kEpiWarps * 2 * kStageOutBytes;  // 32 KB
+constexpr int kCtrlBytes = 1024;                            // barriers, TMEM slot, abort flag
+constexpr int kSmemBytes = kStages * kStageBytes + kCtrlBytes + kOutBytes + 1024 /*alignment slack*/;
 
 // Tile geometry that depends on the operand element size (all rows are 128 bytes).
 template <typename T>
@@ -102,6 +107,7 @@ struct Params {
   int n_seg0, n_seg1;
   int out_fp32;
   int vec_ok;  // rows of every global tensor the epilogue touches are 16-byte aligned
+  int tma_out; // 16-bit results leave through shared memory and tile stores (tensor maps tmO0..2)
   const float* addend;
   int64_t ld_add;
   const void* addend_t;  // second addend, stored in the operand type (a residual stream)
@@ -199,16 +205,56 @@ __device__ __forceinline__ void load_row32(const T* src, float (&v)[32], int val
   }
 }
 
+// A warp's way out for 16-bit results: 32 rows x 32 columns per store.  Each lane writes its row
+// (64 bytes) into the warp's staging buffer with the 64-byte swizzle the tensor map expects
+// (16-byte piece i of row r lands at piece i ^ ((r >> 1) & 3): conflict-free for the eight lanes
+// of a store phase), then one lane issues the tile store.  Two buffers alternate; before a buffer
+// is refilled the store that last read it must have finished reading (wait_group.read 1).
+// base == 0: the launch stores straight from registers instead.  Must be called by all 32 lanes.
+struct OutStage {
+  uint32_t base;
+  uint32_t count;
+};
+
+template <typename T>
+__device__ __forceinline__ void stage_store32(OutStage& st, const CUtensorMap* tm,
+                                              const float (&v)[32], int col0, int row0, int lane) {
+  if constexpr (sizeof(T) == 2) {
+    const uint32_t buf = st.base + (st.count & 1u) * kStageOutBytes;
+    ++st.count;
+    if (lane == 0) ptx::bulk_wait_group_read<1>();
+    __syncwarp();
+    const uint32_t row = buf + static_cast<uint32_t>(lane) * 64u;
+    const uint32_t sw = (static_cast<uint32_t>(lane) >> 1) & 3u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float f[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = v[i * 8 + e];
+      ptx::st_shared_v4(row + ((static_cast<uint32_t>(i) ^ sw) << 4), Cvt<T>::pack(f));
+    }
+    ptx::fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      ptx::tma_store_2d(tm, buf, col0, row0);
+      ptx::bulk_commit_group();
+    }
+  }
+}
+
 // ------------------------------------------------------------------ epilogues
 template <typename T>
 __device__ __forceinline__ void epi_plain(const Params& p, uint32_t taddr, int64_t row, int n0,
-                                          int half) {
+                                          int half, OutStage& stg, const CUtensorMap* tmO0,
+                                          const CUtensorMap* tmO1, const CUtensorMap* tmO2, int lane) {
   const float alpha = p.alpha != nullptr ? __ldg(p.alpha) : 1.0f;
   const bool row_ok = row < p.M;
+  const int row0 = static_cast<int>(row) - lane;  // first row of this warp's 32
   // where this tile's columns live: one result tensor, or one of three side by side
   void* out = p.out;
   int64_t ldo = p.ldo;
   int col_shift = 0, n_end = p.N;
+  const CUtensorMap* tmo = tmO0;
   if (p.n_seg0 > 0) {
     if (n0 < p.n_seg0) {
       n_end = p.n_seg0;
@@ -217,10 +263,12 @@ __device__ __forceinline__ void epi_plain(const Params& p, uint32_t taddr, int64
       ldo = p.ldo1;
       col_shift = p.n_seg0;
       n_end = p.n_seg0 + p.n_seg1;
+      tmo = tmO1;
     } else {
       out = p.out2;
       ldo = p.ldo2;
       col_shift = p.n_seg0 + p.n_seg1;
+      tmo = tmO2;
     }
   }
 #pragma unroll 1
@@ -233,6 +281,36 @@ __device__ __forceinline__ void epi_plain(const Params& p, uint32_t taddr, int64
       load_row32<T>(static_cast<const T*>(p.addend_t) + row * p.ld_add_t + col0, res, valid,
                     p.vec_ok);
     ptx::tmem_ld_32cols(taddr + c * 32, v);
+    if (stg.base != 0) {
+      // every lane computes (rows past M hold zeros and are clipped by the store)
+      if (valid > 0 && row0 < p.M) {
+        if (add_res) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] += res[j];
+        }
+        if (p.addend != nullptr && row_ok) {
+          const float* a = p.addend + row * p.ld_add + col0;
+          if (valid >= 32) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 t = *reinterpret_cast<const float4*>(a + i * 4);
+              v[i * 4] += t.x;
+              v[i * 4 + 1] += t.y;
+              v[i * 4 + 2] += t.z;
+              v[i * 4 + 3] += t.w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < valid) v[j] += a[j];
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= alpha;
+        stage_store32<T>(stg, tmo, v, col0 - col_shift, row0, lane);
+      }
+      continue;
+    }
     if (row_ok && valid > 0) {
       if (add_res) {
 #pragma unroll
@@ -268,8 +346,11 @@ __device__ __forceinline__ void epi_plain(const Params& p, uint32_t taddr, int64
 // Accumulator columns [0,128) = gate, [128,256) = up for output columns n0 .. n0+127.
 template <typename T>
 __device__ __forceinline__ void epi_swiglu_fwd(const Params& p, uint32_t taddr, int64_t row,
-                                               int n0, int half) {
+                                               int n0, int half, OutStage& stg,
+                                               const CUtensorMap* tm_gate, const CUtensorMap* tm_up,
+                                               const CUtensorMap* tm_h, int lane) {
   const bool row_ok = row < p.M;
+  const int row0 = static_cast<int>(row) - lane;
 #pragma unroll 1
   for (int c = half * (BN / 128); c < (half + 1) * (BN / 128); ++c) {
     float g[32], u[32];
@@ -277,6 +358,24 @@ __device__ __forceinline__ void epi_swiglu_fwd(const Params& p, uint32_t taddr, 
     ptx::tmem_ld_32cols(taddr + BN / 2 + c * 32, u);
     const int col0 = n0 + c * 32;
     const int valid = p.N - col0;
+    if (stg.base != 0) {
+      if (valid > 0 && row0 < p.M) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          g[j] = round_through<T>(g[j]);
+          u[j] = round_through<T>(u[j]);
+        }
+        stage_store32<T>(stg, tm_gate, g, col0, row0, lane);
+        stage_store32<T>(stg, tm_up, u, col0, row0, lane);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float silu = round_through<T>(g[j] * __fdividef(1.0f, 1.0f + __expf(-g[j])));
+          g[j] = silu * u[j];
+        }
+        stage_store32<T>(stg, tm_h, g, col0, row0, lane);
+      }
+      continue;
+    }
     if (row_ok && valid > 0) {
       float hh[32];
 #pragma unroll
@@ -297,8 +396,11 @@ __device__ __forceinline__ void epi_swiglu_fwd(const Params& p, uint32_t taddr, 
 // Accumulator = dh tile; reads saved gate/up, writes dgate (p.out) and dup (p.h).
 template <typename T>
 __device__ __forceinline__ void epi_swiglu_bwd(const Params& p, uint32_t taddr, int64_t row,
-                                               int n0, int half) {
+                                               int n0, int half, OutStage& stg,
+                                               const CUtensorMap* tm_dgate, const CUtensorMap* tm_dup,
+                                               int lane) {
   const bool row_ok = row < p.M;
+  const int row0 = static_cast<int>(row) - lane;
 #pragma unroll 1
   for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
     const int col0 = n0 + c * 32;
@@ -311,6 +413,26 @@ __device__ __forceinline__ void epi_swiglu_bwd(const Params& p, uint32_t taddr, 
       load_row32<T>(static_cast<const T*>(p.up) + off, u, valid, p.vec_ok);
     }
     ptx::tmem_ld_32cols(taddr + c * 32, d);
+    if (stg.base != 0) {
+      if (valid > 0 && row0 < p.M) {
+        // rows past M (lanes that loaded nothing) hold a zero accumulator: whatever g and u
+        // contain there is multiplied by dh = 0 unless it is not finite, and the store clips them
+        if (!live) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) g[j] = u[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float dh = round_through<T>(d[j]);
+          const float sg = __fdividef(1.0f, 1.0f + __expf(-g[j]));
+          d[j] = dh * (sg * (1.0f + g[j] * (1.0f - sg))) * u[j];  // dgate
+          g[j] = dh * (g[j] * sg);                                 // dup
+        }
+        stage_store32<T>(stg, tm_dgate, d, col0, row0, lane);
+        stage_store32<T>(stg, tm_dup, g, col0, row0, lane);
+      }
+      continue;
+    }
     if (live) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
@@ -331,8 +453,10 @@ __device__ __forceinline__ void epi_swiglu_bwd(const Params& p, uint32_t taddr, 
 // the logits themselves rounded to T.
 template <typename T>
 __device__ __forceinline__ void epi_lce(const Params& p, uint32_t taddr, int64_t row, int n0,
-                                        int n_idx, int half) {
+                                        int n_idx, int half, OutStage& stg,
+                                        const CUtensorMap* tm_logits, int lane) {
   const bool row_ok = row < p.M;
+  const int row0 = static_cast<int>(row) - lane;
   constexpr float kNegBig = -1e30f;
   int tgt_col = -1;  // column of the label inside this tile, if it is here
   bool owned = false;
@@ -369,8 +493,11 @@ __device__ __forceinline__ void epi_lce(const Params& p, uint32_t taddr, int64_t
         for (int j = 0; j < 32; ++j)
           if (j == jj) tgt = v[j];
       }
-      if (row_ok)
+      if (stg.base != 0) {
+        if (row0 < p.M) stage_store32<T>(stg, tm_logits, v, col0, row0, lane);
+      } else if (row_ok) {
         store_row32<T>(static_cast<T*>(p.out) + row * p.ldo + col0, v, valid, p.vec_ok);
+      }
     }
   }
   if (row_ok) {
@@ -429,7 +556,9 @@ template <int EPI, typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
             const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
-            const __grid_constant__ CUtensorMap tmA2, const Params p) {
+            const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmO0,
+            const __grid_constant__ CUtensorMap tmO1, const __grid_constant__ CUtensorMap tmO2,
+            const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -459,6 +588,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     if ((p.K1 > 0 && p.a_split == A_WHOLE) || p.dual_b) ptx::prefetch_tensormap(&tmB1);
     if (p.K1 > 0 || p.a_split != A_WHOLE) ptx::prefetch_tensormap(&tmA1);
     if (p.a_split != A_WHOLE) ptx::prefetch_tensormap(&tmA2);
+    if (p.tma_out) ptx::prefetch_tensormap(&tmO0);
   }
   if (warp == 1) {
     ptx::tmem_alloc(tmem_slot, kTmemCols);
@@ -576,6 +706,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     const int half = (warp - 2) >> 2;  // which half of the accumulator columns
     int acc = 0;
     uint32_t acc_phase = 0;
+    OutStage stg;
+    stg.base = p.tma_out ? ptx::smem_u32(smem + kStages * kStageBytes + kCtrlBytes) +
+                               static_cast<uint32_t>(warp - 2) * (2 * kStageOutBytes)
+                         : 0u;
+    stg.count = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
       int m_idx, n_idx;
       tile_coords(p, tile, &m_idx, &n_idx);
@@ -584,15 +719,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
       const uint32_t taddr =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
       const int64_t row = static_cast<int64_t>(m_idx) * BM + quarter * 32 + lane;
-      if (EPI == EPI_PLAIN) epi_plain<T>(p, taddr, row, n_idx * BN, half);
-      if (EPI == EPI_SWIGLU_FWD) epi_swiglu_fwd<T>(p, taddr, row, n_idx * (BN / 2), half);
-      if (EPI == EPI_SWIGLU_BWD) epi_swiglu_bwd<T>(p, taddr, row, n_idx * BN, half);
-      if (EPI == EPI_LCE) epi_lce<T>(p, taddr, row, n_idx * BN, n_idx, half);
+      if (EPI == EPI_PLAIN) epi_plain<T>(p, taddr, row, n_idx * BN, half, stg, &tmO0, &tmO1, &tmO2, lane);
+      if (EPI == EPI_SWIGLU_FWD)
+        epi_swiglu_fwd<T>(p, taddr, row, n_idx * (BN / 2), half, stg, &tmO0, &tmO1, &tmO2, lane);
+      if (EPI == EPI_SWIGLU_BWD) epi_swiglu_bwd<T>(p, taddr, row, n_idx * BN, half, stg, &tmO0, &tmO1, lane);
+      if (EPI == EPI_LCE) epi_lce<T>(p, taddr, row, n_idx * BN, n_idx, half, stg, &tmO0, lane);
       ptx::tcgen05_fence_before_sync();
       ptx::mbar_arrive(&tempty[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    // this warp's tile stores must have left shared memory (and landed) before the CTA goes away
+    if (stg.base != 0 && lane == 0) ptx::bulk_wait_group<0>();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -617,7 +755,7 @@ constexpr int kStages2 = 6;
 constexpr int kPairProducerB = 2 + kEpiWarps;       // warp index of the second producer
 constexpr int kThreadsPair = kThreads + 32;
 constexpr int kStageBytes2 = kABytes + kBBytes / 2;
-constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + 1024 + 256;
+constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + kCtrlBytes + kOutBytes + 1024;
 
 // ---- dynamic tile hand-out -------------------------------------------------------------
 // With a fixed round-robin deal a CTA pair that gets its SMs late (a collective's kernel is
@@ -675,7 +813,9 @@ template <int EPI, typename T>
 __global__ void __launch_bounds__(kThreadsPair, 1)
 gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
                  const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
-                 const __grid_constant__ CUtensorMap tmA2, const Params p) {
+                 const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmO0,
+            const __grid_constant__ CUtensorMap tmO1, const __grid_constant__ CUtensorMap tmO2,
+            const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -707,6 +847,7 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
     if ((p.K1 > 0 && p.a_split == A_WHOLE) || p.dual_b) ptx::prefetch_tensormap(&tmB1);
     if (p.K1 > 0 || p.a_split != A_WHOLE) ptx::prefetch_tensormap(&tmA1);
     if (p.a_split != A_WHOLE) ptx::prefetch_tensormap(&tmA2);
+    if (p.tma_out) ptx::prefetch_tensormap(&tmO0);
   }
   if (warp == 1) {
     ptx::tmem_alloc_pair(tmem_slot, kTmemCols);
@@ -846,6 +987,11 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
     const int half = (warp - 2) >> 2;
     int acc = 0;
     uint32_t acc_phase = 0;
+    OutStage stg;
+    stg.base = p.tma_out ? ptx::smem_u32(smem + kStages2 * kStageBytes2 + kCtrlBytes) +
+                               static_cast<uint32_t>(warp - 2) * (2 * kStageOutBytes)
+                         : 0u;
+    stg.count = 0;
     for (int it = 0;; ++it) {
       int tile = 0;
       if (lane == 0) tile = sched_wait(p, pair, npairs, it, cta_abort, ST_EPILOGUE);
@@ -859,10 +1005,11 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
       const int64_t row =
           static_cast<int64_t>(m_idx) * (2 * BM) + static_cast<int64_t>(rank) * BM + quarter * 32 + lane;
-      if (EPI == EPI_PLAIN) epi_plain<T>(p, taddr, row, n_idx * BN, half);
-      if (EPI == EPI_SWIGLU_FWD) epi_swiglu_fwd<T>(p, taddr, row, n_idx * (BN / 2), half);
-      if (EPI == EPI_SWIGLU_BWD) epi_swiglu_bwd<T>(p, taddr, row, n_idx * BN, half);
-      if (EPI == EPI_LCE) epi_lce<T>(p, taddr, row, n_idx * BN, n_idx, half);
+      if (EPI == EPI_PLAIN) epi_plain<T>(p, taddr, row, n_idx * BN, half, stg, &tmO0, &tmO1, &tmO2, lane);
+      if (EPI == EPI_SWIGLU_FWD)
+        epi_swiglu_fwd<T>(p, taddr, row, n_idx * (BN / 2), half, stg, &tmO0, &tmO1, &tmO2, lane);
+      if (EPI == EPI_SWIGLU_BWD) epi_swiglu_bwd<T>(p, taddr, row, n_idx * BN, half, stg, &tmO0, &tmO1, lane);
+      if (EPI == EPI_LCE) epi_lce<T>(p, taddr, row, n_idx * BN, n_idx, half, stg, &tmO0, lane);
       ptx::tcgen05_fence_before_sync();
       if (leader)
         ptx::mbar_arrive(&tempty[acc]);
@@ -871,6 +1018,7 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (stg.base != 0 && lane == 0) ptx::bulk_wait_group<0>();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -989,7 +1137,12 @@ inline int encode_tmap(CUtensorMap* tm, const Operand& o, int dtype, const char*
   }
   cuuint64_t dims[2];
   cuuint32_t box[2];
-  if (o.kmajor) {
+  if (o.kmajor == 2) {  // a result tensor [rows = mn, cols = k]: 32 x 32 boxes of 16-bit elements
+    dims[0] = static_cast<cuuint64_t>(o.k);
+    dims[1] = static_cast<cuuint64_t>(o.mn);
+    box[0] = 32;
+    box[1] = 32;
+  } else if (o.kmajor) {
     dims[0] = static_cast<cuuint64_t>(o.k);
     dims[1] = static_cast<cuuint64_t>(o.mn);
     box[0] = static_cast<cuuint32_t>(row_elems);
@@ -1007,8 +1160,9 @@ inline int encode_tmap(CUtensorMap* tm, const Operand& o, int dtype, const char*
                                                     : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   const CUresult r = fn(tm, dt, 2, const_cast<void*>(o.ptr), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        (dtype == BT_FP32 && !o.kmajor) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
-                                                        : CU_TENSOR_MAP_SWIZZLE_128B,
+                        o.kmajor == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
+                        : (dtype == BT_FP32 && !o.kmajor) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                                          : CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error("%s: cuTensorMapEncodeTiled failed with CUresult %d (dims %llu x %llu, ld %lld)", what,
@@ -1021,7 +1175,8 @@ inline int encode_tmap(CUtensorMap* tm, const Operand& o, int dtype, const char*
 
 template <int EPI, typename T>
 int launch_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1,
-             const CUtensorMap& b1, const CUtensorMap& a2, const Params& p, cudaStream_t s) {
+             const CUtensorMap& b1, const CUtensorMap& a2, const CUtensorMap (&o)[3], const Params& p,
+             cudaStream_t s) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   auto* kern = gemm_kernel<EPI, T>;
@@ -1034,9 +1189,16 @@ int launch_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1
     return BT_ERR_LAUNCH;
   }
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  kern<<<grid, kThreads, kSmemBytes, s>>>(a0, b0, a1, b1, a2, p);
+  kern<<<grid, kThreads, kSmemBytes, s>>>(a0, b0, a1, b1, a2, o[0], o[1], o[2], p);
   BT_CHECK_LAUNCH("gemm_kernel");
   return BT_OK;
+}
+
+// 1 (default): 16-bit results are staged in shared memory and written with tile stores;
+// 0: every epilogue thread stores its own row pieces.
+inline int& tma_out_mode() {
+  static int mode = 1;
+  return mode;
 }
 
 // 0 (default): tiles are dealt round-robin; 1: CTA pairs draw them from a global counter.
@@ -1078,7 +1240,8 @@ inline int sched_slot_of(cudaStream_t s) {
 
 template <int EPI, typename T>
 int launch_pair_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1,
-                  const CUtensorMap& b1, const CUtensorMap& a2, const Params& p, cudaStream_t s) {
+                  const CUtensorMap& b1, const CUtensorMap& a2, const CUtensorMap (&o)[3],
+                  const Params& p, cudaStream_t s) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   auto* kern = gemm_kernel_pair<EPI, T>;
@@ -1128,7 +1291,7 @@ int launch_pair_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMa
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a0, b0, a1, b1, a2, q);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a0, b0, a1, b1, a2, o[0], o[1], o[2], q);
   if (e != cudaSuccess) {
     set_error("gemm_kernel_pair: %s", cudaGetErrorString(e));
     return BT_ERR_LAUNCH;
@@ -1256,17 +1419,63 @@ int launch(Launch& L, cudaStream_t s) {
     L.b1.box_mn = b_box;
     if ((rc = make_tmap(&tb1, L.b1, L.dtype, "gemm B1")) != BT_OK) return rc;
   }
+  // 16-bit results with 16-byte aligned rows leave through shared memory and tile stores
+  CUtensorMap to[3];
+  to[0] = to[1] = to[2] = ta0;  // placeholders when unused
+  p.tma_out = 0;
+  if (tma_out_mode() != 0 && L.dtype != BT_FP32 && !p.out_fp32 && p.vec_ok) {
+    struct Out {
+      void* ptr;
+      int64_t rows, cols, ld;
+    } outs[3] = {};
+    int n_out = 0;
+    if (EPI == EPI_PLAIN) {
+      if (p.n_seg0 > 0) {
+        outs[0] = {p.out, p.M, p.n_seg0, p.ldo};
+        outs[1] = {p.out1, p.M, p.n_seg1, p.ldo1};
+        outs[2] = {p.out2, p.M, p.N - p.n_seg0 - p.n_seg1, p.ldo2};
+        n_out = 3;
+      } else {
+        outs[0] = {p.out, p.M, p.N, p.ldo};
+        n_out = 1;
+      }
+    } else if (EPI == EPI_SWIGLU_FWD) {
+      outs[0] = {p.gate, p.M, p.N, p.ld_act};
+      outs[1] = {p.up, p.M, p.N, p.ld_act};
+      outs[2] = {p.h, p.M, p.N, p.ld_act};
+      n_out = 3;
+    } else if (EPI == EPI_SWIGLU_BWD) {
+      outs[0] = {p.out, p.M, p.N, p.ldo};
+      outs[1] = {p.h, p.M, p.N, p.ldo};
+      n_out = 2;
+    } else {
+      outs[0] = {p.out, p.M, p.N, p.ldo};
+      n_out = 1;
+    }
+    bool ok = true;
+    for (int i = 0; i < n_out && ok; ++i) {
+      Operand o;
+      o.ptr = outs[i].ptr;
+      o.kmajor = 2;  // marks a result map (box 32 x 32, 64-byte swizzle) in the cache key
+      o.mn = outs[i].rows;
+      o.k = outs[i].cols;
+      o.ld = outs[i].ld;
+      o.box_mn = 32;
+      ok = outs[i].ptr != nullptr && make_tmap(&to[i], o, L.dtype, "gemm result") == BT_OK;
+    }
+    p.tma_out = ok ? 1 : 0;
+  }
   if (pair) {
     switch (L.dtype) {
-      case BT_BF16: return launch_pair_t<EPI, __nv_bfloat16>(ta0, tb0, ta1, tb1, ta2, p, s);
-      case BT_FP16: return launch_pair_t<EPI, __half>(ta0, tb0, ta1, tb1, ta2, p, s);
-      default: return launch_pair_t<EPI, float>(ta0, tb0, ta1, tb1, ta2, p, s);
+      case BT_BF16: return launch_pair_t<EPI, __nv_bfloat16>(ta0, tb0, ta1, tb1, ta2, to, p, s);
+      case BT_FP16: return launch_pair_t<EPI, __half>(ta0, tb0, ta1, tb1, ta2, to, p, s);
+      default: return launch_pair_t<EPI, float>(ta0, tb0, ta1, tb1, ta2, to, p, s);
     }
   }
   switch (L.dtype) {
-    case BT_BF16: return launch_t<EPI, __nv_bfloat16>(ta0, tb0, ta1, tb1, ta2, p, s);
-    case BT_FP16: return launch_t<EPI, __half>(ta0, tb0, ta1, tb1, ta2, p, s);
-    default: return launch_t<EPI, float>(ta0, tb0, ta1, tb1, ta2, p, s);
+    case BT_BF16: return launch_t<EPI, __nv_bfloat16>(ta0, tb0, ta1, tb1, ta2, to, p, s);
+    case BT_FP16: return launch_t<EPI, __half>(ta0, tb0, ta1, tb1, ta2, to, p, s);
+    default: return launch_t<EPI, float>(ta0, tb0, ta1, tb1, ta2, to, p, s);
   }
 }
 

@@ -112,6 +112,12 @@ extern "C" int bt_set_gemm_cta_pairs(int enable) {
   return prev;
 }
 
+extern "C" int bt_set_gemm_tile_stores(int enable) {
+  const int prev = bt::gemm::tma_out_mode();
+  if (enable >= 0) bt::gemm::tma_out_mode() = enable ? 1 : 0;
+  return prev;
+}
+
 extern "C" int bt_set_gemm_dynamic_tiles(int enable) {
   const int prev = bt::gemm::dynamic_tiles();
   if (enable >= 0) bt::gemm::dynamic_tiles() = enable ? 1 : 0;

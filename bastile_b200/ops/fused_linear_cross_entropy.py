@@ -38,12 +38,14 @@ from .. import _lib
 _GEMM_DTYPES = (torch.bfloat16, torch.float16, torch.float32)
 
 # With the default chunk_size the op may work on up to this many rows at a time as long as
-# the 16-bit logits chunk stays under AUTO_CHUNK_BYTES: 8192 rows x 4096 hidden is a whole
-# number of waves of 128x256 tiles on 148 SMs for the dx GEMM, and fewer chunks mean fewer
-# read-modify-write passes over the fp32 dW accumulator.  An explicit chunk_size is obeyed.
+# the 16-bit logits chunk stays under AUTO_CHUNK_BYTES.  Fewer chunks mean fewer passes over
+# the fp32 dW accumulator, and with ONE chunk there is no accumulator at all: the single dW
+# product is deferred to the backward and written once in the weight dtype.  At 16384 rows x
+# 151936 columns the logits chunk (5 GB) takes exactly the room that an 8192-row chunk plus
+# the [151936, 4096] fp32 accumulator would.  An explicit chunk_size is obeyed.
 DEFAULT_CHUNK = 4096
-AUTO_CHUNK_ROWS = 8192
-AUTO_CHUNK_BYTES = 3 << 30
+AUTO_CHUNK_ROWS = 16384
+AUTO_CHUNK_BYTES = 11 << 29  # 5.5 GiB
 # a [B, T', H] input that cannot be flattened without a copy is processed batch entry by batch entry
 # when T' is at least this (shorter entries are copied once instead: many small launches cost more)
 _SEGMENT_MIN_ROWS = 1024

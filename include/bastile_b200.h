@@ -231,6 +231,13 @@ int bt_gemm_ex(const bt_gemm_desc* desc, int32_t* status, void* stream);
  * counterpart (cuBLAS picks its own kernels). */
 int bt_set_gemm_cta_pairs(int enable);
 
+/* How the tensor-core kernels write 16-bit results whose rows are 16-byte aligned: 1 (default) =
+ * every epilogue warp stages 32 x 32 pieces in shared memory and issues tile stores
+ * (cp.async.bulk.tensor), 0 = every thread stores its own row pieces from registers.  Same
+ * bits either way.  A negative argument only queries; returns the previous setting.  Process-wide.
+ * No reference counterpart. */
+int bt_set_gemm_tile_stores(int enable);
+
 /* ------------------------------------------- per-head RMSNorm + RoPE, fused */
 
 /* q_norm / k_norm followed by the rotary embedding, for the two tensors of

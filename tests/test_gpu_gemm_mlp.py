@@ -301,3 +301,53 @@ def test_mlp_bwd_c_abi_with_separate_buffers_and_skipped_outputs():
     _lib.check_status(dev, "mlp c abi")
     assert torch.equal(dx, xs.grad) and torch.equal(dwd, wds.grad)
     assert_close(dwg, wgs.grad, what="dWg", rtol=1e-2, atol=1e-2 * float(wgs.grad.float().abs().max()))
+
+
+@pytest.mark.parametrize("pairs", [1, 0])
+def test_tile_stores_give_the_same_bits_as_register_stores(pairs):
+    """16-bit results staged in shared memory and written by tile stores (the default) against the
+    per-thread stores: MLP forward/backward, the fused loss and a plain product, with ragged row and
+    column counts (rows and columns past the tensor are clipped by the store)."""
+    from bastile_b200 import _lib
+    from bastile_b200.ops.fused_linear_cross_entropy import fused_linear_cross_entropy
+    from bastile_b200.ops.swiglu import SwiGLUMLPFunction
+
+    lib = _lib.get_lib()
+    prev_pairs = lib.bt_set_gemm_cta_pairs(pairs)
+    prev = lib.bt_set_gemm_tile_stores(-1)
+    results = {}
+    try:
+        for mode in (1, 0):
+            lib.bt_set_gemm_tile_stores(mode)
+            out = []
+            for t, hidden, inter in ((333, 256, 640), (1000, 512, 1288), (7, 128, 136)):
+                x, wg, wu, wd, dy = _mlp_case(t, hidden, inter, torch.bfloat16, seed=6)
+                xs, wgs, wus, wds = (a.clone().requires_grad_(True) for a in (x, wg, wu, wd))
+                y = SwiGLUMLPFunction.apply(xs, wgs, wus, wds)
+                y.backward(dy)
+                out += [y.detach(), xs.grad, wgs.grad, wus.grad, wds.grad]
+            torch.manual_seed(7)
+            for rows, hidden, vocab in ((300, 128, 1000), (77, 256, 4104)):
+                x = torch.randn(rows, hidden, device=DEV, dtype=torch.bfloat16).requires_grad_(True)
+                w = (torch.randn(vocab, hidden, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_(True)
+                tg = torch.randint(0, vocab, (rows,), device=DEV)
+                tg[::5] = -100
+                loss = fused_linear_cross_entropy(x, w, tg, chunk_size=128)
+                loss.backward()
+                out += [loss.detach(), x.grad, w.grad]
+            a = torch.randn(515, 200, device=DEV, dtype=torch.float16)
+            b = torch.randn(264, 200, device=DEV, dtype=torch.float16)
+            d = torch.empty(515, 264, device=DEV, dtype=torch.float16)
+            st = _lib.status_word(a.device)
+            _lib.check(lib.bt_gemm(a.data_ptr(), b.data_ptr(), d.data_ptr(), 515, 264, 200, 200, 200, 264, 1, 1, 1, 1,
+                                   None, 0, None, st.data_ptr(), _lib.stream_ptr(a.device)), "gemm")
+            out.append(d)
+            _lib.check_status(a.device, f"tile stores {mode}")
+            results[mode] = out
+    finally:
+        lib.bt_set_gemm_tile_stores(prev)
+        lib.bt_set_gemm_cta_pairs(prev_pairs)
+    for i, (u, v) in enumerate(zip(results[1], results[0])):
+        assert torch.equal(u, v), f"result {i} differs between tile stores and register stores"
+    ref = (a.float() @ b.float().T)
+    assert_close(results[1][-1], ref, what="plain product", rtol=2e-2, atol=2e-2 * float(ref.abs().max()))

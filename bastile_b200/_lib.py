@@ -46,6 +46,7 @@ SIGNATURES = {
     "bt_last_error": (c_char_p, []),
     "bt_sm_count": (c_int, []),
     "bt_device_wait_errors": (c_int, []),
+    "bt_set_wait_limit_ms": (c_int, [c_int64]),
     "bt_rmsnorm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                c_float, c_int, c_void_p]),
     "bt_rmsnorm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,

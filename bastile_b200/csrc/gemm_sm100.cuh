@@ -714,7 +714,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
       int m_idx, n_idx;
       tile_coords(p, tile, &m_idx, &n_idx);
-      if (!ptx::mbar_wait(&tfull[acc], acc_phase, cta_abort, p.status, ST_EPILOGUE)) break;
+      // all 32 lanes leave together: what follows is warp-synchronous (tcgen05.ld.sync.aligned)
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&tfull[acc], acc_phase, cta_abort, p.status, ST_EPILOGUE)))
+        break;
       ptx::tcgen05_fence_after_sync();
       const uint32_t taddr =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
@@ -800,7 +802,7 @@ __device__ __forceinline__ int sched_wait(const Params& p, int pair, int npairs,
     if (static_cast<unsigned int>(v >> 32) == static_cast<unsigned int>(i + 1))
       return static_cast<int>(static_cast<unsigned int>(v)) - 1;
     if (*cta_abort != 0) return -1;
-    if (ptx::globaltimer_ns() - t0 > 1000000000ull) {
+    if (ptx::globaltimer_ns() - t0 > *reinterpret_cast<volatile unsigned long long*>(&ptx::g_wait_limit_ns)) {
       *cta_abort = 1;
       if (p.status != nullptr) atomicOr(p.status, status_bit);
       return -1;
@@ -999,7 +1001,8 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
       if (tile < 0) break;
       int m_idx, n_idx;
       tile_coords(p, tile, &m_idx, &n_idx);
-      if (!ptx::mbar_wait(&tfull[acc], acc_phase, cta_abort, p.status, ST_EPILOGUE)) break;
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&tfull[acc], acc_phase, cta_abort, p.status, ST_EPILOGUE)))
+        break;
       ptx::tcgen05_fence_after_sync();
       const uint32_t taddr =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);

@@ -597,6 +597,19 @@ extern "C" int64_t bt_rmsnorm_bwd_ws_bytes(int64_t N) {
   return (static_cast<int64_t>(bt::dw_copies(N)) * N + 1) * 4;
 }
 
+int bt_internal_set_wait_limit_tc(unsigned long long ns);  // tc_ops.cu
+
+extern "C" int bt_set_wait_limit_ms(int64_t ms) {
+  using namespace bt;
+  BT_CHECK_ARG(ms >= 1 && ms <= 600000, "set_wait_limit_ms: the limit must be 1 ms .. 10 min");
+  const unsigned long long ns = static_cast<unsigned long long>(ms) * 1000000ull;
+  if (ptx::set_wait_limit_ns(ns) != cudaSuccess || bt_internal_set_wait_limit_tc(ns) != 0) {
+    set_error("set_wait_limit_ms: writing the limit to the device failed");
+    return BT_ERR_LAUNCH;
+  }
+  return BT_OK;
+}
+
 extern "C" int bt_device_wait_errors(void) {
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, bt::staged::g_wait_error, sizeof(int)) != cudaSuccess) return -1;

@@ -121,14 +121,17 @@ rms_fwd_staged(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__
   uint32_t phase = 0;
   int buf = 0;
   for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-    if (!ptx::mbar_wait(&ring->full[s], phase, &ring->abort_flag, &g_wait_error, 1)) break;
+    // A thread whose wait ran out (or that saw another thread give up) does not leave by itself:
+    // it skips the arithmetic, joins the block-wide sum below, and after that barrier EVERY thread
+    // reads the same abort flag and leaves together - no thread is ever left alone at a barrier.
+    const bool ok = ptx::mbar_wait(&ring->full[s], phase, &ring->abort_flag, &g_wait_error, 1);
     uint8_t* st = data + s * stage_bytes;
     const int64_t r0 = tile * R;
     float ss[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       ss[r] = 0.f;
-      if (r0 + r < M) {
+      if (ok && r0 + r < M) {
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
           const int v = threadIdx.x + i * kThreads;
@@ -154,6 +157,7 @@ rms_fwd_staged(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__
       }
     }
     block_sums<R>(ss, red + buf * R * kWarps, warp, lane);
+    if (*reinterpret_cast<volatile int*>(&ring->abort_flag) != 0) break;  // same value in every thread
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       const int64_t row = r0 + r;
@@ -260,7 +264,8 @@ rms_bwd_staged(const T* __restrict__ dy, const T* __restrict__ x, const T* __res
                          : make_uint4(0, 0, 0, 0);
         }
     }
-    if (!ptx::mbar_wait(&ring->full[s], phase, &ring->abort_flag, &g_wait_error, 2)) break;
+    // as in the forward: nobody leaves before the barrier inside block_sums, everybody after it
+    const bool ok = ptx::mbar_wait(&ring->full[s], phase, &ring->abort_flag, &g_wait_error, 2);
     const uint8_t* sx = data + s * stage_bytes;
     const uint8_t* sg = sx + R * row_bytes;
     float dot[R], rs[R];
@@ -268,7 +273,7 @@ rms_bwd_staged(const T* __restrict__ dy, const T* __restrict__ x, const T* __res
     for (int r = 0; r < R; ++r) {
       dot[r] = 0.f;
       rs[r] = (r0 + r < M) ? rstd[r0 + r] : 0.f;
-      if (r0 + r < M) {
+      if (ok && r0 + r < M) {
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
           const int v = threadIdx.x + i * kThreads;
@@ -287,6 +292,7 @@ rms_bwd_staged(const T* __restrict__ dy, const T* __restrict__ x, const T* __res
       }
     }
     block_sums<R>(dot, red + buf * R * kWarps, warp, lane);
+    if (*reinterpret_cast<volatile int*>(&ring->abort_flag) != 0) break;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       const int64_t row = r0 + r;

@@ -63,24 +63,34 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // `kWaitLimitNs` (or as soon as another role of this CTA has given up) the wait
 // returns false, having recorded `code` in the global status word.  Callers
 // leave their role loop on false and fall through to the common teardown.
-constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s
+constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s: the default
+// The limit in force, in nanoseconds of %globaltimer (wall time: a context that is descheduled -
+// time-slicing, MPS, a debugger - keeps counting).  One copy per translation unit and device;
+// bt_set_wait_limit_ms() writes all of them on the current device.
+static __device__ unsigned long long g_wait_limit_ns = kWaitLimitNs;
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* cta_abort,
                                           int32_t* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
+  const uint64_t limit = *reinterpret_cast<volatile unsigned long long*>(&g_wait_limit_ns);
   uint32_t spins = 0;
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
     if (((++spins) & 0xffu) == 0) {
       if (*cta_abort != 0) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > limit) {
         *cta_abort = 1;
         if (status != nullptr) atomicOr(status, code);
         return false;
       }
     }
   }
+}
+
+// Host side: set this translation unit's copy of the limit on the current device.
+inline cudaError_t set_wait_limit_ns(unsigned long long ns) {
+  return cudaMemcpyToSymbol(g_wait_limit_ns, &ns, sizeof(ns));
 }
 
 // ----------------------------------------------------------------------- TMA

@@ -112,6 +112,11 @@ extern "C" int bt_set_gemm_cta_pairs(int enable) {
   return prev;
 }
 
+// the tensor-core kernels' copy of the wait limit (called by bt_set_wait_limit_ms in rmsnorm.cu)
+int bt_internal_set_wait_limit_tc(unsigned long long ns) {
+  return bt::ptx::set_wait_limit_ns(ns) == cudaSuccess ? 0 : -1;
+}
+
 extern "C" int bt_set_gemm_tile_stores(int enable) {
   const int prev = bt::gemm::tma_out_mode();
   if (enable >= 0) bt::gemm::tma_out_mode() = enable ? 1 : 0;

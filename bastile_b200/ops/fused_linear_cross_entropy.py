@@ -38,14 +38,15 @@ from .. import _lib
 _GEMM_DTYPES = (torch.bfloat16, torch.float16, torch.float32)
 
 # With the default chunk_size the op may work on up to this many rows at a time as long as
-# the 16-bit logits chunk stays under AUTO_CHUNK_BYTES.  Fewer chunks mean fewer passes over
-# the fp32 dW accumulator, and with ONE chunk there is no accumulator at all: the single dW
-# product is deferred to the backward and written once in the weight dtype.  At 16384 rows x
-# 151936 columns the logits chunk (5 GB) takes exactly the room that an 8192-row chunk plus
-# the [151936, 4096] fp32 accumulator would.  An explicit chunk_size is obeyed.
+# the 16-bit logits chunk stays under AUTO_CHUNK_BYTES: 8192 rows x 4096 hidden is a whole
+# number of waves of tiles for the dx GEMM, and fewer chunks mean fewer read-modify-write
+# passes over the fp32 dW accumulator.  Larger is not better: with 16384 rows per chunk (no
+# accumulator at all at 16384 x 151936) the call measured 55-56 ms instead of 51 ms on a B200 -
+# the operand panel that a group of row tiles shares (16 x 256 vocabulary rows x 16384 rows of
+# dlogits = 134 MB) no longer fits the 126 MB L2.  An explicit chunk_size is obeyed.
 DEFAULT_CHUNK = 4096
-AUTO_CHUNK_ROWS = 16384
-AUTO_CHUNK_BYTES = 11 << 29  # 5.5 GiB
+AUTO_CHUNK_ROWS = 8192
+AUTO_CHUNK_BYTES = 3 << 30
 # a [B, T', H] input that cannot be flattened without a copy is processed batch entry by batch entry
 # when T' is at least this (shorter entries are copied once instead: many small launches cost more)
 _SEGMENT_MIN_ROWS = 1024

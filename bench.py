@@ -843,6 +843,9 @@ def main():
                     help="how the GEMM's CTA pairs get their tiles: dealt round-robin at launch (fixed) or drawn from "
                          "a global counter at run time (dynamic: bt_set_gemm_dynamic_tiles(1)); auto = dynamic when "
                          "NCCL collectives share the GPU with the backward pass (more than one rank), else fixed")
+    ap.add_argument("--tile-stores", default="on", choices=["on", "off"],
+                    help="16-bit GEMM results through shared memory + tile stores (on, the library's default) or "
+                         "stored by each epilogue thread from registers (off: bt_set_gemm_tile_stores(0))")
     ap.add_argument("--no-per-op", action="store_true")
     ap.add_argument("--only-op", default=None, choices=["rmsnorm", "rope", "swiglu", "mlp", "lce"],
                     help="run just this op's forward+backward micro-benchmark (small case for profilers)")
@@ -873,6 +876,7 @@ def main():
     from bastile_b200 import _lib
 
     peaks, peak_kind = load_peaks()
+    _lib.get_lib().bt_set_gemm_tile_stores(1 if args.tile_stores == "on" else 0)
     if args.only_op:
         res = per_op_bench(peaks, only=args.only_op, iters=args.op_iters)
         _lib.check_status(dev, "per-op benchmark")

@@ -52,6 +52,15 @@ const char* bt_last_error(void);
 /* Number of SMs of the current device (src/bastile/ops/utils.py:8-13). */
 int bt_sm_count(void);
 
+/* Every device-side wait of this library (mbarrier waits of the tensor-core and bulk-copy
+ * kernels, polls of the run-time tile hand-out) gives up after a limit and reports through the
+ * status word / bt_device_wait_errors().  The limit is WALL time on the device clock (default
+ * 1000 ms): it keeps counting while the context is descheduled (time-slicing between
+ * processes, MPS, a debugger), so a process that shares its GPU that way should raise it.  Sets
+ * the limit for kernels launched afterwards on the CURRENT device; 1 .. 600000 ms.  No reference
+ * counterpart (CuTile kernels do not wait on one another). */
+int bt_set_wait_limit_ms(int64_t ms);
+
 /* Synchronising read-and-clear of the device word in which the RMSNorm kernels
  * record a bulk-copy wait that ran out (0 = none, -1 = the read failed).  For
  * tests and debugging; no reference counterpart. */

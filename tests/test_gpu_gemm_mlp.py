@@ -351,3 +351,22 @@ def test_tile_stores_give_the_same_bits_as_register_stores(pairs):
         assert torch.equal(u, v), f"result {i} differs between tile stores and register stores"
     ref = (a.float() @ b.float().T)
     assert_close(results[1][-1], ref, what="plain product", rtol=2e-2, atol=2e-2 * float(ref.abs().max()))
+
+
+def test_wait_limit_can_be_raised_and_is_validated():
+    """bt_set_wait_limit_ms: out-of-range values are refused, a raised limit leaves results alone."""
+    from bastile_b200 import _lib
+    from bastile_b200.ops.swiglu import SwiGLUMLPFunction
+
+    lib = _lib.get_lib()
+    assert lib.bt_set_wait_limit_ms(0) != 0 and b"limit" in lib.bt_last_error()
+    assert lib.bt_set_wait_limit_ms(10 ** 7) != 0
+    x, wg, wu, wd, dy = _mlp_case(130, 128, 256, torch.bfloat16, seed=9)
+    y0 = SwiGLUMLPFunction.apply(x, wg, wu, wd)
+    try:
+        _lib.check(lib.bt_set_wait_limit_ms(5000), "bt_set_wait_limit_ms")
+        y1 = SwiGLUMLPFunction.apply(x, wg, wu, wd)
+        _lib.check_status(x.device, "raised wait limit")
+        assert torch.equal(y0, y1)
+    finally:
+        _lib.check(lib.bt_set_wait_limit_ms(1000), "bt_set_wait_limit_ms")

@@ -1204,6 +1204,13 @@ inline int& tma_out_mode() {
   return mode;
 }
 
+// Row tiles walked per column tile before the walk moves on (tile rasterisation); 0 = the
+// built-in choice.
+inline int& group_m_override() {
+  static int g = 0;
+  return g;
+}
+
 // 0 (default): tiles are dealt round-robin; 1: CTA pairs draw them from a global counter.
 inline int& dynamic_tiles() {
   static int mode = 0;
@@ -1373,7 +1380,7 @@ int launch(Launch& L, cudaStream_t s) {
     return BT_ERR_ARG;
   }
   p.num_tiles = static_cast<int>(nt);
-  p.group_m = kGroupM;
+  p.group_m = group_m_override() > 0 ? group_m_override() : kGroupM;
   p.a_kmajor = L.a0.kmajor;
   p.b_kmajor = L.b0.kmajor;
   p.dual_b = L.dual_b ? 1 : 0;

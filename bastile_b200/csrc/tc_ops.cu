@@ -117,6 +117,12 @@ int bt_internal_set_wait_limit_tc(unsigned long long ns) {
   return bt::ptx::set_wait_limit_ns(ns) == cudaSuccess ? 0 : -1;
 }
 
+extern "C" int bt_set_gemm_group_rows(int row_tiles) {
+  const int prev = bt::gemm::group_m_override();
+  if (row_tiles >= 0) bt::gemm::group_m_override() = row_tiles;
+  return prev;
+}
+
 extern "C" int bt_set_gemm_tile_stores(int enable) {
   const int prev = bt::gemm::tma_out_mode();
   if (enable >= 0) bt::gemm::tma_out_mode() = enable ? 1 : 0;

@@ -529,11 +529,11 @@ def vp_parity_check(dev, rank, world):
         out["shard_tokens" if shard_tokens else "all_rows_on_every_rank"] = {
             "loss_rel_err": e[0], "dx_max_abs_over_max": e[1], "dw_shard_max_abs_over_max": e[2]}
         del x1, w1
-    out["loss_unsharded"] = float(loss0)
-    out["tolerance"] = {"loss_rel_err": 1e-3, "gradients": 2e-2}
+    checks = [v for v in out.values() if isinstance(v, dict)]
     out["ok"] = all(v["loss_rel_err"] <= 1e-3 and v["dx_max_abs_over_max"] <= 2e-2 and
-                    v["dw_shard_max_abs_over_max"] <= 2e-2 for k, v in out.items() if isinstance(v, dict) and
-                    "loss_rel_err" in v)
+                    v["dw_shard_max_abs_over_max"] <= 2e-2 for v in checks)
+    out["loss_unsharded"] = float(loss0.detach())
+    out["tolerance"] = {"loss": 1e-3, "gradients": 2e-2}
     return out
 
 
@@ -846,6 +846,8 @@ def main():
     ap.add_argument("--tile-stores", default="on", choices=["on", "off"],
                     help="16-bit GEMM results through shared memory + tile stores (on, the library's default) or "
                          "stored by each epilogue thread from registers (off: bt_set_gemm_tile_stores(0))")
+    ap.add_argument("--group-rows", type=int, default=0,
+                    help="tile rasterisation of the GEMMs: row tiles walked per column tile (0 = library default)")
     ap.add_argument("--no-per-op", action="store_true")
     ap.add_argument("--only-op", default=None, choices=["rmsnorm", "rope", "swiglu", "mlp", "lce"],
                     help="run just this op's forward+backward micro-benchmark (small case for profilers)")
@@ -877,6 +879,7 @@ def main():
 
     peaks, peak_kind = load_peaks()
     _lib.get_lib().bt_set_gemm_tile_stores(1 if args.tile_stores == "on" else 0)
+    _lib.get_lib().bt_set_gemm_group_rows(args.group_rows)
     if args.only_op:
         res = per_op_bench(peaks, only=args.only_op, iters=args.op_iters)
         _lib.check_status(dev, "per-op benchmark")

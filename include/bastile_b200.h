@@ -247,6 +247,13 @@ int bt_set_gemm_cta_pairs(int enable);
  * No reference counterpart. */
 int bt_set_gemm_tile_stores(int enable);
 
+/* Tile rasterisation of the tensor-core kernels: CTAs walk `row_tiles` row tiles of the result
+ * for one column tile before moving to the next column tile, so that concurrently running CTAs
+ * share operand tiles in L2.  0 (default) = the library's own choice per launch; a negative
+ * argument only queries; returns the previous setting.  Process-wide; a tuning knob with no
+ * reference counterpart (cuBLAS picks its own schedule). */
+int bt_set_gemm_group_rows(int row_tiles);
+
 /* ------------------------------------------- per-head RMSNorm + RoPE, fused */
 
 /* q_norm / k_norm followed by the rotary embedding, for the two tensors of

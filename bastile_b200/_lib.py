@@ -172,6 +172,31 @@ class device_of:
         return False
 
 
+# Where the gradient of a weight should be written, keyed by the weight's data pointer.  An
+# optimizer that keeps gradients in flat buckets (optim.ShardedAdamW) registers its bucket views
+# here; the ops that allocate weight gradients themselves (MLP block, fused loss) then write
+# straight into the bucket instead of into a fresh tensor that would be copied there afterwards.
+_grad_sinks: dict[int, torch.Tensor] = {}
+
+
+def register_grad_sink(weight: torch.Tensor, destination: torch.Tensor) -> None:
+    _grad_sinks[weight.data_ptr()] = destination
+
+
+def unregister_grad_sinks(destinations) -> None:
+    ids = {id(d) for d in destinations}
+    for key in [k for k, v in _grad_sinks.items() if id(v) in ids]:
+        del _grad_sinks[key]
+
+
+def grad_sink(weight: torch.Tensor, dtype: torch.dtype):
+    """The registered destination for ``weight``'s gradient if it fits (shape, dtype, device)."""
+    dest = _grad_sinks.get(weight.data_ptr())
+    if dest is None or dest.shape != weight.shape or dest.dtype != dtype or dest.device != weight.device:
+        return None
+    return dest
+
+
 # Per (device, stream) scratch that must start zeroed and that kernels leave zeroed.
 _zero_ws: dict[tuple[int, int], torch.Tensor] = {}
 # Per (device, stream) int32 status word for the bounded waits of the GEMM kernels.

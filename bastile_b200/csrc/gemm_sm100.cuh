@@ -1380,7 +1380,16 @@ int launch(Launch& L, cudaStream_t s) {
     return BT_ERR_ARG;
   }
   p.num_tiles = static_cast<int>(nt);
-  p.group_m = group_m_override() > 0 ? group_m_override() : kGroupM;
+  // Rasterisation: CTAs that run at the same time share operand tiles through L2.  With a short
+  // contraction the A panel of 16 row tiles (16 x 256 rows x K) stays in L2 while the walk
+  // crosses all column tiles, so B is fetched once per 16 row tiles.  With a long contraction
+  // that panel does not fit (K x element size > 16 KB <=> more than 64 MB) and nothing is
+  // reused between waves; then a wave of 74 tiles should be as square as possible (8 x 9
+  // tiles touch 17 panels, 16 x 4.6 touch 21).  Measured on the fused loss (dx has K = 151936):
+  // 49.9 ms with 8 against 51-52.5 ms with 16; the MLP block (K <= 24576) is indifferent.
+  const int64_t k_total = L.a_split == A_SPLIT_K ? L.b0.k : (L.a0.k + (L.two_pairs ? L.a1.k : 0));
+  const int esz = L.dtype == BT_FP32 ? 4 : 2;
+  p.group_m = group_m_override() > 0 ? group_m_override() : (k_total * esz > 16384 ? kGroupM / 2 : kGroupM);
   p.a_kmajor = L.a0.kmajor;
   p.b_kmajor = L.b0.kmajor;
   p.dual_b = L.dual_b ? 1 : 0;

@@ -224,7 +224,10 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
                 dx_out = dx_out.view(*batch_shape, hdim)
             if need_w:
                 out_dtype = w_dtype if w_dtype in _lib._DTYPES else x_dtype
-                dw_out = torch.empty((vloc, hdim), dtype=out_dtype, device=dev)
+                # straight into a registered gradient bucket of the weight, if there is one
+                dw_out = _lib.grad_sink(w, out_dtype) if w.dtype == w_dtype else None
+                if dw_out is None:
+                    dw_out = torch.empty((vloc, hdim), dtype=out_dtype, device=dev)
                 if n_chunks == 0:
                     dw_out.zero_()
                 else:

@@ -138,14 +138,22 @@ class SwiGLUMLPFunction(torch.autograd.Function):
         dgate, dup = dgu[:, :inter], dgu[:, inter:]
         dx = torch.empty_like(x2, memory_format=torch.contiguous_format) if need_x else None
         dwg = dwu = None
+        # a gradient destination registered for a weight (a flat bucket of a data-parallel optimizer)
+        # is written directly; dWg | dWu only when the two destinations are stacked like the result
+        sink_g, sink_u, sink_d = (_lib.grad_sink(w, dt) if w.dtype == dt else None
+                                  for w, dt in zip((wg, wu, wd), ctx.w_dtypes))
         if need_g and need_u:
-            dwgu = torch.empty((2 * inter, hidden), dtype=wg.dtype, device=dev)
-            dwg, dwu = dwgu[:inter], dwgu[inter:]
+            if (sink_g is not None and sink_u is not None
+                    and sink_u.data_ptr() == sink_g.data_ptr() + sink_g.numel() * sink_g.element_size()):
+                dwg, dwu = sink_g, sink_u
+            else:
+                dwgu = torch.empty((2 * inter, hidden), dtype=wg.dtype, device=dev)
+                dwg, dwu = dwgu[:inter], dwgu[inter:]
         elif need_g:
-            dwg = torch.empty_like(wg)
+            dwg = sink_g if sink_g is not None else torch.empty_like(wg)
         elif need_u:
-            dwu = torch.empty_like(wu)
-        dwd = torch.empty_like(wd) if need_d else None
+            dwu = sink_u if sink_u is not None else torch.empty_like(wu)
+        dwd = (sink_d if sink_d is not None else torch.empty_like(wd)) if need_d else None
         st = _lib.status_word(dev)
 
         def p(tensor):

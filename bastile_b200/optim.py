@@ -176,7 +176,7 @@ class AdamW(torch.optim.Optimizer):
 # ------------------------------------------------------------------------------------------
 class _Bucket:
     __slots__ = ("params", "offsets", "numel", "flat_p", "flat_g", "lo", "hi", "state", "pending", "arrived",
-                 "launched", "device", "dtype")
+                 "launched", "device", "dtype", "sinks")
 
 
 def _cuda_update(bucket, step, hyper, master_weights):
@@ -258,7 +258,7 @@ class ShardedAdamW:
             dev, dtype = key
             b = _Bucket()
             b.params, b.offsets, off = [], [], 0
-            for unit in units:
+            for unit in reversed(units):  # registration order inside the bucket (gate | up stay adjacent)
                 off = (off + align - 1) // align * align
                 for p in unit:  # members of a unit stay back to back, as they were
                     b.params.append(p)
@@ -281,9 +281,16 @@ class ShardedAdamW:
             if self.master_weights:
                 b.state["master"] = b.flat_p[b.lo:b.hi].to(torch.float32, copy=True)
             b.pending, b.arrived, b.launched = len(b.params), set(), False
+            b.sinks = []
             for i, p in enumerate(b.params):
                 self._where[p] = (b, i)
                 self._hooks.append(p.register_post_accumulate_grad_hook(self._on_grad))
+                if dev.type == "cuda":
+                    # ops that allocate this weight's gradient themselves write it here directly
+                    o = b.offsets[i]
+                    dest = b.flat_g[o:o + p.numel()].view(p.shape)
+                    _lib.register_grad_sink(p.data, dest)
+                    b.sinks.append(dest)
             self.buckets.append(b)
 
         # Units: runs of parameters that already lie one after the other in memory, in registration
@@ -347,10 +354,12 @@ class ShardedAdamW:
         if side is not None:
             side.wait_stream(torch.cuda.current_stream(b.device))  # the gradient's kernels are queued there
         o = b.offsets[i]
-        with self._On(side):
-            b.flat_g[o:o + p.numel()].view(p.shape).copy_(g)
-        if side is not None:
-            g.record_stream(side)
+        dest = b.flat_g[o:o + p.numel()]
+        if g.data_ptr() != dest.data_ptr():  # (an op that knew the destination wrote it there already)
+            with self._On(side):
+                dest.view(p.shape).copy_(g)
+            if side is not None:
+                g.record_stream(side)
         p.grad = None
         b.arrived.add(i)
         b.pending -= 1
@@ -404,6 +413,9 @@ class ShardedAdamW:
         for h in self._hooks:
             h.remove()
         self._hooks.clear()
+        for b in self.buckets:
+            _lib.unregister_grad_sinks(b.sinks)
+            b.sinks = []
 
     def state_bytes(self) -> int:
         """Bytes of optimizer state (moments, master copy) this rank holds."""

@@ -566,7 +566,7 @@ class _LigerPatches:
 def train_run(*, dev, rank, world, local, patches="bastile", parallel="single", optimizer="bastile", seq=SEQ_LEN,
               layers=36, intermediate=12288, steps=5, warmup=3, fused_layers=True, gemm_projections="off",
               overlap_opt=True, tiles="auto", grad_checkpoint=False, measure_e2e=True, sample_clocks=False,
-              master_weights=False, sweep=()):
+              master_weights=False, sweep=(), bucket_mb=256):
     """Build the model under the given patches / parallel wrapper / optimizer, run `warmup` untimed
     and `steps` timed steps (and, optionally, the same loop fed from pinned host memory), then the
     `sweep` entries (dicts with seq, steps, warmup, grad_checkpoint) on the same model.  Everything
@@ -658,7 +658,8 @@ def train_run(*, dev, rank, world, local, patches="bastile", parallel="single", 
     if optimizer == "bastile" and world > 1 and parallel == "sharded":
         from bastile_b200.optim import ShardedAdamW
 
-        opt = ShardedAdamW(net.parameters(), lr=1e-4, group=dist.group.WORLD, master_weights=master_weights)
+        opt = ShardedAdamW(net.parameters(), lr=1e-4, group=dist.group.WORLD, master_weights=master_weights,
+                           bucket_mb=bucket_mb)
         opt_name = "bastile_b200.optim.ShardedAdamW" + (", fp32 master weights" if master_weights else
                                                         ", bf16 params and state")
     elif optimizer == "bastile":
@@ -846,6 +847,7 @@ def main():
     ap.add_argument("--tile-stores", default="on", choices=["on", "off"],
                     help="16-bit GEMM results through shared memory + tile stores (on, the library's default) or "
                          "stored by each epilogue thread from registers (off: bt_set_gemm_tile_stores(0))")
+    ap.add_argument("--bucket-mb", type=int, default=256, help="--parallel sharded: size of a gradient bucket")
     ap.add_argument("--group-rows", type=int, default=0,
                     help="tile rasterisation of the GEMMs: row tiles walked per column tile (0 = library default)")
     ap.add_argument("--no-per-op", action="store_true")
@@ -913,7 +915,8 @@ def main():
     main_run = train_run(**common, patches="bastile", parallel=parallel, optimizer=args.optimizer, seq=args.seq,
                          intermediate=args.intermediate, steps=args.steps, warmup=args.warmup,
                          overlap_opt=not args.no_overlap_optimizer, grad_checkpoint=grad_checkpoint,
-                         measure_e2e=True, sample_clocks=True, master_weights=args.master_weights, sweep=sweep)
+                         measure_e2e=True, sample_clocks=True, master_weights=args.master_weights, sweep=sweep,
+                         bucket_mb=args.bucket_mb)
     m = main_run["main"]
     op_ms = m["op_ms"]
     seq = args.seq

@@ -195,3 +195,54 @@ def test_sharded_adamw_single_rank_matches_plain_adamw(master):
         else:  # AdamW batches small tensors into a scalar kernel whose fp32 contraction may differ by an ulp
             assert_close(a, b, what=name, rtol=1e-2, atol=1e-3)
     opts[1].close()
+
+
+@pytest.mark.gpu
+def test_sharded_adamw_gradient_sinks_are_written_directly():
+    """The MLP block and the fused loss write their weight gradients straight into ShardedAdamW's
+    flat buckets (no copy in the hook); parameters after a few steps equal the plain optimizer's."""
+    from types import SimpleNamespace
+
+    from bastile_b200 import _lib
+    from bastile_b200.ops.fused_linear_cross_entropy import fused_linear_cross_entropy
+    from bastile_b200.ops.swiglu import B200SwiGLUMLP
+    from bastile_b200.optim import AdamW, ShardedAdamW
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            torch.manual_seed(14)
+            self.mlp = B200SwiGLUMLP(SimpleNamespace(hidden_size=256, intermediate_size=768, hidden_act="silu"))
+            self.head = torch.nn.Linear(256, 1000, bias=False)
+
+        def forward(self, x, y):
+            return fused_linear_cross_entropy(x + self.mlp(x), self.head.weight, y)
+
+    nets = [Net().cuda().to(torch.bfloat16), Net().cuda().to(torch.bfloat16)]
+    hp = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    opts = [AdamW(nets[0].parameters(), **hp), ShardedAdamW(nets[1].parameters(), bucket_mb=1, **hp)]
+    seen = []
+    orig = opts[1]._on_grad
+
+    def spy(p):
+        b, i = opts[1]._where[p]
+        seen.append(p.grad.data_ptr() == b.flat_g[b.offsets[i]:].data_ptr())
+        orig(p)
+
+    for h in opts[1]._hooks:
+        h.remove()
+    opts[1]._hooks = [p.register_post_accumulate_grad_hook(spy) for p in nets[1].parameters()]
+    torch.manual_seed(15)
+    for _ in range(3):
+        x = torch.randn(300, 256, device="cuda", dtype=torch.bfloat16)
+        y = torch.randint(0, 1000, (300,), device="cuda")
+        for net, opt in zip(nets, opts):
+            opt.zero_grad(set_to_none=True)
+            net(x, y).backward()
+            opt.step()
+    _lib.check_all_status()
+    assert sum(seen) >= 3 * 3, f"gradients written in place: {sum(seen)} of {len(seen)}"  # gate, up or down, head
+    for (name, a), b in zip(nets[0].named_parameters(), nets[1].parameters()):
+        assert_close(a, b, what=name, rtol=1e-2, atol=1e-3)
+    opts[1].close()
+    assert not any(id(v) in {id(d) for bk in opts[1].buckets for d in bk.sinks} for v in _lib._grad_sinks.values())

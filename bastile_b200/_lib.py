@@ -194,7 +194,9 @@ def grad_sink(weight: torch.Tensor, dtype: torch.dtype):
     dest = _grad_sinks.get(weight.data_ptr())
     if dest is None or dest.shape != weight.shape or dest.dtype != dtype or dest.device != weight.device:
         return None
-    return dest
+    # a FRESH view object: autograd only adopts an incoming gradient without cloning it when nothing
+    # else holds a reference to that tensor object (the registry keeps the original)
+    return dest.view(dest.shape)
 
 
 # Per (device, stream) scratch that must start zeroed and that kernels leave zeroed.

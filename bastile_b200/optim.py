@@ -208,7 +208,8 @@ class ShardedAdamW:
     all-gather of the parameters - without re-sharding the weights for every layer:
 
     * parameters are re-laid as views into flat buckets (``bucket_mb`` each, filled in reverse
-      registration order, the order in which gradients become final);
+      registration order, the order in which gradients become final; 1 GiB measured best on a
+      Qwen3-8B step on two B200: 416 ms against 420 ms with 256 MiB and 429 ms with 64 MiB);
     * a post-accumulate-grad hook copies each gradient into its bucket on a side stream; when a
       bucket is complete the side stream reduce-scatters it (NCCL, average), runs the AdamW
       kernel on this rank's 1/N slice of the bucket (moments - and the fp32 master copy with
@@ -225,7 +226,7 @@ class ShardedAdamW:
     """
 
     def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 1e-2,
-                 group=None, bucket_mb: int = 256, master_weights: bool = False, update_fn=None):
+                 group=None, bucket_mb: int = 1024, master_weights: bool = False, update_fn=None):
         import torch.distributed as dist
 
         if lr < 0 or eps < 0 or not 0 <= betas[0] < 1 or not 0 <= betas[1] < 1 or weight_decay < 0:

@@ -566,7 +566,7 @@ class _LigerPatches:
 def train_run(*, dev, rank, world, local, patches="bastile", parallel="single", optimizer="bastile", seq=SEQ_LEN,
               layers=36, intermediate=12288, steps=5, warmup=3, fused_layers=True, gemm_projections="off",
               overlap_opt=True, tiles="auto", grad_checkpoint=False, measure_e2e=True, sample_clocks=False,
-              master_weights=False, sweep=(), bucket_mb=256):
+              master_weights=False, sweep=(), bucket_mb=1024):
     """Build the model under the given patches / parallel wrapper / optimizer, run `warmup` untimed
     and `steps` timed steps (and, optionally, the same loop fed from pinned host memory), then the
     `sweep` entries (dicts with seq, steps, warmup, grad_checkpoint) on the same model.  Everything
@@ -847,7 +847,7 @@ def main():
     ap.add_argument("--tile-stores", default="on", choices=["on", "off"],
                     help="16-bit GEMM results through shared memory + tile stores (on, the library's default) or "
                          "stored by each epilogue thread from registers (off: bt_set_gemm_tile_stores(0))")
-    ap.add_argument("--bucket-mb", type=int, default=256, help="--parallel sharded: size of a gradient bucket")
+    ap.add_argument("--bucket-mb", type=int, default=1024, help="--parallel sharded: size of a gradient bucket")
     ap.add_argument("--group-rows", type=int, default=0,
                     help="tile rasterisation of the GEMMs: row tiles walked per column tile (0 = library default)")
     ap.add_argument("--no-per-op", action="store_true")

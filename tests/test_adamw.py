@@ -220,7 +220,8 @@ def test_sharded_adamw_gradient_sinks_are_written_directly():
 
     nets = [Net().cuda().to(torch.bfloat16), Net().cuda().to(torch.bfloat16)]
     hp = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
-    opts = [AdamW(nets[0].parameters(), **hp), ShardedAdamW(nets[1].parameters(), bucket_mb=1, **hp)]
+    # one bucket: gate | up lie back to back in it, so the stacked dWg | dWu product can go there too
+    opts = [AdamW(nets[0].parameters(), **hp), ShardedAdamW(nets[1].parameters(), bucket_mb=64, **hp)]
     seen = []
     orig = opts[1]._on_grad
 
@@ -241,7 +242,7 @@ def test_sharded_adamw_gradient_sinks_are_written_directly():
             net(x, y).backward()
             opt.step()
     _lib.check_all_status()
-    assert sum(seen) >= 3 * 3, f"gradients written in place: {sum(seen)} of {len(seen)}"  # gate, up or down, head
+    assert sum(seen) == len(seen) == 3 * 4, f"gradients written in place: {sum(seen)} of {len(seen)}"  # gate, up, down, head
     for (name, a), b in zip(nets[0].named_parameters(), nets[1].parameters()):
         assert_close(a, b, what=name, rtol=1e-2, atol=1e-3)
     opts[1].close()

@@ -305,9 +305,10 @@ def _lce_inputs(dev, rows=16384, hdim=4096, vocab=151936, full_weight=False, ran
     return hid, lab, w
 
 
-def per_op_bench(peaks, only=None, iters=None):
+def per_op_bench(peaks, only=None, iters=None, rows=None, lce_chunk=None):
     """Forward+backward of each op at the per-op benchmark shapes (bf16, seed 1), called through
-    the public ops; the time is that of the kernels (events around the library calls)."""
+    the public ops; the time is that of the kernels (events around the library calls).  `rows`
+    shrinks the token count of the MLP block / fused loss (small cases for profiler captures)."""
     import torch
 
     from bastile_b200.ops.fused_linear_cross_entropy import fused_linear_cross_entropy
@@ -410,17 +411,19 @@ def per_op_bench(peaks, only=None, iters=None):
         del g, u, dh
 
     if want("mlp"):
-        xm = torch.randn(8192, 4096, device=dev, dtype=bf).requires_grad_(True)
+        t_mlp = rows or 8192
+        xm = torch.randn(t_mlp, 4096, device=dev, dtype=bf).requires_grad_(True)
         wg = (torch.randn(12288, 4096, device=dev) * 0.02).to(bf).requires_grad_(True)
         wu = (torch.randn(12288, 4096, device=dev) * 0.02).to(bf).requires_grad_(True)
         wd = (torch.randn(4096, 12288, device=dev) * 0.02).to(bf).requires_grad_(True)
-        dym = torch.randn(8192, 4096, device=dev, dtype=bf)
+        dym = torch.randn(t_mlp, 4096, device=dev, dtype=bf)
 
         def mlp():
             xm.grad = wg.grad = wu.grad = wd.grad = None
             SwiGLUMLPFunction.apply(xm, wg, wu, wd).backward(dym)
 
-        out["swiglu_mlp_8192x4096x12288_fwd_bwd"] = _tensor(_kernel_ms(mlp, flush, iters or 10, 3), 7.4217e12, peaks)
+        out[f"swiglu_mlp_{t_mlp}x4096x12288_fwd_bwd"] = _tensor(_kernel_ms(mlp, flush, iters or 10, 3),
+                                                                7.4217e12 * t_mlp / 8192, peaks)
         del xm, wg, wu, wd, dym
 
     if want("lce"):
@@ -429,7 +432,8 @@ def per_op_bench(peaks, only=None, iters=None):
         world = dist.get_world_size() if dist.is_initialized() else 1
         rank = dist.get_rank() if dist.is_initialized() else 0
         vloc = 151936 // world  # 75968 / 37984 / 18992 rows of lm_head per rank at 2 / 4 / 8 GPUs
-        hid, lab, wl = _lce_inputs(dev, rank=rank, world=world)
+        t_lce = rows or 16384
+        hid, lab, wl = _lce_inputs(dev, rows=t_lce, rank=rank, world=world)
         hid.requires_grad_(True)
         wl.requires_grad_(True)
         group = dist.group.WORLD if world > 1 else None
@@ -437,7 +441,7 @@ def per_op_bench(peaks, only=None, iters=None):
         def lce():
             hid.grad = wl.grad = None
             fused_linear_cross_entropy(hid, wl, lab, vocab_parallel_group=group, vocab_start=rank * vloc,
-                                       vocab_size=151936).backward()
+                                       vocab_size=151936, **({"chunk_size": lce_chunk} if lce_chunk else {})).backward()
 
         def timed_whole(fn, n):  # collectives sit between the kernels: time the whole call, max over ranks
             ts = []
@@ -462,7 +466,7 @@ def per_op_bench(peaks, only=None, iters=None):
             for _ in range(2):
                 lce()
             ms = timed_whole(lce, iters or 5)
-        res = _tensor(ms, 61.1775e12, peaks)
+        res = _tensor(ms, 61.1775e12 * t_lce / 16384, peaks)
         if world > 1:
             # the two exchanges of the call, timed by themselves on buffers of the call's sizes
             chunk = 8192
@@ -486,7 +490,7 @@ def per_op_bench(peaks, only=None, iters=None):
                    "sharding": f"vocabulary: {vloc} lm_head rows per rank; one all-gather of [rows,3] fp32 statistics per "
                                "chunk, one fp32 all-reduce of d(hidden)", "algorithmic_TFLOP": 61.1775}
             del mine, gathered, dxf
-        out["fused_linear_ce_16384x4096x151936_fwd_bwd"] = res
+        out[f"fused_linear_ce_{t_lce}x4096x151936_fwd_bwd"] = res
         del hid, lab, wl
     return out
 
@@ -602,7 +606,9 @@ def train_run(*, dev, rank, world, local, patches="bastile", parallel="single", 
     cfg._attn_implementation = "sdpa"
     torch.manual_seed(1234)  # same initial weights on every rank
     prev = torch.get_default_dtype()
-    torch.set_default_dtype(torch.bfloat16)
+    # under FSDP "fp32 master" means fp32 shards that FSDP casts to bf16 for every layer's compute
+    fsdp_fp32 = master_weights and world > 1 and parallel in ("fsdp", "fsdp-vp")
+    torch.set_default_dtype(torch.float32 if fsdp_fp32 else torch.bfloat16)
     with torch.device(dev):
         model = q3.Qwen3ForCausalLM(cfg)
     torch.set_default_dtype(prev)
@@ -641,8 +647,8 @@ def train_run(*, dev, rank, world, local, patches="bastile", parallel="single", 
                    auto_wrap_policy=functools.partial(transformer_auto_wrap_policy,
                                                       transformer_layer_cls={q3.Qwen3DecoderLayer}),
                    use_orig_params=True, device_id=dev, ignored_modules=ignored)
-        parallelism = (f"fsdp{world} FULL_SHARD bf16, per-layer wrap" +
-                       (", lm_head vocabulary-parallel" if vp_on else ""))
+        parallelism = (f"fsdp{world} FULL_SHARD, bf16 compute" + (" over fp32 parameter shards" if fsdp_fp32 else "") +
+                       ", per-layer wrap" + (", lm_head vocabulary-parallel" if vp_on else ""))
     elif world > 1 and parallel == "ddp":
         from torch.nn.parallel import DistributedDataParallel as DDP
 
@@ -668,9 +674,11 @@ def train_run(*, dev, rank, world, local, patches="bastile", parallel="single", 
         # one process: every large parameter is updated as soon as its gradient is complete, on a side
         # stream underneath the rest of the backward pass (under DDP / FSDP gradients are only final after
         # the reduction, so the update stays in step())
-        opt = AdamW(net.parameters(), lr=1e-4, overlap_backward=overlap, master_weights=master_weights)
+        opt = AdamW(net.parameters(), lr=1e-4, overlap_backward=overlap,
+                    master_weights=master_weights and not fsdp_fp32)
         opt_name = ("bastile_b200.optim.AdamW" + (", updates overlapped with the backward pass" if overlap else "") +
-                    (", fp32 master weights" if master_weights else ", bf16 params and state"))
+                    (", fp32 parameter shards and state (bf16 copies made by FSDP)" if fsdp_fp32 else
+                     ", fp32 master weights" if master_weights else ", bf16 params and state"))
     else:
         if parallel == "sharded" and world > 1:
             raise SystemExit("--parallel sharded needs --optimizer bastile")
@@ -854,6 +862,9 @@ def main():
     ap.add_argument("--only-op", default=None, choices=["rmsnorm", "rope", "swiglu", "mlp", "lce"],
                     help="run just this op's forward+backward micro-benchmark (small case for profilers)")
     ap.add_argument("--op-iters", type=int, default=None)
+    ap.add_argument("--lce-chunk", type=int, default=None, help="with --only-op lce: rows per chunk (chunk_size=)")
+    ap.add_argument("--op-rows", type=int, default=None,
+                    help="with --only-op mlp / lce: token rows instead of 8192 / 16384 (small case for a profiler)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
                     help="only the main timed loop: no sequence sweep, comparators, DDP / FSDP companion runs")
@@ -883,7 +894,7 @@ def main():
     _lib.get_lib().bt_set_gemm_tile_stores(1 if args.tile_stores == "on" else 0)
     _lib.get_lib().bt_set_gemm_group_rows(args.group_rows)
     if args.only_op:
-        res = per_op_bench(peaks, only=args.only_op, iters=args.op_iters)
+        res = per_op_bench(peaks, only=args.only_op, iters=args.op_iters, rows=args.op_rows, lce_chunk=args.lce_chunk)
         _lib.check_status(dev, "per-op benchmark")
         if rank == 0:
             print(json.dumps({"per_op": res, "peaks": peaks, "peak_kind": peak_kind, "n_gpus": world}), flush=True)
@@ -1043,10 +1054,17 @@ def main():
                 **common, patches="bastile", parallel="fsdp-vp", optimizer=args.optimizer, seq=seq,
                 intermediate=args.intermediate, steps=3, warmup=3, measure_e2e=False,
                 sweep=[{"seq": 32768, "steps": 2, "warmup": 2, "grad_checkpoint": True}]))
+            fm = guarded("fsdp-vp, fp32 master", lambda: train_run(
+                **common, patches="bastile", parallel="fsdp-vp", optimizer=args.optimizer, seq=32768,
+                intermediate=args.intermediate, steps=2, warmup=2, measure_e2e=False, grad_checkpoint=True,
+                master_weights=True))
             if "main" in f:
                 line["sharded"] = {"parallelism": f["parallelism"], "optimizer": f["optimizer_name"],
                                    "seq_8192_per_rank": _slim(f["main"]),
                                    "seq_32768_per_rank": [_slim(r) for r in f["sweep"]],
+                                   "seq_32768_per_rank_fp32_master": (
+                                       {**_slim(fm["main"]), "parallelism": fm["parallelism"],
+                                        "optimizer": fm["optimizer_name"]} if "main" in fm else fm),
                                    "note": "FSDP FULL_SHARD per decoder layer (the reference's qwen_8b_fsdp.py recipe) with "
                                            "the lm_head rows sharded over the ranks and the fused loss vocabulary-parallel; "
                                            "32768 tokens per rank runs with activation checkpointing; tokens/s is the "

@@ -41,9 +41,10 @@ _GEMM_DTYPES = (torch.bfloat16, torch.float16, torch.float32)
 # the 16-bit logits chunk stays under AUTO_CHUNK_BYTES: 8192 rows x 4096 hidden is a whole
 # number of waves of tiles for the dx GEMM, and fewer chunks mean fewer read-modify-write
 # passes over the fp32 dW accumulator.  Larger is not better: with 16384 rows per chunk (no
-# accumulator at all at 16384 x 151936) the call measured 55-56 ms instead of 51 ms on a B200 -
-# the operand panel that a group of row tiles shares (16 x 256 vocabulary rows x 16384 rows of
-# dlogits = 134 MB) no longer fits the 126 MB L2.  An explicit chunk_size is obeyed.
+# accumulator at all at 16384 x 151936) the call measured 50.8-51.5 ms against 49.8-50.0 ms on
+# one B200 (4096 rows: 50.1-50.9 ms) - the operand panel that a group of row tiles shares in the
+# dW product grows with the chunk and stops fitting the 126 MB L2.  An explicit chunk_size is
+# obeyed.
 DEFAULT_CHUNK = 4096
 AUTO_CHUNK_ROWS = 8192
 AUTO_CHUNK_BYTES = 3 << 30

@@ -79,6 +79,7 @@ SIGNATURES = {
     "bt_lce_logits_stats": (c_int, [c_void_p] * 6 + [c_int64] * 7 + [c_int, c_void_p, c_void_p]),
     "bt_lce_num_vtiles": (c_int64, [c_int64]),
     "bt_lce_row_stats": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "bt_lce_stats_combine": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "bt_lce_dlogits": (c_int, [c_void_p] * 5 + [c_int64] * 5 + [c_int, c_int, c_void_p]),
     "bt_lce_count_valid": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p,
                                    c_void_p]),

@@ -41,6 +41,27 @@ lce_row_stats_kernel(const float2* __restrict__ tile_stats, const float* __restr
   }
 }
 
+// Merge of the per-shard statistics of a vocabulary-parallel loss: shard_stats is
+// [n_shards][rows][3] = (max, sum exp, target logit or 0) as gathered from the ranks; the
+// result [rows][3] describes the full vocabulary (one thread per row).
+__global__ void __launch_bounds__(kThreads)
+lce_stats_combine_kernel(const float* __restrict__ shard_stats, float* __restrict__ row_stats,
+                         int64_t rows, int64_t shard_stride, int n_shards) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (row >= rows) return;
+  float mx = -1e30f;
+  for (int s = 0; s < n_shards; ++s) mx = fmaxf(mx, shard_stats[s * shard_stride + row * 3]);
+  float sum = 0.f, tgt = 0.f;
+  for (int s = 0; s < n_shards; ++s) {
+    const float* st = shard_stats + s * shard_stride + row * 3;
+    sum += st[1] * __expf(st[0] - mx);
+    tgt += st[2];
+  }
+  row_stats[row * 3 + 0] = mx;
+  row_stats[row * 3 + 1] = sum;
+  row_stats[row * 3 + 2] = tgt;
+}
+
 // logits[row, :] -> (softmax - onehot) * scale in place; one CTA walks whole rows so the
 // row's statistics and label are read once.  Also writes the per-row loss.
 template <typename T>
@@ -245,6 +266,19 @@ extern "C" int bt_lce_dlogits(void* logits, const float* row_stats, const int64_
                                                         ld_logits, v_offset, ignore_index,
                                                         write_loss);
   BT_CHECK_LAUNCH("lce_dlogits");
+  return BT_OK;
+}
+
+extern "C" int bt_lce_stats_combine(const float* shard_stats, float* row_stats, int64_t rows,
+                                    int64_t shard_stride, int n_shards, void* stream) {
+  using namespace bt;
+  BT_CHECK_ARG(rows >= 0 && n_shards >= 1 && shard_stride >= rows * 3, "lce_stats_combine: bad extents");
+  if (rows == 0) return BT_OK;
+  BT_CHECK_ARG(shard_stats && row_stats, "lce_stats_combine: null pointer");
+  lce_stats_combine_kernel<<<static_cast<unsigned>(ceil_div(rows, kThreads)), kThreads, 0,
+                             static_cast<cudaStream_t>(stream)>>>(shard_stats, row_stats, rows,
+                                                                  shard_stride, n_shards);
+  BT_CHECK_LAUNCH("lce_stats_combine");
   return BT_OK;
 }
 

@@ -54,7 +54,9 @@ _SEGMENT_MIN_ROWS = 1024
 
 
 def merge_shard_stats(gathered: Tensor) -> Tensor:
-    """[n_shards, rows, 3] (max, sum-exp, target logit) -> [rows, 3] for the full vocabulary."""
+    """[n_shards, rows, 3] (max, sum-exp, target logit) -> [rows, 3] for the full vocabulary.
+    The op itself runs this merge as one kernel (``bt_lce_stats_combine``); this torch form is the
+    same arithmetic for CPU ranks and tests."""
     mx = gathered[..., 0]
     gmax = mx.max(dim=0).values
     gsum = (gathered[..., 1] * torch.exp(mx - gmax)).sum(dim=0)
@@ -146,7 +148,16 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         if group is not None:
             world = dist.get_world_size(group)
             gathered = torch.empty((world, chunk, 3), **f32)
+            merged = torch.empty((chunk, 3), **f32)
 
+        # d(hidden) is a sum over the vocabulary shards.  Each chunk's rows are reduced as soon as its dx
+        # GEMM is queued - NCCL runs that on its own stream underneath the next chunk's GEMMs - so only
+        # the last chunk's reduction is exposed: an all-reduce per chunk when every rank needs all rows,
+        # a reduce to the owning rank when the ranks brought their own rows and the chunk lies inside one
+        # rank's block (otherwise one reduce-scatter at the end).
+        reductions = []
+        per_chunk_reduce = group is not None and bt > 0 and (
+            not shard_tokens or all(s0 // bt_local == (s0 + xc0.shape[0] - 1) // bt_local for xc0, s0 in chunks))
         n_k = 2 + 5 * n_chunks - (1 if n_chunks else 0)
         with _lib.device_of(dev), _lib.timed("lce_fwd", n_k, dev):
             v_total = vloc if group is None else int(vocab_size or 0)  # 0: bound unknown, labels unchecked
@@ -171,7 +182,9 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
                 stats = row_stats
                 if group is not None:
                     dist.all_gather_into_tensor(gathered.view(-1), row_stats.view(-1), group=group)
-                    stats = merge_shard_stats(gathered[:, :rows])
+                    stats = merged
+                    _lib.check(lib.bt_lce_stats_combine(gathered.data_ptr(), merged.data_ptr(), rows, chunk * 3, world,
+                                                        stream), "bt_lce_stats_combine")
                 _lib.check(lib.bt_lce_dlogits(logits_buf.data_ptr(), stats.data_ptr(), lc.data_ptr(),
                                               loss_row[s:].data_ptr(), scal[1:].data_ptr(), rows, vloc, ld_logits,
                                               int(vocab_start), ignore_index, 1, code, stream), "bt_lce_dlogits")
@@ -179,6 +192,12 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
                 _lib.check(lib.bt_gemm(logits_buf.data_ptr(), w.data_ptr(), dx[s:].data_ptr(), rows, hdim, vloc,
                                        ld_logits, hdim, hdim, 1, 0, code, _lib.dtype_code(dx_dtype), None, 0, None,
                                        st.data_ptr(), stream), "bt_gemm(dx)")
+                if per_chunk_reduce:
+                    if shard_tokens:
+                        owner = dist.get_global_rank(group, s // bt_local)
+                        reductions.append(dist.reduce(dx[s:s + rows], dst=owner, group=group, async_op=True))
+                    else:
+                        reductions.append(dist.all_reduce(dx[s:s + rows], group=group, async_op=True))
                 if i < n_chunks - 1:
                     # dW += dlogits^T[V, rows] @ x_chunk[rows, H], fp32 accumulation across chunks
                     _lib.check(lib.bt_gemm(logits_buf.data_ptr(), xc.data_ptr(), dw_acc.data_ptr(), vloc, hdim, rows,
@@ -190,12 +209,18 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             _lib.check(lib.bt_lce_reduce_loss(loss_row.data_ptr(), bt, scal[1:].data_ptr() if reduction == "mean"
                                               else None, scal[2:].data_ptr(), stream), "bt_lce_reduce_loss")
         if group is not None and bt > 0:
+            for work in reductions:
+                work.wait()  # the current stream waits; the host does not
             if shard_tokens:  # each rank only needs the gradient of its own rows
-                dx_local = torch.empty((bt_local, hdim), dtype=dx.dtype, device=dev)
-                dist.reduce_scatter_tensor(dx_local, dx, group=group)
-                dx = dx_local
+                if per_chunk_reduce:
+                    me = dist.get_rank(group)
+                    dx = dx[me * bt_local:(me + 1) * bt_local]
+                else:
+                    dx_local = torch.empty((bt_local, hdim), dtype=dx.dtype, device=dev)
+                    dist.reduce_scatter_tensor(dx_local, dx, group=group)
+                    dx = dx_local
                 batch_shape = x.shape[:-1]
-            else:
+            elif not per_chunk_reduce:
                 dist.all_reduce(dx, group=group)
 
         ctx.save_for_backward(dx, w, logits_buf, x_last if x_last is not None else segments[0][:0],

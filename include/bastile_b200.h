@@ -359,6 +359,15 @@ int64_t bt_lce_num_vtiles(int64_t V);
 int bt_lce_row_stats(const float* tile_stats, const float* tgt_logit,
                      float* row_stats, int64_t rows, int64_t n_vtiles, void* stream);
 
+/* Vocabulary-parallel form, between steps 2 and 3: shard_stats holds the row_stats of all
+ * n_shards ranks as gathered by ONE collective (shard s at shard_stats + s * shard_stride floats,
+ * [rows,3] each); row_stats[rows,3] receives their log-sum-exp merge - global max, sum exp
+ * rescaled to it, and the target logit (non-zero on exactly one shard).  The reference has no
+ * sharded loss; this is the exchange step of a vocabulary split of
+ * src/bastile/ops/fused_linear_cross_entropy.py:46-100. */
+int bt_lce_stats_combine(const float* shard_stats, float* row_stats, int64_t rows,
+                         int64_t shard_stride, int n_shards, void* stream);
+
 /* Step 3: given (possibly cross-shard merged) row statistics, write
  * loss_row = max + log(sum) - target (0 for ignored rows) and turn the logits
  * chunk in place into scaled gradients

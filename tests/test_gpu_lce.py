@@ -338,3 +338,28 @@ def test_lce_batched_slice_runs_without_flattening_copy():
         assert x.grad.shape == x.shape
         assert_close(x.grad.reshape(-1, h), dx_ref, what=f"dx b={b}", rtol=2e-2, atol=2e-2 * float(np.abs(dx_ref).max()))
         assert_close(w.grad, dw_ref, what=f"dw b={b}", rtol=2e-2, atol=2e-2 * float(np.abs(dw_ref).max()))
+
+
+def test_lce_stats_combine_matches_oracle_merge():
+    """bt_lce_stats_combine (the cross-shard log-sum-exp merge as one kernel) against the oracle's
+    merge and the torch form used on CPU ranks; shard blocks with a stride larger than rows * 3."""
+    from bastile_b200 import _lib
+    from bastile_b200.ops.fused_linear_cross_entropy import merge_shard_stats
+
+    lib = _lib.get_lib()
+    rng = np.random.default_rng(5)
+    n_shards, rows, cap = 8, 1000, 1024
+    st = rng.standard_normal((n_shards, cap, 3)).astype(np.float32) * 5
+    st[..., 1] = np.abs(st[..., 1]) + 0.1
+    st[..., 2] = 0.0
+    st[rng.integers(0, n_shards, rows), np.arange(rows), 2] = rng.standard_normal(rows).astype(np.float32)
+    g = torch.tensor(st, device=DEV)
+    out = torch.empty(rows, 3, device=DEV)
+    _lib.check(lib.bt_lce_stats_combine(g.data_ptr(), out.data_ptr(), rows, cap * 3, n_shards,
+                                        _lib.stream_ptr(g.device)), "bt_lce_stats_combine")
+    want = oracle.merge_shard_stats(st[:, :rows])
+    got = out.cpu().numpy()
+    np.testing.assert_allclose(got[:, 0] + np.log(got[:, 1]), want[:, 0] + np.log(want[:, 1]), rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(got[:, 2], want[:, 2], rtol=1e-6, atol=1e-6)
+    torch_form = merge_shard_stats(g[:, :rows]).cpu().numpy()
+    np.testing.assert_allclose(got, torch_form, rtol=1e-5, atol=1e-5)

@@ -62,6 +62,19 @@ def _worker(rank, world, port, q):
         ok_dx &= np.allclose(xs2.grad.float().cpu().numpy(), 2.0 * dx_ref[rank * half:(rank + 1) * half], rtol=2e-2,
                              atol=4e-2 * sx)
         ok_dw &= np.allclose(wl2.grad.float().cpu().numpy(), dw_ref[rank * vs:(rank + 1) * vs], rtol=2e-2, atol=2e-2 * sw)
+        # chunks that lie inside one rank's block of rows: every chunk's d(hidden) is reduced to its owner
+        # while the next chunk computes (175 divides the 350 rows a rank brings)
+        xs3 = x[rank * half:(rank + 1) * half].clone().requires_grad_(True)
+        wl3 = w[rank * vs:(rank + 1) * vs].clone().requires_grad_(True)
+        loss3 = fused_linear_cross_entropy(xs3, wl3, t[rank * half:(rank + 1) * half], chunk_size=175,
+                                           vocab_parallel_group=dist.group.WORLD, vocab_start=rank * vs,
+                                           shard_tokens=True, grad_hidden_scale=1.0, vocab_size=v)
+        loss3.backward()
+        _lib.check_all_status()
+        ok_loss &= abs(loss3.item() - float(l_ref)) <= 2e-3 * abs(float(l_ref))
+        ok_dx &= np.allclose(xs3.grad.float().cpu().numpy(), dx_ref[rank * half:(rank + 1) * half], rtol=2e-2,
+                             atol=2e-2 * sx)
+        ok_dw &= np.allclose(wl3.grad.float().cpu().numpy(), dw_ref[rank * vs:(rank + 1) * vs], rtol=2e-2, atol=2e-2 * sw)
         q.put((rank, ok_loss, ok_dx, ok_dw, loss.item(), float(l_ref)))
     finally:
         dist.destroy_process_group()

@@ -210,7 +210,9 @@ class ShardedAdamW:
     * parameters are re-laid as views into flat buckets (``bucket_mb`` each, filled in reverse
       registration order, the order in which gradients become final; 1 GiB measured best on a
       Qwen3-8B step on two B200: 416 ms against 420 ms with 256 MiB and 429 ms with 64 MiB);
-    * a post-accumulate-grad hook copies each gradient into its bucket on a side stream; when a
+    * a post-accumulate-grad hook copies each gradient into its bucket on a side stream - unless
+      the op that produced it (the MLP block, the fused loss) found the bucket view registered as
+      the weight's gradient destination and wrote it there in the first place; when a
       bucket is complete the side stream reduce-scatters it (NCCL, average), runs the AdamW
       kernel on this rank's 1/N slice of the bucket (moments - and the fp32 master copy with
       ``master_weights=True`` - exist only for that slice) and all-gathers the bucket's

@@ -139,6 +139,63 @@ struct Cvt<float> {
   __device__ __forceinline__ static float from_f(float x) { return x; }
 };
 
+// ---------------------------------------------------------------- packed fp32 pairs
+// sm_100 issues fp32 add / mul / fma on PAIRS of values held in a 64-bit register
+// (fma.rn.f32x2 and friends): same IEEE results per lane, half the issue slots.  The row
+// kernels are bound by instruction issue (a few resident warps per scheduler), not by
+// arithmetic throughput, so their inner loops work on pairs.
+struct f32x2 {
+  unsigned long long r;
+};
+__device__ __forceinline__ f32x2 pair(float lo, float hi) {
+  f32x2 p;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(p.r) : "f"(lo), "f"(hi));
+  return p;
+}
+__device__ __forceinline__ float lo_of(f32x2 p) {
+  float lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p.r));
+  return lo;
+}
+__device__ __forceinline__ float hi_of(f32x2 p) {
+  float lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p.r));
+  return hi;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d.r) : "l"(a.r), "l"(b.r));
+  return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d.r) : "l"(a.r), "l"(b.r));
+  return d;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d.r) : "l"(a.r), "l"(b.r), "l"(c.r));
+  return d;
+}
+// A 16-byte vector as fp32 pairs (N / 2 of them) and back.
+template <typename T>
+__device__ __forceinline__ void unpack_pairs(uint4 v, f32x2 (&p)[Cvt<T>::N / 2]) {
+  float f[Cvt<T>::N];
+  Cvt<T>::unpack(v, f);
+#pragma unroll
+  for (int i = 0; i < Cvt<T>::N / 2; ++i) p[i] = pair(f[2 * i], f[2 * i + 1]);
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack_pairs(const f32x2 (&p)[Cvt<T>::N / 2]) {
+  float f[Cvt<T>::N];
+#pragma unroll
+  for (int i = 0; i < Cvt<T>::N / 2; ++i) {
+    f[2 * i] = lo_of(p[i]);
+    f[2 * i + 1] = hi_of(p[i]);
+  }
+  return Cvt<T>::pack(f);
+}
+
 // Tells the compiler that a packed 16-byte vector "changed": values unpacked from it before
 // this point cannot be kept alive in registers across it and are recomputed from the packed
 // form instead.  Costs nothing at run time; keeps two-pass row kernels at ~1 register per

@@ -109,12 +109,13 @@ rms_fwd_staged(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__
     }
   }
 
-  float wf[VPT][E];
+  constexpr int P = E / 2;  // fp32 pairs per 16-byte vector
+  f32x2 wf[VPT][P];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = threadIdx.x + i * kThreads;
-    Cvt<T>::unpack(v < nv ? ld_global_v4(w + static_cast<int64_t>(v) * E) : make_uint4(0, 0, 0, 0),
-                   wf[i]);
+    unpack_pairs<T>(v < nv ? ld_global_v4(w + static_cast<int64_t>(v) * E) : make_uint4(0, 0, 0, 0),
+                    wf[i]);
   }
 
   int s = 0;
@@ -130,31 +131,32 @@ rms_fwd_staged(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__
     float ss[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      ss[r] = 0.f;
+      f32x2 ss2 = pair(0.f, 0.f);  // even / odd elements of this thread's slices
       if (ok && r0 + r < M) {
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
           const int v = threadIdx.x + i * kThreads;
           if (v < nv) {
-            float f[E];
+            f32x2 f[P];
             if constexpr (ADD) {
-              float b[E];
-              Cvt<T>::unpack(lds_v4(st + r * row_bytes + v * 16), f);
-              Cvt<T>::unpack(lds_v4(st + (R + r) * row_bytes + v * 16), b);
+              f32x2 b[P];
+              unpack_pairs<T>(lds_v4(st + r * row_bytes + v * 16), f);
+              unpack_pairs<T>(lds_v4(st + (R + r) * row_bytes + v * 16), b);
 #pragma unroll
-              for (int e = 0; e < E; ++e) f[e] += b[e];
-              const uint4 packed = Cvt<T>::pack(f);
+              for (int e = 0; e < P; ++e) f[e] = add2(f[e], b[e]);
+              const uint4 packed = pack_pairs<T>(f);
               *reinterpret_cast<uint4*>(st + r * row_bytes + v * 16) = packed;
               st_global_v4(sum + (r0 + r) * ld_sum + static_cast<int64_t>(v) * E, packed);
-              Cvt<T>::unpack(packed, f);
+              unpack_pairs<T>(packed, f);
             } else {
-              Cvt<T>::unpack(lds_v4(st + r * row_bytes + v * 16), f);
+              unpack_pairs<T>(lds_v4(st + r * row_bytes + v * 16), f);
             }
 #pragma unroll
-            for (int e = 0; e < E; ++e) ss[r] = fmaf(f[e], f[e], ss[r]);
+            for (int e = 0; e < P; ++e) ss2 = fma2(f[e], f[e], ss2);
           }
         }
       }
+      ss[r] = lo_of(ss2) + hi_of(ss2);
     }
     block_sums<R>(ss, red + buf * R * kWarps, warp, lane);
     if (*reinterpret_cast<volatile int*>(&ring->abort_flag) != 0) break;  // same value in every thread
@@ -164,15 +166,16 @@ rms_fwd_staged(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__
       if (row < M) {
         const float rs = rsqrtf(ss[r] * inv_n + eps);
         if (threadIdx.x == 0) rstd[row] = rs;
+        const f32x2 rs2 = pair(rs, rs);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
           const int v = threadIdx.x + i * kThreads;
           if (v < nv) {
-            float f[E];
-            Cvt<T>::unpack(lds_v4(st + r * row_bytes + v * 16), f);
+            f32x2 f[P];
+            unpack_pairs<T>(lds_v4(st + r * row_bytes + v * 16), f);
 #pragma unroll
-            for (int e = 0; e < E; ++e) f[e] = f[e] * rs * wf[i][e];
-            st_global_v4(y + row * ld_y + static_cast<int64_t>(v) * E, Cvt<T>::pack(f));
+            for (int e = 0; e < P; ++e) f[e] = mul2(mul2(f[e], rs2), wf[i][e]);
+            st_global_v4(y + row * ld_y + static_cast<int64_t>(v) * E, pack_pairs<T>(f));
           }
         }
       }
@@ -237,14 +240,15 @@ rms_bwd_staged(const T* __restrict__ dy, const T* __restrict__ x, const T* __res
     }
   }
 
-  float wf[VPT][E], acc[VPT][E];
+  constexpr int P = E / 2;  // fp32 pairs per 16-byte vector
+  f32x2 wf[VPT][P], acc[VPT][P];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = threadIdx.x + i * kThreads;
-    Cvt<T>::unpack(v < nv ? ld_global_v4(w + static_cast<int64_t>(v) * E) : make_uint4(0, 0, 0, 0),
-                   wf[i]);
+    unpack_pairs<T>(v < nv ? ld_global_v4(w + static_cast<int64_t>(v) * E) : make_uint4(0, 0, 0, 0),
+                    wf[i]);
 #pragma unroll
-    for (int e = 0; e < E; ++e) acc[i][e] = 0.f;
+    for (int e = 0; e < P; ++e) acc[i][e] = pair(0.f, 0.f);
   }
 
   int s = 0;
@@ -271,25 +275,27 @@ rms_bwd_staged(const T* __restrict__ dy, const T* __restrict__ x, const T* __res
     float dot[R], rs[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      dot[r] = 0.f;
+      f32x2 dot2 = pair(0.f, 0.f);
       rs[r] = (r0 + r < M) ? rstd[r0 + r] : 0.f;
+      const f32x2 rs2 = pair(rs[r], rs[r]);
       if (ok && r0 + r < M) {
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
           const int v = threadIdx.x + i * kThreads;
           if (v < nv) {
-            float xf[E], gf[E];
-            Cvt<T>::unpack(lds_v4(sx + r * row_bytes + v * 16), xf);
-            Cvt<T>::unpack(lds_v4(sg + r * row_bytes + v * 16), gf);
+            f32x2 xf[P], gf[P];
+            unpack_pairs<T>(lds_v4(sx + r * row_bytes + v * 16), xf);
+            unpack_pairs<T>(lds_v4(sg + r * row_bytes + v * 16), gf);
 #pragma unroll
-            for (int e = 0; e < E; ++e) {
-              const float xh = xf[e] * rs[r];
-              dot[r] = fmaf(xh, gf[e] * wf[i][e], dot[r]);
-              acc[i][e] = fmaf(gf[e], xh, acc[i][e]);
+            for (int e = 0; e < P; ++e) {
+              const f32x2 xh = mul2(xf[e], rs2);
+              dot2 = fma2(xh, mul2(gf[e], wf[i][e]), dot2);
+              acc[i][e] = fma2(gf[e], xh, acc[i][e]);
             }
           }
         }
       }
+      dot[r] = lo_of(dot2) + hi_of(dot2);
     }
     block_sums<R>(dot, red + buf * R * kWarps, warp, lane);
     if (*reinterpret_cast<volatile int*>(&ring->abort_flag) != 0) break;
@@ -298,22 +304,24 @@ rms_bwd_staged(const T* __restrict__ dy, const T* __restrict__ x, const T* __res
       const int64_t row = r0 + r;
       if (row < M) {
         const float c = dot[r] * inv_n;
+        const f32x2 rs2 = pair(rs[r], rs[r]);
+        const f32x2 neg_rs_c = pair(-rs[r] * c, -rs[r] * c);  // (g*w - x*rs*c)*rs = (g*w + x*(-rs*c))*rs
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
           const int v = threadIdx.x + i * kThreads;
           if (v < nv) {
-            float xf[E], gf[E], o[E];
-            Cvt<T>::unpack(lds_v4(sx + r * row_bytes + v * 16), xf);
-            Cvt<T>::unpack(lds_v4(sg + r * row_bytes + v * 16), gf);
+            f32x2 xf[P], gf[P], o[P];
+            unpack_pairs<T>(lds_v4(sx + r * row_bytes + v * 16), xf);
+            unpack_pairs<T>(lds_v4(sg + r * row_bytes + v * 16), gf);
 #pragma unroll
-            for (int e = 0; e < E; ++e) o[e] = (gf[e] * wf[i][e] - xf[e] * rs[r] * c) * rs[r];
+            for (int e = 0; e < P; ++e) o[e] = mul2(fma2(xf[e], neg_rs_c, mul2(gf[e], wf[i][e])), rs2);
             if constexpr (ADD) {
-              float a[E];
-              Cvt<T>::unpack(rv[r][i], a);
+              f32x2 a[P];
+              unpack_pairs<T>(rv[r][i], a);
 #pragma unroll
-              for (int e = 0; e < E; ++e) o[e] += a[e];
+              for (int e = 0; e < P; ++e) o[e] = add2(o[e], a[e]);
             }
-            st_global_v4(dx + row * ld_dx + static_cast<int64_t>(v) * E, Cvt<T>::pack(o));
+            st_global_v4(dx + row * ld_dx + static_cast<int64_t>(v) * E, pack_pairs<T>(o));
           }
         }
       }
@@ -338,8 +346,9 @@ rms_bwd_staged(const T* __restrict__ dy, const T* __restrict__ x, const T* __res
       const int v = threadIdx.x + i * kThreads;
       if (v < nv) {
 #pragma unroll
-        for (int e = 0; e < E; e += 4)
-          red_add_v4(my_ws + v * E + e, acc[i][e], acc[i][e + 1], acc[i][e + 2], acc[i][e + 3]);
+        for (int e = 0; e < P; e += 2)
+          red_add_v4(my_ws + v * E + 2 * e, lo_of(acc[i][e]), hi_of(acc[i][e]), lo_of(acc[i][e + 1]),
+                     hi_of(acc[i][e + 1]));
       }
     }
   }

@@ -162,6 +162,11 @@ __device__ __forceinline__ float hi_of(f32x2 p) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p.r));
   return hi;
 }
+__device__ __forceinline__ f32x2 neg2(f32x2 a) {  // flips both sign bits
+  f32x2 d;
+  d.r = a.r ^ 0x8000000080000000ull;
+  return d;
+}
 __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
   f32x2 d;
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d.r) : "l"(a.r), "l"(b.r));

@@ -103,9 +103,13 @@ headnorm_rope_fwd(const __grid_constant__ HeadPair pp) {
   const uint32_t items = static_cast<uint32_t>(a.B * a.T) * hblocks;
   const float inv_n = 1.0f / static_cast<float>(a.D);
 
-  float w1[E], w2[E];
-  Cvt<T>::unpack(ld_global_v4(static_cast<const T*>(a.w) + lane * E), w1);
-  Cvt<T>::unpack(ld_global_v4(static_cast<const T*>(a.w) + half + lane * E), w2);
+  // Elementwise arithmetic runs on packed fp32 pairs (same results per element, half the issue
+  // slots); the row sums keep their scalar chains, whose order is part of the bit-identity with
+  // the stand-alone kernels.
+  constexpr int P = E / 2;
+  f32x2 w1[P], w2[P];
+  unpack_pairs<T>(ld_global_v4(static_cast<const T*>(a.w) + lane * E), w1);
+  unpack_pairs<T>(ld_global_v4(static_cast<const T*>(a.w) + half + lane * E), w2);
 
   for (uint32_t base = bid * kGroups; base < items; base += nblk * kGroups) {
     const Item it = locate<HPI>(a, base + group, items, hblocks);
@@ -122,40 +126,45 @@ headnorm_rope_fwd(const __grid_constant__ HeadPair pp) {
       x1[u] = ok ? ld_stream_v4(xp) : make_uint4(0, 0, 0, 0);
       x2[u] = ok ? ld_stream_v4(xp + half) : make_uint4(0, 0, 0, 0);
     }
-    float c[E], s[E];
-    Cvt<T>::unpack(cv, c);
-    Cvt<T>::unpack(sv, s);
+    f32x2 c[P], s[P];
+    unpack_pairs<T>(cv, c);
+    unpack_pairs<T>(sv, s);
 #pragma unroll
     for (int u = 0; u < HPI; ++u) {
-      float f1[E], f2[E], o1[E], o2[E];
-      Cvt<T>::unpack(x1[u], f1);
-      Cvt<T>::unpack(x2[u], f2);
+      f32x2 y1[P], y2[P], o1[P], o2[P];
+      unpack_pairs<T>(x1[u], y1);
+      unpack_pairs<T>(x2[u], y2);
       float p1 = 0.f, p2 = 0.f;
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        p1 = fmaf(f1[e], f1[e], p1);
-        p2 = fmaf(f2[e], f2[e], p2);
+      for (int e = 0; e < P; ++e) {  // element order 0, 1, 2, ... within each slice
+        p1 = fmaf(lo_of(y1[e]), lo_of(y1[e]), p1);
+        p2 = fmaf(lo_of(y2[e]), lo_of(y2[e]), p2);
+        p1 = fmaf(hi_of(y1[e]), hi_of(y1[e]), p1);
+        p2 = fmaf(hi_of(y2[e]), hi_of(y2[e]), p2);
       }
       const float ss = group_sum<LPR>(p1 + p2);
       const float rs = rsqrtf(ss * inv_n + a.eps);
-      float y1[E], y2[E];
+      const f32x2 rs2 = pair(rs, rs);
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        y1[e] = f1[e] * rs * w1[e];
-        y2[e] = f2[e] * rs * w2[e];
+      for (int e = 0; e < P; ++e) {
+        y1[e] = mul2(mul2(y1[e], rs2), w1[e]);
+        y2[e] = mul2(mul2(y2[e], rs2), w2[e]);
       }
-      round_vec<T>(y1);  // the normalised row as the stand-alone norm kernel would have stored it
-      round_vec<T>(y2);
+      if constexpr (sizeof(T) < 4) {
+        // the normalised row as the stand-alone norm kernel would have stored it
+        unpack_pairs<T>(pack_pairs<T>(y1), y1);
+        unpack_pairs<T>(pack_pairs<T>(y2), y2);
+      }
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        o1[e] = fmaf(-y2[e], s[e], y1[e] * c[e]);  // y1*cos - y2*sin
-        o2[e] = fmaf(y1[e], s[e], y2[e] * c[e]);   // y2*cos + y1*sin
+      for (int e = 0; e < P; ++e) {
+        o1[e] = fma2(neg2(y2[e]), s[e], mul2(y1[e], c[e]));  // y1*cos - y2*sin
+        o2[e] = fma2(y1[e], s[e], mul2(y2[e], c[e]));   // y2*cos + y1*sin
       }
       if (it.valid && it.h0 + u < H) {
         if (lane == 0) a.rstd_out[it.row0 + u] = rs;
         T* op = static_cast<T*>(a.out) + it.o_off + u * a.os[2] + lane * E;
-        st_global_v4(op, Cvt<T>::pack(o1));
-        st_global_v4(op + half, Cvt<T>::pack(o2));
+        st_global_v4(op, pack_pairs<T>(o1));
+        st_global_v4(op + half, pack_pairs<T>(o2));
       }
     }
   }
@@ -184,11 +193,14 @@ headnorm_rope_bwd(const __grid_constant__ HeadPair pp) {
 
   for (int c = threadIdx.x; c < N; c += kThreads) s_dw[c] = 0.f;
 
-  float w1[E], w2[E], acc1[E], acc2[E];
-  Cvt<T>::unpack(ld_global_v4(static_cast<const T*>(a.w) + lane * E), w1);
-  Cvt<T>::unpack(ld_global_v4(static_cast<const T*>(a.w) + half + lane * E), w2);
+  // Elementwise arithmetic on packed fp32 pairs; the dot product keeps its scalar chains (their
+  // order is part of the bit-identity with the stand-alone kernels).
+  constexpr int P = E / 2;
+  f32x2 w1[P], w2[P], acc1[P], acc2[P];
+  unpack_pairs<T>(ld_global_v4(static_cast<const T*>(a.w) + lane * E), w1);
+  unpack_pairs<T>(ld_global_v4(static_cast<const T*>(a.w) + half + lane * E), w2);
 #pragma unroll
-  for (int e = 0; e < E; ++e) acc1[e] = acc2[e] = 0.f;
+  for (int e = 0; e < P; ++e) acc1[e] = acc2[e] = pair(0.f, 0.f);
 
   for (uint32_t base = bid * kGroups; base < items; base += nblk * kGroups) {
     const Item it = locate<HPI>(a, base + group, items, hblocks);
@@ -210,56 +222,77 @@ headnorm_rope_bwd(const __grid_constant__ HeadPair pp) {
       g1[u] = ok ? ld_stream_v4(gp) : make_uint4(0, 0, 0, 0);
       g2[u] = ok ? ld_stream_v4(gp + half) : make_uint4(0, 0, 0, 0);
     }
-    float c[E], s[E];
-    Cvt<T>::unpack(cv, c);
-    Cvt<T>::unpack(sv, s);
+    f32x2 c[P], s[P];
+    unpack_pairs<T>(cv, c);
+    unpack_pairs<T>(sv, s);
 #pragma unroll
     for (int u = 0; u < HPI; ++u) {
-      float xa[E], xb[E], ga[E], gb[E], d1[E], d2[E];
-      Cvt<T>::unpack(x1[u], xa);
-      Cvt<T>::unpack(x2[u], xb);
-      Cvt<T>::unpack(g1[u], ga);
-      Cvt<T>::unpack(g2[u], gb);
+      f32x2 h1[P], h2[P], d1[P], d2[P];
+      {
+        f32x2 ga[P], gb[P];
+        unpack_pairs<T>(g1[u], ga);
+        unpack_pairs<T>(g2[u], gb);
+#pragma unroll
+        for (int e = 0; e < P; ++e) {
+          // inverse rotation: d1*cos + d2*sin ; d2*cos - d1*sin
+          d1[e] = fma2(gb[e], s[e], mul2(ga[e], c[e]));
+          d2[e] = fma2(neg2(ga[e]), s[e], mul2(gb[e], c[e]));
+        }
+      }
+      if constexpr (sizeof(T) < 4) {
+        // the un-rotated gradient as the stand-alone RoPE backward would have stored it
+        unpack_pairs<T>(pack_pairs<T>(d1), d1);
+        unpack_pairs<T>(pack_pairs<T>(d2), d2);
+      }
+      const f32x2 rs2 = pair(rs[u], rs[u]);
+      unpack_pairs<T>(x1[u], h1);
+      unpack_pairs<T>(x2[u], h2);
       float p1 = 0.f, p2 = 0.f;
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        // inverse rotation: d1*cos + d2*sin ; d2*cos - d1*sin
-        d1[e] = fmaf(gb[e], s[e], ga[e] * c[e]);
-        d2[e] = fmaf(-ga[e], s[e], gb[e] * c[e]);
-      }
-      round_vec<T>(d1);  // the un-rotated gradient as the stand-alone RoPE backward would have stored it
-      round_vec<T>(d2);
-#pragma unroll
-      for (int e = 0; e < E; ++e) {
-        const float h1 = xa[e] * rs[u], h2 = xb[e] * rs[u];
-        p1 = fmaf(h1, d1[e] * w1[e], p1);
-        p2 = fmaf(h2, d2[e] * w2[e], p2);
-        acc1[e] = fmaf(d1[e], h1, acc1[e]);
-        acc2[e] = fmaf(d2[e], h2, acc2[e]);
+      for (int e = 0; e < P; ++e) {
+        h1[e] = mul2(h1[e], rs2);  // x * rstd
+        h2[e] = mul2(h2[e], rs2);
+        const f32x2 t1 = mul2(d1[e], w1[e]), t2 = mul2(d2[e], w2[e]);
+        p1 = fmaf(lo_of(h1[e]), lo_of(t1), p1);  // element order 0, 1, 2, ... within each slice
+        p2 = fmaf(lo_of(h2[e]), lo_of(t2), p2);
+        p1 = fmaf(hi_of(h1[e]), hi_of(t1), p1);
+        p2 = fmaf(hi_of(h2[e]), hi_of(t2), p2);
+        acc1[e] = fma2(d1[e], h1[e], acc1[e]);
+        acc2[e] = fma2(d2[e], h2[e], acc2[e]);
       }
       const float dot = group_sum<LPR>(p1 + p2) * inv_n;
       if (it.valid && it.h0 + u < H) {
-        float o1[E], o2[E];
+        const f32x2 ndot = pair(-dot, -dot);
+        f32x2 o1[P], o2[P];
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
-          o1[e] = fmaf(-(xa[e] * rs[u]), dot, d1[e] * w1[e]) * rs[u];
-          o2[e] = fmaf(-(xb[e] * rs[u]), dot, d2[e] * w2[e]) * rs[u];
+        for (int e = 0; e < P; ++e) {
+          // fmaf(-(x*rs), dot, d*w) * rs
+          o1[e] = mul2(fma2(h1[e], ndot, mul2(d1[e], w1[e])), rs2);
+          o2[e] = mul2(fma2(h2[e], ndot, mul2(d2[e], w2[e])), rs2);
         }
         T* op = static_cast<T*>(a.out) + it.o_off + u * a.os[2] + lane * E;
-        st_global_v4(op, Cvt<T>::pack(o1));
-        st_global_v4(op + half, Cvt<T>::pack(o2));
+        st_global_v4(op, pack_pairs<T>(o1));
+        st_global_v4(op + half, pack_pairs<T>(o2));
       }
     }
   }
 
   __syncthreads();  // s_dw zeroed
   // Row groups that share a warp hold the same columns: fold them together first.
+  float a1[E], a2[E];
+#pragma unroll
+  for (int e = 0; e < P; ++e) {
+    a1[2 * e] = lo_of(acc1[e]);
+    a1[2 * e + 1] = hi_of(acc1[e]);
+    a2[2 * e] = lo_of(acc2[e]);
+    a2[2 * e + 1] = hi_of(acc2[e]);
+  }
 #pragma unroll
   for (int o = LPR; o < 32; o <<= 1) {
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      acc1[e] += __shfl_xor_sync(0xffffffffu, acc1[e], o);
-      acc2[e] += __shfl_xor_sync(0xffffffffu, acc2[e], o);
+      a1[e] += __shfl_xor_sync(0xffffffffu, a1[e], o);
+      a2[e] += __shfl_xor_sync(0xffffffffu, a2[e], o);
     }
   }
   // element-major in shared memory (index (2e + which half) * LPR + lane): lanes of one
@@ -267,8 +300,8 @@ headnorm_rope_bwd(const __grid_constant__ HeadPair pp) {
   if ((threadIdx.x & 31) < LPR) {
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      atomicAdd(&s_dw[(2 * e) * LPR + lane], acc1[e]);
-      atomicAdd(&s_dw[(2 * e + 1) * LPR + lane], acc2[e]);
+      atomicAdd(&s_dw[(2 * e) * LPR + lane], a1[e]);
+      atomicAdd(&s_dw[(2 * e + 1) * LPR + lane], a2[e]);
     }
   }
   __syncthreads();

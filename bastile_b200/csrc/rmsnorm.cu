@@ -86,7 +86,7 @@ rms_fwd_rows(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y
 #pragma unroll
     for (int r = 0; r < RPI; ++r) {
       const int64_t row = base + r * kGroups + group;
-      float ss = 0.f;
+      float ss = 0.f;  // one scalar chain, element by element: its order is pinned by tests
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         float f[E];
@@ -100,16 +100,18 @@ rms_fwd_rows(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y
       for (int i = 0; i < VPT; ++i) forget_unpacked(xv[r][i]);
       if (row < M) {
         if (lane == 0) rstd[row] = rs;
+        const f32x2 rs2 = pair(rs, rs);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
           const int v = lane + i * LPR;
           if (v < nv) {
-            float f[E], wf[E];
-            Cvt<T>::unpack(xv[r][i], f);
-            Cvt<T>::unpack(ld_global_v4(w + static_cast<int64_t>(v) * E), wf);
+            // elementwise part on packed fp32 pairs: same value per element, half the issue slots
+            f32x2 f[E / 2], wf[E / 2];
+            unpack_pairs<T>(xv[r][i], f);
+            unpack_pairs<T>(ld_global_v4(w + static_cast<int64_t>(v) * E), wf);
 #pragma unroll
-            for (int e = 0; e < E; ++e) f[e] = f[e] * rs * wf[e];
-            st_global_v4(y + row * ld_y + static_cast<int64_t>(v) * E, Cvt<T>::pack(f));
+            for (int e = 0; e < E / 2; ++e) f[e] = mul2(mul2(f[e], rs2), wf[e]);
+            st_global_v4(y + row * ld_y + static_cast<int64_t>(v) * E, pack_pairs<T>(f));
           }
         }
       }
@@ -181,15 +183,18 @@ rms_bwd_rows(const T* __restrict__ dy, const T* __restrict__ x, const T* __restr
 
   for (int c = threadIdx.x; c < N; c += kThreads) s_dw[c] = 0.f;
 
-  float wf[VPT][E];
-  float acc[VPT][E];
+  // elementwise arithmetic on packed fp32 pairs (half the issue slots, same values); the dot
+  // product stays one scalar chain, whose order is pinned by tests
+  constexpr int P = E / 2;
+  f32x2 wf[VPT][P];
+  f32x2 acc[VPT][P];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = lane + i * LPR;
     uint4 wv = (v < nv) ? ld_global_v4(w + static_cast<int64_t>(v) * E) : make_uint4(0, 0, 0, 0);
-    Cvt<T>::unpack(wv, wf[i]);
+    unpack_pairs<T>(wv, wf[i]);
 #pragma unroll
-    for (int e = 0; e < E; ++e) acc[i][e] = 0.f;
+    for (int e = 0; e < P; ++e) acc[i][e] = pair(0.f, 0.f);
   }
 
   for (int64_t base = static_cast<int64_t>(blockIdx.x) * rows_per_iter; base < M;
@@ -214,16 +219,19 @@ rms_bwd_rows(const T* __restrict__ dy, const T* __restrict__ x, const T* __restr
     for (int r = 0; r < RPI; ++r) {
       const int64_t row = base + r * kGroups + group;
       float dot = 0.f;
+      const f32x2 rs2 = pair(rs[r], rs[r]);
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
-        float xf[E], gf[E];
-        Cvt<T>::unpack(xv[r][i], xf);
-        Cvt<T>::unpack(gv[r][i], gf);
+        f32x2 xf[P], gf[P];
+        unpack_pairs<T>(xv[r][i], xf);
+        unpack_pairs<T>(gv[r][i], gf);
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
-          const float xh = xf[e] * rs[r];
-          dot = fmaf(xh, gf[e] * wf[i][e], dot);
-          acc[i][e] = fmaf(gf[e], xh, acc[i][e]);
+        for (int e = 0; e < P; ++e) {
+          const f32x2 xh = mul2(xf[e], rs2);
+          const f32x2 t = mul2(gf[e], wf[i][e]);
+          dot = fmaf(lo_of(xh), lo_of(t), dot);
+          dot = fmaf(hi_of(xh), hi_of(t), dot);
+          acc[i][e] = fma2(gf[e], xh, acc[i][e]);
         }
       }
       dot = group_sum<LPR>(dot) * inv_n;
@@ -237,20 +245,21 @@ rms_bwd_rows(const T* __restrict__ dy, const T* __restrict__ x, const T* __restr
         for (int i = 0; i < VPT; ++i) {
           const int v = lane + i * LPR;
           if (v < nv) {
-            float xf[E], gf[E], o[E];
-            Cvt<T>::unpack(xv[r][i], xf);
-            Cvt<T>::unpack(gv[r][i], gf);
+            f32x2 xf[P], gf[P], o[P];
+            unpack_pairs<T>(xv[r][i], xf);
+            unpack_pairs<T>(gv[r][i], gf);
+            const f32x2 ndot = pair(-dot, -dot);
 #pragma unroll
-            for (int e = 0; e < E; ++e)  // explicit operations: the fused q/k-norm + RoPE
-              // backward spells out the same ones and stays bit-identical
-              o[e] = fmaf(-(xf[e] * rs[r]), dot, gf[e] * wf[i][e]) * rs[r];
+            for (int e = 0; e < P; ++e)  // explicit operations: the fused q/k-norm + RoPE backward
+              // spells out the same ones and stays bit-identical: fma(-(x*rs), dot, g*w) * rs
+              o[e] = mul2(fma2(mul2(xf[e], rs2), ndot, mul2(gf[e], wf[i][e])), rs2);
             if constexpr (ADD) {
-              float a[E];
-              Cvt<T>::unpack(ld_stream_v4(dres + row * ld_dres + static_cast<int64_t>(v) * E), a);
+              f32x2 a[P];
+              unpack_pairs<T>(ld_stream_v4(dres + row * ld_dres + static_cast<int64_t>(v) * E), a);
 #pragma unroll
-              for (int e = 0; e < E; ++e) o[e] += a[e];
+              for (int e = 0; e < P; ++e) o[e] = add2(o[e], a[e]);
             }
-            st_global_v4(dx + row * ld_dx + static_cast<int64_t>(v) * E, Cvt<T>::pack(o));
+            st_global_v4(dx + row * ld_dx + static_cast<int64_t>(v) * E, pack_pairs<T>(o));
           }
         }
       }
@@ -259,12 +268,20 @@ rms_bwd_rows(const T* __restrict__ dy, const T* __restrict__ x, const T* __restr
 
   __syncthreads();  // s_dw zeroed
   // Row groups that share a warp hold the same columns: fold them together first.
+  float accf[VPT][E];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+#pragma unroll
+    for (int e = 0; e < P; ++e) {
+      accf[i][2 * e] = lo_of(acc[i][e]);
+      accf[i][2 * e + 1] = hi_of(acc[i][e]);
+    }
 #pragma unroll
   for (int o = LPR; o < 32; o <<= 1) {
 #pragma unroll
     for (int i = 0; i < VPT; ++i)
 #pragma unroll
-      for (int e = 0; e < E; ++e) acc[i][e] += __shfl_xor_sync(0xffffffffu, acc[i][e], o);
+      for (int e = 0; e < E; ++e) accf[i][e] += __shfl_xor_sync(0xffffffffu, accf[i][e], o);
   }
   // s_dw is kept element-major (index e * nv + v) so that the lanes of one instruction,
   // which differ in v, fall into different banks.
@@ -274,7 +291,7 @@ rms_bwd_rows(const T* __restrict__ dy, const T* __restrict__ x, const T* __restr
       const int v = lane + i * LPR;
       if (v < nv) {
 #pragma unroll
-        for (int e = 0; e < E; ++e) atomicAdd(&s_dw[e * nv + v], acc[i][e]);
+        for (int e = 0; e < E; ++e) atomicAdd(&s_dw[e * nv + v], accf[i][e]);
       }
     }
   }

@@ -74,6 +74,7 @@ SIGNATURES = {
     "bt_set_gemm_dynamic_tiles": (c_int, [c_int]),
     "bt_set_gemm_tile_stores": (c_int, [c_int]),
     "bt_set_gemm_group_rows": (c_int, [c_int]),
+    "bt_set_dependent_launch": (c_int, [c_int]),
     "bt_mlp_fwd": (c_int, [c_void_p] * 8 + [c_int64] * 4 + [c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "bt_mlp_bwd": (c_int, [c_void_p] * 14 + [c_int64] * 6 + [c_int, c_void_p, c_void_p]),
     "bt_lce_logits_stats": (c_int, [c_void_p] * 6 + [c_int64] * 7 + [c_int, c_void_p, c_void_p]),

@@ -78,6 +78,7 @@ __global__ void __launch_bounds__(kThreads)
 adamw_one(T* __restrict__ p, const T* __restrict__ g, T* __restrict__ m, T* __restrict__ v,
           int64_t n, int vec_ok, Hyper h) {
   constexpr int E = Cvt<T>::N;
+  grid_dependency_wait();
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
   const int64_t nvec = vec_ok ? n / E : 0;
@@ -117,10 +118,11 @@ int one_t(void* p, const void* g, void* m, void* v, int64_t n, const Hyper& h, i
   const int64_t work = vec_ok ? ceil_div(n, E) : n;
   const int64_t blocks = ceil_div(work, kThreads);
   const int64_t cap = static_cast<int64_t>(sm_count()) * ctas_per_sm;
-  adamw_one<T><<<static_cast<unsigned>(blocks < 1 ? 1 : (blocks < cap ? blocks : cap)), kThreads, 0,
-                 s>>>(static_cast<T*>(p), static_cast<const T*>(g), static_cast<T*>(m),
-                      static_cast<T*>(v), n, vec_ok, h);
-  BT_CHECK_LAUNCH("adamw_one");
+  BT_CHECK_LAUNCHED(
+      launch_dependent(adamw_one<T>, dim3(static_cast<unsigned>(blocks < 1 ? 1 : (blocks < cap ? blocks : cap))),
+                       dim3(kThreads), 0, s, static_cast<T*>(p), static_cast<const T*>(g), static_cast<T*>(m),
+                       static_cast<T*>(v), n, vec_ok, h),
+      "adamw_one");
   return BT_OK;
 }
 
@@ -145,6 +147,7 @@ adamw_master(float* __restrict__ p32, float* __restrict__ m, float* __restrict__
              Hyper h) {
   constexpr int E = Cvt<T>::N;   // elements per 16-byte vector of T
   constexpr int Q = E / 4;       // float4 vectors of fp32 state per vector of T
+  grid_dependency_wait();
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
   const int64_t nvec = vec_ok ? n / E : 0;
@@ -204,10 +207,11 @@ int master_t(float* p32, float* m, float* v, const void* g, void* p_out, int64_t
   const int64_t work = vec_ok ? ceil_div(n, E) : n;
   const int64_t blocks = ceil_div(work, kThreads);
   const int64_t cap = static_cast<int64_t>(sm_count()) * ctas_per_sm;
-  adamw_master<T><<<static_cast<unsigned>(blocks < 1 ? 1 : (blocks < cap ? blocks : cap)), kThreads,
-                    0, s>>>(p32, m, v, static_cast<const T*>(g), static_cast<T*>(p_out), n, vec_ok,
-                            gscale, h);
-  BT_CHECK_LAUNCH("adamw_master");
+  BT_CHECK_LAUNCHED(
+      launch_dependent(adamw_master<T>, dim3(static_cast<unsigned>(blocks < 1 ? 1 : (blocks < cap ? blocks : cap))),
+                       dim3(kThreads), 0, s, p32, m, v, static_cast<const T*>(g), static_cast<T*>(p_out), n,
+                       vec_ok, gscale, h),
+      "adamw_master");
   return BT_OK;
 }
 

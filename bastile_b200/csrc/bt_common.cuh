@@ -219,6 +219,41 @@ __device__ __forceinline__ float group_sum(float v) {
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// Programmatic dependent launch: a kernel launched through launch_dependent() may be set up on
+// the SMs (its CTAs scheduled, their prologues run) while the previous kernel of the stream is
+// still draining; it must call grid_dependency_wait() before its first access to global memory,
+// which blocks until the previous kernel has completed and its writes are visible.  Launched
+// the ordinary way the wait is a no-op.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+int dependent_launch_mode();  // 1 (default): kernels are launched as programmatic dependents (c_api.cu)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = dependent_launch_mode() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+#define BT_CHECK_LAUNCHED(err, what)                                         \
+  do {                                                                       \
+    const cudaError_t e__ = (err);                                           \
+    if (e__ != cudaSuccess) {                                                \
+      ::bt::set_error("%s: %s", (what), cudaGetErrorString(e__));            \
+      return BT_ERR_LAUNCH;                                                  \
+    }                                                                        \
+  } while (0)
+
 // RMSNorm backward scratch: K private copies of the N fp32 column sums (CTA b adds into
 // copy b % K, which divides the same-address atomic traffic by K) followed by one arrival
 // counter.  K * N stays within 16384 words.

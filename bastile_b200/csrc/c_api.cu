@@ -18,6 +18,11 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
+namespace {
+int g_dependent_launch = 1;
+}
+int dependent_launch_mode() { return g_dependent_launch; }
+
 int sm_count() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
@@ -37,3 +42,9 @@ extern "C" int bt_version(void) { return 100; }  // 0.1.0
 extern "C" const char* bt_last_error(void) { return bt::g_err; }
 
 extern "C" int bt_sm_count(void) { return bt::sm_count(); }
+
+extern "C" int bt_set_dependent_launch(int enable) {
+  const int prev = bt::g_dependent_launch;
+  if (enable >= 0) bt::g_dependent_launch = enable ? 1 : 0;
+  return prev;
+}

@@ -598,6 +598,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CU
   __syncthreads();
   ptx::tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  grid_dependency_wait();  // barriers, tensor memory and descriptors were set up while the previous kernel drained
 
   constexpr int kBk = Geo<T>::kBk, kMnBox = Geo<T>::kMnBox, kBoxBytes = Geo<T>::kBoxBytes;
   const int nkb0 = (p.K0 + kBk - 1) / kBk;
@@ -860,6 +861,7 @@ gemm_kernel_pair(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
   ptx::cluster_sync_all();  // the peer's barriers exist before anything signals them
   ptx::tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  grid_dependency_wait();  // barriers, tensor memory and descriptors were set up while the previous kernel drained
 
   constexpr int kBk = Geo<T>::kBk, kMnBox = Geo<T>::kMnBox, kBoxBytes = Geo<T>::kBoxBytes;
   const int nkb0 = (p.K0 + kBk - 1) / kBk;
@@ -1192,8 +1194,9 @@ int launch_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1
     return BT_ERR_LAUNCH;
   }
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  kern<<<grid, kThreads, kSmemBytes, s>>>(a0, b0, a1, b1, a2, o[0], o[1], o[2], p);
-  BT_CHECK_LAUNCH("gemm_kernel");
+  BT_CHECK_LAUNCHED(launch_dependent(kern, dim3(grid), dim3(kThreads), kSmemBytes, s, a0, b0, a1, b1, a2, o[0],
+                                     o[1], o[2], p),
+                    "gemm_kernel");
   return BT_OK;
 }
 
@@ -1294,13 +1297,15 @@ int launch_pair_t(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMa
   cfg.blockDim = dim3(kThreadsPair, 1, 1);
   cfg.dynamicSmemBytes = kSmemBytes2;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = dependent_launch_mode() ? 1 : 0;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a0, b0, a1, b1, a2, o[0], o[1], o[2], q);
   if (e != cudaSuccess) {
     set_error("gemm_kernel_pair: %s", cudaGetErrorString(e));

@@ -91,6 +91,7 @@ __global__ void __launch_bounds__(kThreads, MINB)
 headnorm_rope_fwd(const __grid_constant__ HeadPair pp) {
   constexpr int E = Cvt<T>::N;
   constexpr int kGroups = kThreads / LPR;
+  grid_dependency_wait();
   const bool side = blockIdx.x >= pp.split;
   const HeadArgs& a = pp.p[side ? 1 : 0];
   const unsigned bid = side ? blockIdx.x - pp.split : blockIdx.x;
@@ -192,6 +193,7 @@ headnorm_rope_bwd(const __grid_constant__ HeadPair pp) {
   const float inv_n = 1.0f / static_cast<float>(N);
 
   for (int c = threadIdx.x; c < N; c += kThreads) s_dw[c] = 0.f;
+  grid_dependency_wait();
 
   // Elementwise arithmetic on packed fp32 pairs; the dot product keeps its scalar chains (their
   // order is part of the bit-identity with the stand-alone kernels).
@@ -368,18 +370,19 @@ int launch_t(const HeadPair& pp, cudaStream_t s) {
   HeadPair q = pp;
   q.split = static_cast<unsigned>(g0);
   const unsigned grid = static_cast<unsigned>(g0 + g1);
+  cudaError_t le = cudaSuccess;
 #define BT_HEAD(L)                                                         \
   if (lpr == L) {                                                          \
     if constexpr (BWD)                                                     \
-      headnorm_rope_bwd<T, L, kHpi, 2><<<grid, kThreads, 0, s>>>(q);       \
+      le = launch_dependent(headnorm_rope_bwd<T, L, kHpi, 2>, dim3(grid), dim3(kThreads), 0, s, q); \
     else                                                                   \
-      headnorm_rope_fwd<T, L, kHpi, 3><<<grid, kThreads, 0, s>>>(q);       \
+      le = launch_dependent(headnorm_rope_fwd<T, L, kHpi, 3>, dim3(grid), dim3(kThreads), 0, s, q); \
   }
   BT_HEAD(4)
   BT_HEAD(8)
   BT_HEAD(16)
 #undef BT_HEAD
-  BT_CHECK_LAUNCH(BWD ? "headnorm_rope_bwd" : "headnorm_rope_fwd");
+  BT_CHECK_LAUNCHED(le, BWD ? "headnorm_rope_bwd" : "headnorm_rope_fwd");
   return BT_OK;
 }
 

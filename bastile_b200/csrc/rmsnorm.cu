@@ -39,6 +39,7 @@ rms_fwd_rows(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y
   const int nv = N / E;
   const float inv_n = 1.0f / static_cast<float>(N);
   const int64_t rows_per_iter = static_cast<int64_t>(kGroups) * RPI;
+  grid_dependency_wait();
 
   for (int64_t base = static_cast<int64_t>(blockIdx.x) * rows_per_iter; base < M;
        base += static_cast<int64_t>(gridDim.x) * rows_per_iter) {
@@ -182,6 +183,7 @@ rms_bwd_rows(const T* __restrict__ dy, const T* __restrict__ x, const T* __restr
   const int64_t rows_per_iter = static_cast<int64_t>(kGroups) * RPI;
 
   for (int c = threadIdx.x; c < N; c += kThreads) s_dw[c] = 0.f;
+  grid_dependency_wait();
 
   // elementwise arithmetic on packed fp32 pairs (half the issue slots, same values); the dot
   // product stays one scalar chain, whose order is pinned by tests
@@ -422,9 +424,11 @@ int fwd_t(const void* x, const void* w, void* y, float* rstd, int64_t M, int64_t
     (void)attr;                                                                                  \
     const size_t smem = staged::smem_bytes(static_cast<int>(N), sizeof(T), R, ADD ? 2 : 1);      \
     const int grid = grid_for(ceil_div(M, R), 2);                                                \
-    staged::rms_fwd_staged<T, V, R, ADD><<<grid, staged::kThreads, smem, s>>>(                   \
-        xp, wp, yp, rstd, M, static_cast<int>(N), ld_x, ld_y, eps, rp, sp, rr.ld_res, rr.ld_sum); \
-    BT_CHECK_LAUNCH("rms_fwd_staged");                                                           \
+    BT_CHECK_LAUNCHED(launch_dependent(staged::rms_fwd_staged<T, V, R, ADD>, dim3(grid),          \
+                                       dim3(staged::kThreads), smem, s, xp, wp, yp, rstd, M,     \
+                                       static_cast<int>(N), ld_x, ld_y, eps, rp, sp, rr.ld_res,  \
+                                       rr.ld_sum),                                               \
+                      "rms_fwd_staged");                                                         \
     return BT_OK;                                                                                \
   }
     BT_FWDS(1, 8)
@@ -437,9 +441,10 @@ int fwd_t(const void* x, const void* w, void* y, float* rstd, int64_t M, int64_t
   const int grid = grid_for(ceil_div(M, rows_per_iter), 32);
 #define BT_FWD(L, V, R)                                                                        \
   if (c.lpr == L && c.vpt == V) {                                                              \
-    rms_fwd_rows<T, V, L, R, ADD><<<grid, kThreads, 0, s>>>(                                   \
-        xp, wp, yp, rstd, M, static_cast<int>(N), ld_x, ld_y, eps, rp, sp, rr.ld_res, rr.ld_sum); \
-    BT_CHECK_LAUNCH("rms_fwd_rows");                                                           \
+    BT_CHECK_LAUNCHED(launch_dependent(rms_fwd_rows<T, V, L, R, ADD>, dim3(grid), dim3(kThreads), \
+                                       0, s, xp, wp, yp, rstd, M, static_cast<int>(N), ld_x,   \
+                                       ld_y, eps, rp, sp, rr.ld_res, rr.ld_sum),               \
+                      "rms_fwd_rows");                                                         \
     return BT_OK;                                                                              \
   }
   BT_FWD(8, 1, 4)
@@ -479,10 +484,11 @@ int bwd_t(const void* dy, const void* x, const void* w, const float* rstd, void*
     (void)attr;                                                                                  \
     const size_t smem = staged::smem_bytes(static_cast<int>(N), sizeof(T), R, 2);                \
     const int grid = grid_for(ceil_div(M, R), 2);                                                \
-    staged::rms_bwd_staged<T, V, R, ADD><<<grid, staged::kThreads, smem, s>>>(                   \
-        gp, xp, wp, rstd, dxp, dwp, wsp, M, static_cast<int>(N), ld_dy, ld_x, ld_dx, rp,         \
-        rr.ld_dres);                                                                             \
-    BT_CHECK_LAUNCH("rms_bwd_staged");                                                           \
+    BT_CHECK_LAUNCHED(launch_dependent(staged::rms_bwd_staged<T, V, R, ADD>, dim3(grid),          \
+                                       dim3(staged::kThreads), smem, s, gp, xp, wp, rstd, dxp,   \
+                                       dwp, wsp, M, static_cast<int>(N), ld_dy, ld_x, ld_dx, rp, \
+                                       rr.ld_dres),                                              \
+                      "rms_bwd_staged");                                                         \
     return BT_OK;                                                                                \
   }
     BT_BWDS(1, 4)
@@ -496,10 +502,10 @@ int bwd_t(const void* dy, const void* x, const void* w, const float* rstd, void*
     const size_t smem = static_cast<size_t>(N) * sizeof(float);
 #define BT_BWD(L, V, R)                                                                         \
   if (c.lpr == L && c.vpt == V) {                                                               \
-    rms_bwd_rows<T, V, L, R, ADD><<<grid, kThreads, smem, s>>>(                                 \
-        gp, xp, wp, rstd, dxp, dwp, wsp, M, static_cast<int>(N), ld_dy, ld_x, ld_dx, rp,        \
-        rr.ld_dres);                                                                            \
-    BT_CHECK_LAUNCH("rms_bwd_rows");                                                            \
+    BT_CHECK_LAUNCHED(launch_dependent(rms_bwd_rows<T, V, L, R, ADD>, dim3(grid), dim3(kThreads),  \
+                                       smem, s, gp, xp, wp, rstd, dxp, dwp, wsp, M,             \
+                                       static_cast<int>(N), ld_dy, ld_x, ld_dx, rp, rr.ld_dres), \
+                      "rms_bwd_rows");                                                          \
     return BT_OK;                                                                               \
   }
     BT_BWD(8, 1, 4)

@@ -90,6 +90,7 @@ rms_fwd_staged(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__
     ptx::fence_mbar_init();
   }
   __syncthreads();
+  grid_dependency_wait();  // everything above ran while the previous kernel of the stream drained
 
   auto issue = [&](int64_t tile, int s) {
     const int64_t r0 = tile * R;
@@ -222,6 +223,7 @@ rms_bwd_staged(const T* __restrict__ dy, const T* __restrict__ x, const T* __res
     ptx::fence_mbar_init();
   }
   __syncthreads();
+  grid_dependency_wait();  // everything above ran while the previous kernel of the stream drained
 
   auto issue = [&](int64_t tile, int s) {
     const int64_t r0 = tile * R;

@@ -34,6 +34,7 @@ struct RopeArgs {
 template <typename T>
 __global__ void __launch_bounds__(kThreads) rope_vec(const RopeArgs a) {
   constexpr int E = Cvt<T>::N;
+  grid_dependency_wait();
   const int half = a.D / 2;
   const int vph = half / E;  // vectors per half row
   const int64_t H = a.Hq + a.Hk;
@@ -157,8 +158,9 @@ int launch(const RopeArgs& a, cudaStream_t s) {
     const int64_t total = a.B * a.T * hblocks * (half / E);
     const int64_t blocks = ceil_div(total, kThreads);
     const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
-    rope_vec<T><<<static_cast<unsigned>(blocks < cap ? blocks : cap), kThreads, 0, s>>>(a);
-    BT_CHECK_LAUNCH("rope_vec");
+    BT_CHECK_LAUNCHED(launch_dependent(rope_vec<T>, dim3(static_cast<unsigned>(blocks < cap ? blocks : cap)),
+                                       dim3(kThreads), 0, s, a),
+                      "rope_vec");
   } else {
     const int64_t total = a.B * H * a.T * half;
     const int64_t blocks = ceil_div(total, kThreads);

@@ -885,6 +885,9 @@ def main():
     ap.add_argument("--bucket-mb", type=int, default=1024, help="--parallel sharded: size of a gradient bucket")
     ap.add_argument("--group-rows", type=int, default=0,
                     help="tile rasterisation of the GEMMs: row tiles walked per column tile (0 = library default)")
+    ap.add_argument("--dependent-launch", default="on", choices=["on", "off"],
+                    help="launch the library's kernels as programmatic dependents of their predecessors (on, the "
+                         "library's default) or the ordinary way (off: bt_set_dependent_launch(0))")
     ap.add_argument("--no-per-op", action="store_true")
     ap.add_argument("--only-op", default=None, choices=["rmsnorm", "rope", "swiglu", "mlp", "lce"],
                     help="run just this op's forward+backward micro-benchmark (small case for profilers)")
@@ -920,6 +923,7 @@ def main():
     peaks, peak_kind = load_peaks()
     _lib.get_lib().bt_set_gemm_tile_stores(1 if args.tile_stores == "on" else 0)
     _lib.get_lib().bt_set_gemm_group_rows(args.group_rows)
+    _lib.get_lib().bt_set_dependent_launch(1 if args.dependent_launch == "on" else 0)
     if args.only_op:
         res = per_op_bench(peaks, only=args.only_op, iters=args.op_iters, rows=args.op_rows, lce_chunk=args.lce_chunk)
         _lib.check_status(dev, "per-op benchmark")

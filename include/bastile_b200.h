@@ -254,6 +254,14 @@ int bt_set_gemm_tile_stores(int enable);
  * reference counterpart (cuBLAS picks its own schedule). */
 int bt_set_gemm_group_rows(int row_tiles);
 
+/* 1 (default): the library launches its kernels as programmatic dependents of whatever precedes
+ * them in the stream (cudaLaunchAttributeProgrammaticStreamSerialization): a kernel is set up on
+ * the SMs while its predecessor drains and executes griddepcontrol.wait before its first access
+ * to global memory, which takes the launch gap (about 2 us per launch on a B200) out of a chain
+ * of short kernels.  0: ordinary launches.  Same results either way.  A negative argument only
+ * queries; returns the previous setting.  Process-wide.  No reference counterpart. */
+int bt_set_dependent_launch(int enable);
+
 /* ------------------------------------------- per-head RMSNorm + RoPE, fused */
 
 /* q_norm / k_norm followed by the rotary embedding, for the two tensors of

@@ -830,6 +830,37 @@ def _slim(m):
     return {k: m[k] for k in keep if k in m}
 
 
+def _row_ops_in_step(op_ms, steps, seq, layers, fused_layers, grad_checkpoint, hbm_gbs):
+    """GB/s of the bandwidth-bound ops INSIDE the training step: algorithmic bytes of the calls a step makes over the
+    CUDA-event time of those calls (the events `op_ms_per_step` is built from).  Only for the layout whose call
+    list is known here: fused layers, no recomputation, Qwen3-8B heads (32 q + 8 k/v heads of 128)."""
+    if not fused_layers or grad_checkpoint:
+        return None
+    h, hq, hk, d, e = QWEN3_8B["hidden_size"], 32, 8, 128, 2
+    act = seq * h * e                                   # one [seq, hidden] bf16 tensor
+    heads = seq * (hq + hk) * d * e                     # q and k of one layer
+    cs = 2 * seq * d * e                                # cos and sin
+    want = {  # name -> (calls per step, algorithmic bytes per step)
+        "rmsnorm_fwd": (2 * layers + 1, layers * (2 * act + 4 * act) + 2 * act),       # norm; add + norm (x, r -> y, stream)
+        "rmsnorm_bwd": (2 * layers + 1, 2 * layers * 4 * act + 3 * act),               # dy, x, d(stream) -> dx
+        "rope_fwd": (layers, layers * (2 * heads + cs)),                               # q/k-norm + RoPE, q and k at once
+        "rope_bwd": (layers, layers * (3 * heads + cs)),                               # d(out), heads -> d(heads)
+    }
+    out = {}
+    for name, (calls, nbytes) in want.items():
+        got = op_ms.get(name)
+        if not got or got[0] != calls * steps or got[1] <= 0:
+            continue
+        ms = got[1] / steps
+        gbs = nbytes / (ms / 1e3) / 1e9
+        out[name] = {"calls_per_step": calls, "ms_per_step": ms, "algorithmic_GB_per_step": nbytes / 1e9,
+                     "GBps": gbs, "frac_of_hbm_peak": gbs / hbm_gbs}
+    if out:
+        out["note"] = ("inside the step these kernels run at the power-capped clock (see clocks) and share HBM with the "
+                       "AdamW updates of the side stream; per_op holds the same kernels timed alone")
+    return out or None
+
+
 def _traffic_from_profile():
     """DRAM bytes per launch of the dominant kernel, from the committed summary of its ncu capture."""
     p = ROOT / "profiles" / "gemm_kernel_pair_mlp_8192x4096x12288.json"
@@ -1012,6 +1043,9 @@ def main():
             "peak_mem_GB": m["peak_mem_GB"], "applied": main_run["applied"]}
     if main_run["sweep"]:
         line["seq_sweep"] = [_slim(r) for r in main_run["sweep"]]
+    row_ops = _row_ops_in_step(op_ms, args.steps, seq, args.layers, fused_layers, grad_checkpoint, peaks["hbm_gbs"])
+    if row_ops:
+        line["row_ops_in_step"] = row_ops
     rc = 0
 
     def guarded(name, fn):

@@ -18,9 +18,11 @@ in the reference.
 One addition, off by default: ``apply(fused_layers=True)`` also replaces
 ``Qwen3DecoderLayer.forward`` and ``Qwen3Attention.forward`` with versions that
 fold the residual adds into the norm / down-projection kernels and run
-q/k-norm + RoPE as one kernel (``ops/fused_layers.py``; ``gemm_projections="dx"``
-or ``"all"`` additionally moves the q/k/v/o projections' input gradient, or all of
-their products, from ``nn.Linear`` to the library's GEMM); the names
+q/k-norm + RoPE as one kernel (``ops/fused_layers.py``).  With it the q/k/v
+projections keep their library GEMMs but let those GEMMs accumulate the shared
+input gradient (``gemm_projections="acc"``, the default; ``"off"`` leaves
+``nn.Linear`` alone; ``"dx"``, ``"all"`` and ``"qkv"`` move the input gradient, every
+product, or the stacked q|k|v product to the library's own GEMM); the names
 ``"decoder_layer_qwen3"`` and ``"attention_qwen3"`` are then appended to the
 returned list, and ``reset()`` restores both methods.
 """
@@ -117,7 +119,7 @@ def apply(rms_norm: bool = True, swiglu: bool = True, rope: bool = True,
 
             applied.extend(fused_layers.install(importlib.import_module(_QWEN3), decoder_layer=True,
                                                 attention=bool(rope),
-                                                projections=kwargs.get("gemm_projections", "off")))
+                                                projections=kwargs.get("gemm_projections", "acc")))
         except Exception as exc:  # patch failures are reported, not raised
             log.warning("Could not apply the fused decoder-layer forwards: %s", exc)
 

@@ -245,7 +245,7 @@ _GEMM_DTYPES = (torch.bfloat16, torch.float16, torch.float32)
 #   instead of nine GEMMs and two accumulation passes) wherever the three weights lie one after the
 #   other in memory (stack_qkv_weights), o_proj on nn.Linear; layers whose weights are not stacked
 #   run as in "off".
-PROJECTION_MODES = ("off", "dx", "all", "qkv")
+PROJECTION_MODES = ("off", "acc", "dx", "all", "qkv")
 _projection_mode = "off"
 
 
@@ -361,6 +361,51 @@ class SharedInputLinearFunction(torch.autograd.Function):
                     dw.zero_()
                 dws[i] = dw.to(ctx.w_dtypes[i])
         return (None, dx, *dws)
+
+
+class AccumulatedInputGradFunction(torch.autograd.Function):
+    """``tuple(x @ w.T for w in weights)`` for bias-free linear layers that share their input,
+    on the LIBRARY GEMMs exactly as ``nn.Linear`` runs them, with one difference in the backward:
+    ``dx = sum_i dy_i @ w_i`` is accumulated by the GEMMs themselves (``addmm_``, beta = 1) instead
+    of one result per layer plus the elementwise additions autograd would append - for q / k / v
+    that is two passes over a [tokens, hidden] tensor less per layer.  Weight gradients go
+    straight into a registered gradient destination when there is one."""
+
+    @staticmethod
+    def forward(ctx, x, *weights):
+        _lib.require_cuda(x, *weights)
+        x2 = _rows2d(x)
+        ws = [_weight(w, x.dtype) for w in weights]
+        outs = tuple(torch.mm(x2, w.t()).view(*x.shape[:-1], w.shape[0]) for w in ws)
+        ctx.save_for_backward(x2, *ws)
+        ctx.x_shape = x.shape
+        ctx.w_dtypes = [w.dtype for w in weights]
+        ctx.sinks = [w if w.dtype == x.dtype else None for w in weights]
+        ctx.set_materialize_grads(False)
+        return outs
+
+    @staticmethod
+    def backward(ctx, *dys):
+        x2, *ws = ctx.saved_tensors
+        live = [(i, _rows2d(dy.to(x2.dtype))) for i, dy in enumerate(dys) if dy is not None]
+        dx = None
+        if ctx.needs_input_grad[0]:
+            for i, g in live:
+                if dx is None:
+                    dx = torch.mm(g, ws[i])
+                else:
+                    dx.addmm_(g, ws[i])
+            dx = dx.view(ctx.x_shape) if dx is not None else torch.zeros(ctx.x_shape, dtype=x2.dtype, device=x2.device)
+        dws = [None] * len(ws)
+        for i, g in live:
+            if ctx.needs_input_grad[1 + i]:
+                sink = _lib.grad_sink(ctx.sinks[i], x2.dtype) if ctx.sinks[i] is not None else None
+                if sink is not None:
+                    dws[i] = torch.mm(g.t(), x2, out=sink)
+                else:
+                    dws[i] = torch.mm(g.t(), x2).to(ctx.w_dtypes[i])
+        ctx.sinks = None
+        return (dx, *dws)
 
 
 def _stacked(wq, wk, wv) -> bool:
@@ -548,6 +593,10 @@ def attention_forward(self, hidden_states, position_embeddings, attention_mask, 
             and _qkv_fusable(hidden_states, self.q_proj.weight, self.k_proj.weight, self.v_proj.weight)):
         q_lin, k_lin, v_lin = QKVProjectionFunction.apply(hidden_states, self.q_proj.weight, self.k_proj.weight,
                                                           self.v_proj.weight)
+    elif (_projection_mode == "acc" and plain and hidden_states.is_cuda and torch.is_grad_enabled()
+          and not torch.is_autocast_enabled()):
+        q_lin, k_lin, v_lin = AccumulatedInputGradFunction.apply(hidden_states, self.q_proj.weight,
+                                                                 self.k_proj.weight, self.v_proj.weight)
     elif on_gemm:
         q_lin, k_lin, v_lin = shared_input_linear(hidden_states, self.q_proj.weight, self.k_proj.weight,
                                                   self.v_proj.weight, dx_only=_projection_mode == "dx")

@@ -595,7 +595,7 @@ class _LigerPatches:
 
 
 def train_run(*, dev, rank, world, local, patches="bastile", parallel="single", optimizer="bastile", seq=SEQ_LEN,
-              layers=36, intermediate=12288, steps=5, warmup=3, fused_layers=True, gemm_projections="off",
+              layers=36, intermediate=12288, steps=5, warmup=3, fused_layers=True, gemm_projections="acc",
               overlap_opt=True, tiles="auto", grad_checkpoint=False, measure_e2e=True, sample_clocks=False,
               master_weights=False, sweep=(), bucket_mb=1024):
     """Build the model under the given patches / parallel wrapper / optimizer, run `warmup` untimed
@@ -899,8 +899,10 @@ def main():
                     help="leave Qwen3DecoderLayer.forward / Qwen3Attention.forward as HF has them (by default the "
                          "bench applies bastile_b200.apply(fused_layers=True): residual adds folded into the norm "
                          "and down-projection kernels, q/k-norm + RoPE as one kernel)")
-    ap.add_argument("--gemm-projections", default="off", choices=["off", "dx", "all", "qkv"],
-                    help="with fused layers: off = q/k/v/o_proj stay on nn.Linear (cuBLAS); dx = their shared input "
+    ap.add_argument("--gemm-projections", default="acc", choices=["off", "acc", "dx", "all", "qkv"],
+                    help="with fused layers: off = q/k/v/o_proj stay on nn.Linear (cuBLAS); acc = the same library "
+                         "GEMMs, the q/k/v input gradient accumulated by the GEMMs (beta = 1) instead of added "
+                         "afterwards; dx = their shared input "
                          "gradient from two bt_gemm_ex launches; all = every product of theirs on bt_gemm_ex; qkv = "
                          "q/k/v weights stacked in memory and the three projections run as one product each way")
     ap.add_argument("--no-overlap-optimizer", action="store_true",

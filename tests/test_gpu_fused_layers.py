@@ -362,8 +362,47 @@ def test_qkv_mode_whole_model_matches_separate_projections():
 
 
 
+def test_acc_mode_matches_separate_projections_and_fills_gradient_destinations():
+    """gemm_projections="acc": the library GEMMs of nn.Linear with dx accumulated by the GEMMs.
+    The forward is the same product; gradients agree with autograd's separate products + adds to
+    bf16 rounding of the running sum; with a registered destination dW lands in it uncopied."""
+    from bastile_b200 import _lib
+    from bastile_b200.ops.fused_layers import AccumulatedInputGradFunction
+
+    torch.manual_seed(5)
+    x = torch.randn(2, 67, 256, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    ws = [(0.05 * torch.randn(n, 256, device=DEV)).to(torch.bfloat16).requires_grad_(True) for n in (512, 128, 128)]
+    dys = [torch.randn(2, 67, n, device=DEV).to(torch.bfloat16) for n in (512, 128, 128)]
+    ref = [torch.nn.functional.linear(x, w) for w in ws]
+    torch.autograd.backward(ref, dys)
+    want = [x.grad.clone()] + [w.grad.clone() for w in ws]
+    x.grad = None
+    for w in ws:
+        w.grad = None
+    dest = torch.zeros_like(ws[1])
+    _lib.register_grad_sink(ws[1].data, dest)
+    try:
+        outs = AccumulatedInputGradFunction.apply(x, *ws)
+        for o, r in zip(outs, ref):
+            assert torch.equal(o, r)
+        # v arrives as the transposed view attention hands back: not contiguous
+        dys[2] = dys[2].view(2, 67, 2, 64).transpose(1, 2).contiguous().transpose(1, 2).reshape(2, 67, 128)
+        torch.autograd.backward(outs, dys)
+    finally:
+        _lib.unregister_grad_sinks([dest])
+    assert_close(x.grad, want[0].float().cpu().numpy(), what="dx", rtol=2e-2, atol=2e-2 * float(want[0].abs().max()))
+    for w, g in zip(ws, want[1:]):
+        assert_close(w.grad, g.float().cpu().numpy(), what="dw", rtol=1e-2, atol=1e-2 * float(g.abs().max()))
+    assert ws[1].grad.data_ptr() == dest.data_ptr()
+    # a gradient that never arrives (k unused) is skipped, not materialised
+    x.grad = None
+    q, k, v = AccumulatedInputGradFunction.apply(x, *ws)
+    (q.float().sum() + v.float().sum()).backward()
+    assert x.grad is not None and torch.isfinite(x.grad.float()).all()
+
+
 # ------------------------------------------------------------------ whole model
-@pytest.fixture(params=["off", "dx", "all", "qkv"])
+@pytest.fixture(params=["off", "acc", "dx", "all", "qkv"])
 def fused(request):
     """apply(fused_layers=True) in each mode of the q/k/v/o projections."""
     import bastile_b200

@@ -209,7 +209,9 @@ class ShardedAdamW:
 
     * parameters are re-laid as views into flat buckets (``bucket_mb`` each, filled in reverse
       registration order, the order in which gradients become final; 1 GiB measured best on a
-      Qwen3-8B step on two B200: 416 ms against 420 ms with 256 MiB and 429 ms with 64 MiB);
+      Qwen3-8B step on two B200: 416 ms against 420 ms with 256 MiB and 429 ms with 64 MiB; the
+      parameters whose gradients arrive last go into smaller buckets of ``last_bucket_mb``,
+      a quarter of ``bucket_mb`` unless given, because their collectives are what a step exposes);
     * a post-accumulate-grad hook copies each gradient into its bucket on a side stream - unless
       the op that produced it (the MLP block, the fused loss) found the bucket view registered as
       the weight's gradient destination and wrote it there in the first place; when a
@@ -228,7 +230,8 @@ class ShardedAdamW:
     """
 
     def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 1e-2,
-                 group=None, bucket_mb: int = 1024, master_weights: bool = False, update_fn=None):
+                 group=None, bucket_mb: int = 1024, master_weights: bool = False, update_fn=None,
+                 last_bucket_mb: int | None = None):
         import torch.distributed as dist
 
         if lr < 0 or eps < 0 or not 0 <= betas[0] < 1 or not 0 <= betas[1] < 1 or weight_decay < 0:
@@ -246,10 +249,11 @@ class ShardedAdamW:
         self._where: dict = {}
         self._streams: dict = {}
         self._hooks = []
-        self._build([p for p in params if p.requires_grad], int(bucket_mb) << 20)
+        last_mb = max(1, int(bucket_mb) // 4) if last_bucket_mb is None else int(last_bucket_mb)
+        self._build([p for p in params if p.requires_grad], int(bucket_mb) << 20, min(last_mb, int(bucket_mb)) << 20)
 
     # -- layout
-    def _build(self, params, bucket_bytes):
+    def _build(self, params, bucket_bytes, last_bucket_bytes):
         align = 128  # elements: every parameter view starts on a 256-byte (16-bit) boundary
         quantum = align * self.world
         open_buckets: dict = {}
@@ -310,12 +314,36 @@ class ShardedAdamW:
                 units[-1].append(p)
             else:
                 units.append([p])
-        sizes: dict = {}
-        for unit in reversed(units):  # reverse registration order: the order in which gradients become final
+        def nbytes(unit):
+            return sum(p.numel() * p.element_size() for p in unit)
+
+        # Buckets are filled in reverse registration order: the order in which gradients become final.
+        # What a step leaves exposed is the collectives of the buckets that complete last, so the last
+        # 2 x bucket_bytes of parameters go into buckets of last_bucket_bytes: their reductions start
+        # while the first layers' backward still runs.  A tensor as large as a bucket (embedding,
+        # lm_head) gets a bucket of its own instead of holding its neighbours back, and two neighbours
+        # of the same shape (gate | up, k | v) are never separated, so that an op which writes both
+        # gradients as one stacked result finds their destinations side by side.
+        order = list(reversed(units))
+        remaining: dict = {}
+        for unit in order:
             key = (unit[0].device, unit[0].dtype)
+            remaining[key] = remaining.get(key, 0) + nbytes(unit)
+        sizes: dict = {}
+        for i, unit in enumerate(order):
+            key = (unit[0].device, unit[0].dtype)
+            limit = bucket_bytes if remaining[key] > 2 * bucket_bytes else last_bucket_bytes
+            size = nbytes(unit)
+            if size >= limit and open_buckets.get(key):
+                close(key)
+                sizes[key] = 0
             open_buckets.setdefault(key, []).append(unit)
-            sizes[key] = sizes.get(key, 0) + sum(p.numel() * p.element_size() for p in unit)
-            if sizes[key] >= bucket_bytes:
+            sizes[key] = sizes.get(key, 0) + size
+            remaining[key] -= size
+            nxt = order[i + 1] if i + 1 < len(order) else None
+            twin = (nxt is not None and len(unit) == 1 and len(nxt) == 1 and nxt[0].shape == unit[0].shape
+                    and (nxt[0].device, nxt[0].dtype) == key and unit[0].dim() >= 2 and size < limit)
+            if sizes[key] >= limit and not twin:
                 close(key)
                 sizes[key] = 0
         for key in list(open_buckets):

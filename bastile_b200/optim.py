@@ -329,21 +329,26 @@ class ShardedAdamW:
         for unit in order:
             key = (unit[0].device, unit[0].dtype)
             remaining[key] = remaining.get(key, 0) + nbytes(unit)
+        def twins(a, b):
+            return (a is not None and b is not None and len(a) == 1 and len(b) == 1 and a[0].dim() >= 2
+                    and a[0].shape == b[0].shape and a[0].device == b[0].device and a[0].dtype == b[0].dtype)
+
         sizes: dict = {}
         for i, unit in enumerate(order):
             key = (unit[0].device, unit[0].dtype)
             limit = bucket_bytes if remaining[key] > 2 * bucket_bytes else last_bucket_bytes
             size = nbytes(unit)
-            if size >= limit and open_buckets.get(key):
+            held = open_buckets.get(key)
+            if size >= limit and held and not twins(held[-1], unit):
                 close(key)
                 sizes[key] = 0
             open_buckets.setdefault(key, []).append(unit)
             sizes[key] = sizes.get(key, 0) + size
             remaining[key] -= size
             nxt = order[i + 1] if i + 1 < len(order) else None
-            twin = (nxt is not None and len(unit) == 1 and len(nxt) == 1 and nxt[0].shape == unit[0].shape
-                    and (nxt[0].device, nxt[0].dtype) == key and unit[0].dim() >= 2 and size < limit)
-            if sizes[key] >= limit and not twin:
+            # a pair stays together; a run of three or more same-shaped tensors may still be cut after a pair
+            pair_open = twins(unit, nxt) and not (len(open_buckets[key]) > 1 and twins(open_buckets[key][-2], unit))
+            if sizes[key] >= limit and not pair_open:
                 close(key)
                 sizes[key] = 0
         for key in list(open_buckets):

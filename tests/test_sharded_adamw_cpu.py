@@ -118,3 +118,41 @@ def test_sharded_adamw_two_gloo_ranks_match_single_process(master):
     # every rank ends with the same parameters
     for a, b in zip(results[0][1], results[1][1]):
         assert torch.equal(a, b)
+
+
+def test_bucket_plan_tapers_and_keeps_large_and_twin_tensors_apart_and_together():
+    """Buckets fill in reverse registration order; the parameters whose gradients arrive last get
+    quarter-size buckets, a tensor as large as a bucket sits alone, and two same-shaped neighbours
+    (gate | up) are never split, so a stacked gradient finds both destinations side by side."""
+    from bastile_b200.optim import ShardedAdamW
+
+    def mat(rows):  # fp32 [rows, 1024] = 4 * rows KiB
+        return torch.nn.Parameter(torch.zeros(rows, 1024))
+
+    # "embedding" 5 MiB, then 8 "layers" of q 1 MiB | gate 1.5 | up 1.5 | norm, then "head" 5 MiB
+    params = [mat(1280)]
+    for _ in range(8):
+        params += [mat(256), mat(384), mat(384), torch.nn.Parameter(torch.zeros(256))]
+    params.append(mat(1280))
+    opt = ShardedAdamW(params, bucket_mb=4, update_fn=lambda *a: None)
+    try:
+        index = {id(p): i for i, p in enumerate(params)}
+        plan = [[index[id(p)] for p in b.params] for b in opt.buckets]
+        sizes = [sum(params[i].numel() * 4 for i in b) for b in plan]
+        assert plan[0] == [len(params) - 1] and plan[-1] == [0]          # head and embedding alone
+        assert sorted(i for b in plan for i in b) == list(range(len(params)))
+        for b in plan:                                                   # gate | up: same bucket, adjacent, in order
+            for i in b:
+                if params[i].shape == (384, 1024) and params[i - 1].shape == (384, 1024):
+                    assert b[b.index(i) - 1] == i - 1
+            assert b == sorted(b)                                        # registration order inside a bucket
+        early = [s for s, b in zip(sizes[1:-1], plan[1:-1]) if min(b) > 16]
+        late = [s for s, b in zip(sizes[1:-1], plan[1:-1]) if max(b) <= 4]
+        assert early and len(late) >= 2 and max(late) < min(early)       # the tail's buckets are the small ones
+        assert all(s >= 4 << 20 for s in early) and all(s < 4 << 20 for s in late)
+        # every parameter is a view into its bucket at an aligned offset
+        for b in opt.buckets:
+            for p, o in zip(b.params, b.offsets):
+                assert o % 128 == 0 and p.data_ptr() == b.flat_p[o:].data_ptr()
+    finally:
+        opt.close()

@@ -597,7 +597,7 @@ class _LigerPatches:
 def train_run(*, dev, rank, world, local, patches="bastile", parallel="single", optimizer="bastile", seq=SEQ_LEN,
               layers=36, intermediate=12288, steps=5, warmup=3, fused_layers=True, gemm_projections="acc",
               overlap_opt=True, tiles="auto", grad_checkpoint=False, measure_e2e=True, sample_clocks=False,
-              master_weights=False, sweep=(), bucket_mb=1024):
+              master_weights=False, sweep=(), bucket_mb=1024, last_bucket_mb=None):
     """Build the model under the given patches / parallel wrapper / optimizer, run `warmup` untimed
     and `steps` timed steps (and, optionally, the same loop fed from pinned host memory), then the
     `sweep` entries (dicts with seq, steps, warmup, grad_checkpoint) on the same model.  Everything
@@ -692,7 +692,7 @@ def train_run(*, dev, rank, world, local, patches="bastile", parallel="single", 
         from bastile_b200.optim import ShardedAdamW
 
         opt = ShardedAdamW(net.parameters(), lr=1e-4, group=dist.group.WORLD, master_weights=master_weights,
-                           bucket_mb=bucket_mb)
+                           bucket_mb=bucket_mb, last_bucket_mb=last_bucket_mb)
         opt_name = "bastile_b200.optim.ShardedAdamW" + (", fp32 master weights" if master_weights else
                                                         ", bf16 params and state")
     elif optimizer == "bastile":
@@ -916,6 +916,9 @@ def main():
                     help="16-bit GEMM results through shared memory + tile stores (on, the library's default) or "
                          "stored by each epilogue thread from registers (off: bt_set_gemm_tile_stores(0))")
     ap.add_argument("--bucket-mb", type=int, default=1024, help="--parallel sharded: size of a gradient bucket")
+    ap.add_argument("--last-bucket-mb", type=int, default=None,
+                    help="--parallel sharded: bucket size for the parameters whose gradients arrive last (default: a "
+                         "quarter of --bucket-mb; equal to --bucket-mb = no tapering)")
     ap.add_argument("--group-rows", type=int, default=0,
                     help="tile rasterisation of the GEMMs: row tiles walked per column tile (0 = library default)")
     ap.add_argument("--dependent-launch", default="on", choices=["on", "off"],
@@ -991,7 +994,7 @@ def main():
                          intermediate=args.intermediate, steps=args.steps, warmup=args.warmup,
                          overlap_opt=not args.no_overlap_optimizer, grad_checkpoint=grad_checkpoint,
                          measure_e2e=True, sample_clocks=True, master_weights=args.master_weights, sweep=sweep,
-                         bucket_mb=args.bucket_mb)
+                         bucket_mb=args.bucket_mb, last_bucket_mb=args.last_bucket_mb)
     m = main_run["main"]
     op_ms = m["op_ms"]
     seq = args.seq

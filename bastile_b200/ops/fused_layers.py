@@ -624,6 +624,10 @@ def attention_forward(self, hidden_states, position_embeddings, attention_mask, 
     out = out.reshape(*lead, -1).contiguous()
     if on_gemm and _projection_mode == "all":
         return shared_input_linear(out, self.o_proj.weight)[0], weights
+    if (_projection_mode == "acc" and plain and out.is_cuda and torch.is_grad_enabled()
+            and not torch.is_autocast_enabled() and _lib.grad_sink(self.o_proj.weight, out.dtype) is not None):
+        # same library products; the weight gradient lands in its registered destination uncopied
+        return AccumulatedInputGradFunction.apply(out, self.o_proj.weight)[0], weights
     return self.o_proj(out), weights
 
 

@@ -247,3 +247,66 @@ def test_sharded_adamw_gradient_sinks_are_written_directly():
         assert_close(a, b, what=name, rtol=1e-2, atol=1e-3)
     opts[1].close()
     assert not any(id(v) in {id(d) for bk in opts[1].buckets for d in bk.sinks} for v in _lib._grad_sinks.values())
+
+
+@pytest.mark.gpu
+def test_sharded_single_rank_whole_model_projection_gradients_land_in_the_buckets():
+    """A small Qwen3 under apply(fused_layers=True) (projections in "acc" mode) with ShardedAdamW:
+    the weight gradients of q/k/v/o, gate/up/down and lm_head are written where the optimizer
+    reduces them, without a copy, and training matches the plain optimizer on unfused projections."""
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+
+    import bastile_b200
+    from bastile_b200 import _lib
+    from bastile_b200.optim import AdamW, ShardedAdamW
+
+    cfg = Qwen3Config(vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=64, rms_norm_eps=1e-6, rope_theta=1e6,
+                      tie_word_embeddings=False, use_cache=False)
+    cfg._attn_implementation = "sdpa"
+    hp = dict(lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    ids = [torch.randint(0, 1024, (2, 64), generator=torch.Generator().manual_seed(s)).cuda() for s in (1, 2, 3)]
+    finals, in_place, first_grads = {}, {}, {"off": {}, "acc": {}}
+    try:
+        for mode in ("off", "acc"):
+            bastile_b200.reset()
+            bastile_b200.apply(fused_layers=True, gemm_projections=mode)
+            torch.manual_seed(9)
+            model = Qwen3ForCausalLM(cfg).cuda().to(torch.bfloat16).train()
+            if mode == "off":
+                opt = AdamW(model.parameters(), **hp)
+            else:
+                opt = ShardedAdamW(model.parameters(), bucket_mb=64, **hp)
+                names = {p: n for n, p in model.named_parameters()}
+                orig = opt._on_grad
+
+                def spy(p, opt=opt, names=names, orig=orig):
+                    b, i = opt._where[p]
+                    in_place.setdefault(names[p], []).append(p.grad.data_ptr() == b.flat_g[b.offsets[i]:].data_ptr())
+                    first_grads["acc"].setdefault(names[p], p.grad.detach().float().clone())
+                    orig(p)
+
+                for h in opt._hooks:
+                    h.remove()
+                opt._hooks = [p.register_post_accumulate_grad_hook(spy) for p in model.parameters()]
+            for step, x in enumerate(ids):
+                opt.zero_grad(set_to_none=True)
+                model(input_ids=x, labels=x).loss.backward()
+                if mode == "off" and step == 0:
+                    first_grads["off"] = {n: p.grad.detach().float().clone() for n, p in model.named_parameters()}
+                opt.step()
+            _lib.check_all_status()
+            finals[mode] = {n: p.detach().float().clone() for n, p in model.named_parameters()}
+            opt.close()
+    finally:
+        bastile_b200.reset()
+    for n, hits in in_place.items():
+        if n.endswith(("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight", "down_proj.weight",
+                       "lm_head.weight")):
+            assert all(hits) and len(hits) == 3, (n, hits)
+    assert set(first_grads["acc"]) == set(first_grads["off"])
+    for n, g in first_grads["off"].items():  # same weights, same batch: the gradients of the first step
+        assert_close(first_grads["acc"][n], g.cpu().numpy(), what=f"grad {n}", rtol=2e-2,
+                     atol=2e-2 * float(g.abs().max()) + 1e-6)
+    for n in finals["off"]:  # three Adam steps move an element by at most 3 * lr whatever its gradient
+        assert_close(finals["acc"][n], finals["off"][n].cpu().numpy(), what=n, rtol=2e-2, atol=8e-3)

@@ -351,7 +351,7 @@ def test_qkv_mode_whole_model_matches_separate_projections():
             out = model(input_ids=ids, labels=ids)
             out.loss.backward()
             _lib.check_status(torch.device(DEV, torch.cuda.current_device()), mode)
-            results[mode] = (float(out.loss), {n: p.grad.detach().float().clone() for n, p in model.named_parameters()})
+            results[mode] = (float(out.loss.detach()), {n: p.grad.detach().float().clone() for n, p in model.named_parameters()})
     finally:
         bastile_b200.reset()
     (l0, g0), (l1, g1) = results["off"], results["qkv"]

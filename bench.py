@@ -9,10 +9,11 @@ intermediate 12288, vocab 151936, bf16) on one sequence of 8192 synthetic tokens
 with RMSNorm, RoPE, the SwiGLU MLP and the fused lm_head + cross-entropy running on
 the bastile_b200 kernels and the optimizer step on bastile_b200.optim (--optimizer torch
 selects torch.optim.AdamW as in the reference's own benchmark,
-tests/benchmarks/e2e/qwen_8b_seqlen.py:80-203); attention and the q/k/v/o projections are
-stock PyTorch.  By default the patch set is `apply(fused_layers=True)` (residual adds folded into
-the norm / down-projection kernels, q/k-norm + RoPE as one kernel; --no-fused-layers for exactly
-the reference's four patches) and, on one GPU, the optimizer updates each large parameter
+tests/benchmarks/e2e/qwen_8b_seqlen.py:80-203); attention and the products of the q/k/v/o
+projections are stock PyTorch (cuDNN, cuBLAS).  By default the patch set is
+`apply(fused_layers=True)` (residual adds folded into the norm / down-projection kernels,
+q/k-norm + RoPE as one kernel, the q/k/v input gradient accumulated by the projection GEMMs;
+--no-fused-layers for exactly the reference's four patches) and, on one GPU, the optimizer updates each large parameter
 underneath the backward pass as soon as its gradient is complete (--no-overlap-optimizer).
 
 With N > 1 (launched by torchrun, one rank per GPU) every rank steps its own sequence: weak

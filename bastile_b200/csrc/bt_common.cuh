@@ -254,6 +254,19 @@ inline cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 bloc
     }                                                                        \
   } while (0)
 
+// CTAs of `kern` that one SM holds at once (at least 1), for kernels whose grid should be exactly
+// one wave.  `smem` is the dynamic shared memory of the launch (an upper bound is fine when it is
+// small next to the SM's).
+template <typename K>
+inline int resident_ctas(K kern, int threads, size_t smem) {
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, smem) != cudaSuccess || n < 1) {
+    (void)cudaGetLastError();
+    n = 1;
+  }
+  return n;
+}
+
 // RMSNorm backward scratch: K private copies of the N fp32 column sums (CTA b adds into
 // copy b % K, which divides the same-address atomic traffic by K) followed by one arrival
 // counter.  K * N stays within 16384 words.

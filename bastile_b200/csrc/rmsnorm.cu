@@ -498,10 +498,14 @@ int bwd_t(const void* dy, const void* x, const void* w, const float* rstd, void*
   }
   if (vec_ok && pick_rows(nv, 4, &c)) {
     const int64_t rows_per_iter = static_cast<int64_t>(kThreads / c.lpr) * c.rpi;
-    const int grid = grid_for(ceil_div(M, rows_per_iter), 4);
     const size_t smem = static_cast<size_t>(N) * sizeof(float);
+    // One wave exactly: the kernel walks its rows with a grid stride and ends with one set of
+    // column-sum reductions per CTA, so the grid is what is resident at once (3 CTAs per SM at its
+    // register count; 4 per SM meant a second wave at a third of the occupancy).
 #define BT_BWD(L, V, R)                                                                         \
   if (c.lpr == L && c.vpt == V) {                                                               \
+    static const int resident = resident_ctas(rms_bwd_rows<T, V, L, R, ADD>, kThreads, 4 * 1024);  \
+    const int grid = grid_for(ceil_div(M, rows_per_iter), resident);                            \
     BT_CHECK_LAUNCHED(launch_dependent(rms_bwd_rows<T, V, L, R, ADD>, dim3(grid), dim3(kThreads),  \
                                        smem, s, gp, xp, wp, rstd, dxp, dwp, wsp, M,             \
                                        static_cast<int>(N), ld_dy, ld_x, ld_dx, rp, rr.ld_dres), \

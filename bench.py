@@ -438,6 +438,24 @@ def per_op_bench(peaks, only=None, iters=None, rows=None, lce_chunk=None):
         # fwd: gate, up in, h out; bwd: dh, gate, up in, dgate, dup out
         out[f"swiglu_elementwise_{m}x{n}_fwd_bwd"] = hbm_entry(make_swi, swi, 8 * m * n * 2, iters or 20)
 
+    if want("adamw"):
+        from bastile_b200.optim import AdamW as OurAdamW
+
+        m, n = 12288, 4096  # one gate / up projection weight
+
+        def make_adam():
+            w = torch.nn.Parameter((torch.randn(m, n, device=dev) * 0.02).to(bf))
+            w.grad = (torch.randn(m, n, device=dev) * 1e-3).to(bf)
+            opt_w = OurAdamW([w], lr=1e-4)
+            opt_w.step()  # creates the moments
+            return w, opt_w
+
+        def adam(t):
+            t[1].step()
+
+        # parameter, both moments: read and written; gradient: read (bf16 everything)
+        out[f"adamw_{m}x{n}_step"] = hbm_entry(make_adam, adam, 7 * m * n * 2, iters or 20)
+
     if want("mlp"):
         t_mlp = rows or 8192
         xm = torch.randn(t_mlp, 4096, device=dev, dtype=bf).requires_grad_(True)
@@ -926,7 +944,7 @@ def main():
                     help="launch the library's kernels as programmatic dependents of their predecessors (on, the "
                          "library's default) or the ordinary way (off: bt_set_dependent_launch(0))")
     ap.add_argument("--no-per-op", action="store_true")
-    ap.add_argument("--only-op", default=None, choices=["rmsnorm", "rope", "swiglu", "mlp", "lce"],
+    ap.add_argument("--only-op", default=None, choices=["rmsnorm", "rope", "swiglu", "adamw", "mlp", "lce"],
                     help="run just this op's forward+backward micro-benchmark (small case for profilers)")
     ap.add_argument("--op-iters", type=int, default=None)
     ap.add_argument("--lce-chunk", type=int, default=None, help="with --only-op lce: rows per chunk (chunk_size=)")

@@ -129,7 +129,8 @@ class ClockSampler:
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm),
+                "sm_mhz_highest_seen": sm[-1]}
 
 
 # ------------------------------------------------------------------- CPU baseline
@@ -1086,7 +1087,11 @@ def main():
     if world == 1:
         line["reference_published"] = REFERENCE_CHART
         if not args.no_per_op:
-            line["per_op"] = guarded("per_op", lambda: per_op_bench(peaks))
+            with ClockSampler(local) as op_clocks:
+                line["per_op"] = guarded("per_op", lambda: per_op_bench(peaks))
+            # the micro-benchmarks leave the GPU idle between calls, so the median says little; the
+            # highest clock seen tells a box whose clocks are held down from a healthy one
+            line["per_op_clocks"] = op_clocks.summary()
             torch.cuda.empty_cache()
         if extras and seq == SEQ_LEN:
             sw = guarded("intermediate 14336", lambda: train_run(

@@ -981,10 +981,12 @@ def main():
     _lib.get_lib().bt_set_gemm_group_rows(args.group_rows)
     _lib.get_lib().bt_set_dependent_launch(1 if args.dependent_launch == "on" else 0)
     if args.only_op:
-        res = per_op_bench(peaks, only=args.only_op, iters=args.op_iters, rows=args.op_rows, lce_chunk=args.lce_chunk)
+        with ClockSampler(local) as op_clocks:
+            res = per_op_bench(peaks, only=args.only_op, iters=args.op_iters, rows=args.op_rows, lce_chunk=args.lce_chunk)
         _lib.check_status(dev, "per-op benchmark")
         if rank == 0:
-            print(json.dumps({"per_op": res, "peaks": peaks, "peak_kind": peak_kind, "n_gpus": world}), flush=True)
+            print(json.dumps({"per_op": res, "peaks": peaks, "peak_kind": peak_kind, "n_gpus": world,
+                              "clocks": op_clocks.summary()}), flush=True)
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()
